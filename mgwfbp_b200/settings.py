@@ -1,0 +1,93 @@
+# -*- coding: utf-8 -*-
+"""Process-wide switches and the shared logger.
+
+Mirrors the switch set of the reference's ``settings.py:7-53`` (``DEBUG``, ``WARMUP``,
+``CONNECTION``, ``FP16``, ``ADAPTIVE_MERGE``, ``ORIGINAL_HOROVOD``, ``MAX_EPOCHS``, ``PREFIX``,
+``logger``, ``formatter``, ``hostname``) so scripts written against the reference keep working,
+and adds the switches that only exist here (``FAKE_DATA`` made real, fused-update control,
+communication algorithm selection).  Every switch can be overridden from the environment as
+``MGWFBP_<NAME>`` so launch scripts need not edit this file.
+"""
+from __future__ import annotations
+
+import logging
+import os
+import socket
+
+
+def _env_flag(name: str, default: bool) -> bool:
+    raw = os.environ.get('MGWFBP_' + name)
+    if raw is None:
+        return default
+    return raw.strip().lower() not in ('0', 'false', 'no', 'off', '')
+
+
+def _env_str(name: str, default: str) -> str:
+    return os.environ.get('MGWFBP_' + name, default)
+
+
+DEBUG = _env_flag('DEBUG', False)
+
+# Kept for name compatibility with the reference (unused there as well).
+GPU_CONSTRUCTION = True
+DELAY_COMM = 1
+EXCHANGE_MODE = 'MODEL'
+TENSORBOARD = False
+
+# Linear LR warm-up over the first five epochs (reference dl_trainer.py:612-621).
+WARMUP = _env_flag('WARMUP', True)
+
+# Which alpha-beta table the scheduler falls back to when nothing was measured.
+# '10GbE' and '56GbIB' are the reference's tables; 'NVLink5' is the table for the
+# peer-to-peer kernels of this package on an NVSwitch box.
+CONNECTION = _env_str('CONNECTION', 'NVLink5')
+
+FP16 = _env_flag('FP16', False)
+ADAPTIVE_MERGE = _env_flag('ADAPTIVE_MERGE', True)
+ORIGINAL_HOROVOD = _env_flag('ORIGINAL_HOROVOD', False)
+
+# The reference declares FAKE_DATA but never reads it; here it selects synthetic datasets.
+FAKE_DATA = _env_flag('FAKE_DATA', False)
+
+# Apply the momentum-SGD update inside the all-reduce kernel of each merged group
+# (weights change during backward, ``step()`` only waits).  Switched off automatically
+# for optimizers other than plain SGD and whenever ``norm_clip`` is requested.
+FUSED_UPDATE = _env_flag('FUSED_UPDATE', True)
+
+# After the fused kernels ran, leave the averaged gradient readable in ``p.grad``.
+WRITE_BACK_GRADS = _env_flag('WRITE_BACK_GRADS', True)
+
+# 'auto' | 'oneshot' | 'twoshot' | 'nvls'
+COMM_ALGO = _env_str('COMM_ALGO', 'auto')
+
+MAX_EPOCHS = 200
+
+
+def _build_prefix() -> str:
+    prefix = ''
+    if WARMUP:
+        prefix += 'gwarmup'
+    prefix += '-dc' + str(DELAY_COMM)
+    prefix += '-' + EXCHANGE_MODE.lower()
+    exp = '-tpds' + CONNECTION
+    if FP16:
+        exp += '-fp16'
+    prefix += exp
+    if ADAPTIVE_MERGE:
+        prefix += '-ada'
+    if ORIGINAL_HOROVOD:
+        prefix += '-hvd'
+    return prefix
+
+
+PREFIX = _build_prefix()
+
+hostname = socket.gethostname()
+logger = logging.getLogger(hostname)
+logger.setLevel(logging.DEBUG if DEBUG else logging.INFO)
+formatter = logging.Formatter('%(asctime)s [%(filename)s:%(lineno)d] %(levelname)s %(message)s')
+if not logger.handlers:
+    strhdlr = logging.StreamHandler()
+    strhdlr.setFormatter(formatter)
+    logger.addHandler(strhdlr)
+logger.propagate = False

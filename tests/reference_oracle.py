@@ -45,7 +45,6 @@ def main():
 
     import logging
     import torch
-    torch.set_num_threads(1)
     import settings
     settings.logger.setLevel(logging.ERROR)
     import distributed_optimizer as ref_opt
@@ -58,7 +57,9 @@ def main():
         ref_opt.ADAPTIVE_MERGE = bool(req['adaptive'])
         params = collections.OrderedDict()
         for name, numel in req['layers']:
-            params[name] = torch.nn.Parameter(torch.zeros(int(numel)))
+            # meta tensors carry sizes without memory; only the backward case needs real storage
+            dev = 'cpu' if req.get('run_backward') else 'meta'
+            params[name] = torch.nn.Parameter(torch.zeros(int(numel), device=dev))
         sgd = torch.optim.SGD(list(params.values()), lr=0.1)
         names = [n for n, _ in req['layers']]
         tb = req.get('tb')

@@ -1,0 +1,218 @@
+"""CPU / gloo plumbing: two real processes, the public API end to end (no GPU)."""
+import os
+import socket
+import sys
+import tempfile
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(('127.0.0.1', 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, fn, args, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR='127.0.0.1',
+                      MASTER_PORT=str(port), MGWFBP_CONNECTION='10GbE')
+    sys.path.insert(0, ROOT)
+    torch.set_num_threads(1)
+    import mgwfbp_b200 as hvd
+    hvd.init(timeout_s=120)
+    try:
+        result = fn(rank, world, *args)
+        torch.save(result, os.path.join(out_dir, 'rank%d.pt' % rank))
+    finally:
+        hvd.shutdown()
+
+
+def run_ranks(fn, args=(), world=2):
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_worker, args=(world, _free_port(), fn, args, d), nprocs=world, join=True)
+        return [torch.load(os.path.join(d, 'rank%d.pt' % r), weights_only=False) for r in range(world)]
+
+
+# ----------------------------------------------------------------------------- worker bodies
+def _train_resnet20(rank, world, policy, steps):
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
+    from mgwfbp_b200.trainer import DLTrainer
+    from mgwfbp_b200.utils.profiling import benchmark
+    settings.ADAPTIVE_MERGE = policy == 'mgwfbp'
+    torch.manual_seed(0)
+    trainer = DLTrainer(rank, world, dist=False, batch_size=32, ngpus=0, data_dir='synthetic', dataset='cifar10',
+                        dnn='resnet20', lr=0.1, nworkers=world, prefix='allreduce', seed=0)
+    seq = times = None
+    if policy == 'mgwfbp':
+        seq, times, sizes = benchmark(trainer, warmup=1, iteration=2)
+        times = hvd.broadcast_object(list(times), 0)
+    threshold = {'wfbp': 0, 'single': 524288000, 'mgwfbp': 0, 'bucket': 20000}[policy]
+    opt = hvd.DistributedOptimizer(trainer.optimizer, named_parameters=trainer.net.named_parameters(),
+                                   seq_layernames=seq, layerwise_times=times, threshold=threshold)
+    hvd.broadcast_parameters(trainer.net.state_dict(), root_rank=0)
+    trainer.update_optimizer(opt)
+    # identical data on every policy: a fixed generator per rank
+    g = torch.Generator().manual_seed(100 + rank)
+    losses = []
+    for _ in range(steps):
+        x = torch.randn(32, 3, 32, 32, generator=g)
+        y = torch.randint(0, 10, (32,), generator=g)
+        opt.zero_grad()
+        trainer.train(1, data=(x, y))
+        trainer.update_model()
+        losses.append(trainer.loss)
+    return {'params': {k: v.clone() for k, v in trainer.net.state_dict().items()}, 'losses': losses,
+            'ngroups': len(opt.merge_schedule.groups), 'iters': opt.train_iter}
+
+
+def _train_lenet_vs_concat(rank, world, steps):
+    """No BatchNorm, so data parallel over two halves must equal one process on the whole batch."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200.models import create_net
+    torch.manual_seed(0)
+    net, _ = create_net(10, 'lenet')
+    ref, _ = create_net(10, 'lenet')
+    hvd.broadcast_parameters(net.state_dict(), 0)
+    ref.load_state_dict(net.state_dict())
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(net.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4),
+                                   named_parameters=net.named_parameters(), threshold=3000)
+    ref_opt = torch.optim.SGD(ref.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+    crit = torch.nn.CrossEntropyLoss()
+    g = torch.Generator().manual_seed(7)
+    for _ in range(steps):
+        x = torch.randn(world * 8, 1, 32, 32, generator=g)
+        y = torch.randint(0, 10, (world * 8,), generator=g)
+        opt.zero_grad()
+        crit(net(x[rank * 8:(rank + 1) * 8]), y[rank * 8:(rank + 1) * 8]).backward()
+        opt.step()
+        ref_opt.zero_grad()
+        crit(ref(x), y).backward()
+        ref_opt.step()
+    return {'dp': [p.detach().clone() for p in net.parameters()], 'ref': [p.detach().clone() for p in ref.parameters()]}
+
+
+def _accumulate_and_clip(rank, world):
+    import mgwfbp_b200 as hvd
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Tanh(), torch.nn.Linear(16, 4))
+    hvd.broadcast_parameters(net.state_dict(), 0)
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(net.parameters(), lr=0.1), named_parameters=net.named_parameters(),
+                                   threshold=524288000)
+    g = torch.Generator().manual_seed(rank)
+    xs = [torch.randn(4, 8, generator=g) for _ in range(2)]
+    opt.zero_grad()
+    opt.local = True
+    net(xs[0]).pow(2).mean().backward()
+    local_only = [p.grad.clone() for p in net.parameters()]
+    opt.local = False
+    net(xs[1]).pow(2).mean().backward()
+    opt.synchronize()                      # averaged, accumulated gradients are visible here
+    grads = [p.grad.clone() for p in net.parameters()]
+    total = torch.nn.utils.clip_grad_norm_(net.parameters(), 1e-3)
+    opt.step()
+    return {'local_only': local_only, 'grads': grads, 'total_norm': float(total),
+            'params': [p.detach().clone() for p in net.parameters()]}
+
+
+def _broadcast_optimizer_state(rank, world):
+    import mgwfbp_b200 as hvd
+    torch.manual_seed(rank)                # different weights / state per rank on purpose
+    net = torch.nn.Linear(4, 3)
+    opt = torch.optim.SGD(net.parameters(), lr=0.1 * (rank + 1), momentum=0.9)
+    net(torch.randn(2, 4)).sum().backward()
+    opt.step()
+    hvd.broadcast_parameters(net.state_dict(), 0)
+    hvd.broadcast_optimizer_state(opt, 0)
+    return {'lr': opt.param_groups[0]['lr'], 'mom': [opt.state[p]['momentum_buffer'].clone() for p in net.parameters()],
+            'w': net.weight.detach().clone()}
+
+
+def _mismatched_schedule(rank, world):
+    import mgwfbp_b200 as hvd
+    net = torch.nn.Sequential(torch.nn.Linear(8, 16), torch.nn.Linear(16, 4))
+    try:
+        hvd.DistributedOptimizer(torch.optim.SGD(net.parameters(), lr=0.1), named_parameters=net.named_parameters(),
+                                 threshold=0 if rank == 0 else 524288000)
+    except RuntimeError as e:
+        return {'error': str(e)}
+    return {'error': None}
+
+
+def _cli_run(rank, world, tmp):
+    os.chdir(tmp)
+    sys.argv = ['dist_trainer.py']
+    import dist_trainer
+    trainer = dist_trainer.mgwfbp('resnet20', 'cifar10', 'synthetic', world, 0.1, 8, 1, 1, world, None, 35, None, 1, 0,
+                                  max_iters=3)
+    return {'iter': trainer.get_train_iter()}
+
+
+# ----------------------------------------------------------------------------- tests
+@pytest.fixture(scope='module')
+def resnet20_runs():
+    return {p: run_ranks(_train_resnet20, (p, 3)) for p in ('wfbp', 'single', 'mgwfbp', 'bucket')}
+
+
+def test_replicas_stay_bit_identical(resnet20_runs):
+    for policy, (r0, r1) in resnet20_runs.items():
+        for k in r0['params']:
+            if 'running_' in k or 'num_batches' in k:
+                continue          # BatchNorm statistics are per worker, as in the reference
+            assert torch.equal(r0['params'][k], r1['params'][k]), (policy, k)
+        assert r0['iters'] == 3
+
+
+def test_merge_policies_agree(resnet20_runs):
+    base = resnet20_runs['wfbp'][0]['params']
+    assert resnet20_runs['wfbp'][0]['ngroups'] == 59
+    assert resnet20_runs['single'][0]['ngroups'] == 1
+    assert 1 < resnet20_runs['bucket'][0]['ngroups'] < 59
+    for policy in ('single', 'mgwfbp', 'bucket'):
+        other = resnet20_runs[policy][0]['params']
+        for k in base:
+            # running statistics also see the profiler's extra forward passes in the mgwfbp run
+            if base[k].dtype.is_floating_point and 'running_' not in k:
+                torch.testing.assert_close(other[k], base[k], rtol=1e-5, atol=1e-6, msg=lambda m: '%s %s: %s' % (policy, k, m))
+    assert all(l == l for l in resnet20_runs['mgwfbp'][0]['losses'])      # finite, not NaN
+
+
+def test_data_parallel_equals_large_batch():
+    r0, r1 = run_ranks(_train_lenet_vs_concat, (4,))
+    for dp, ref in zip(r0['dp'], r0['ref']):
+        torch.testing.assert_close(dp, ref, rtol=1e-4, atol=1e-6)
+    for a, b in zip(r0['dp'], r1['dp']):
+        assert torch.equal(a, b)
+
+
+def test_local_accumulation_synchronize_and_clip():
+    r0, r1 = run_ranks(_accumulate_and_clip)
+    for a, b in zip(r0['grads'], r1['grads']):
+        assert torch.equal(a, b)                       # averaged gradients agree across ranks
+    assert any(not torch.equal(a, b) for a, b in zip(r0['local_only'], r1['local_only']))
+    for a, b in zip(r0['params'], r1['params']):
+        assert torch.equal(a, b)
+    assert r0['total_norm'] > 1e-3
+
+
+def test_broadcast_optimizer_state():
+    r0, r1 = run_ranks(_broadcast_optimizer_state)
+    assert r0['lr'] == r1['lr'] == pytest.approx(0.1)
+    for a, b in zip(r0['mom'], r1['mom']):
+        assert torch.equal(a, b)
+    assert torch.equal(r0['w'], r1['w'])
+
+
+def test_mismatched_schedule_is_detected():
+    r0, r1 = run_ranks(_mismatched_schedule)
+    assert r0['error'] and 'disagree' in r0['error']
+    assert r1['error'] and 'disagree' in r1['error']
+
+
+def test_dist_trainer_loop_runs(tmp_path):
+    r0, r1 = run_ranks(_cli_run, (str(tmp_path),))
+    assert r0['iter'] == 3 and r1['iter'] == 3

@@ -22,8 +22,7 @@ TOY_TB = [1e-4, 2e-5, 3e-4, 1e-5, 5e-5, 1e-5, 2e-4, 1e-5]
 _MODELS = ['resnet20', 'resnet50', 'densenet201', 'vgg16i', 'lstm']
 _WORLDS = [(2, '10GbE'), (4, '10GbE'), (8, '10GbE'), (8, '56GbIB'), (16, '56GbIB')]
 _THRESHOLDS = [0, 1000, 65536, 1 << 20, 524288000]
-_BIG = ('vgg16i', 'lstm')        # the oracle materialises every parameter: keep big models to two cases
-_MG_CASES = [(d, w, c) for d in _MODELS for (w, c) in _WORLDS if d not in _BIG or (w, c) in ((4, '10GbE'), (8, '56GbIB'))]
+_MG_CASES = [(d, w, c) for d in _MODELS for (w, c) in _WORLDS]
 _layers_cache = {}
 
 

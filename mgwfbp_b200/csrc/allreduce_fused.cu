@@ -1,0 +1,220 @@
+// Fused gradient all-reduce for one merged group, launched from the backward hook of the group's
+// last tensor on a side stream:
+//
+//   pack (gather the group's scattered gradient tensors through a pointer table)
+//   -> sum across GPUs through peer memory (NVLink 5 / NVSwitch loads and stores, or NVLS multimem)
+//   -> x 1/N
+//   -> weight decay + momentum + learning-rate update of the parameters (optional)
+//   -> averaged gradient written back / sum of squares emitted (optional)
+//
+// in ONE kernel.  No NCCL call and no separate elementwise kernel runs on this path.
+//
+// Work split: CTA b owns a contiguous chunk of the group's float4 slots and only ever talks to CTA
+// b of the other ranks, through its own row of flags, so there is no grid-wide barrier and CTAs of
+// one launch need not be co-resident.  Flags carry a per-CTA launch counter that only grows, so
+// they are never reset and a slow rank cannot confuse two launches.
+//
+// Algorithms
+//   one-shot : every rank stores its packed chunk into slot [rank] of every peer's inbox, one
+//              barrier, every rank sums the N local slots in rank order.  (N-1)*S bytes out per GPU,
+//              one NVLink traversal of latency.  The inbox is double-buffered by launch parity.
+//   two-shot : pack into the local staging buffer, barrier, rank r pulls sub-chunk r from all
+//              peers and sums in rank order, stores the average into every peer's staging buffer,
+//              barrier, every rank consumes its (now averaged) local buffer.  2*(N-1)/N*S bytes.
+//   NVLS     : as two-shot, but the pull is one multimem.ld_reduce (the switch adds the N copies)
+//              and the push one multimem.st on the multicast address of the staging buffer.
+// Every rank applies the same arithmetic to the same reduced values, so replicas stay bit-identical.
+//
+// Every wait is bounded: after `timeout_ns` the CTA records (code, peer, expected, observed, cta) in
+// the host-visible status block, skips the rest of its work and returns normally.
+#include "api.h"
+
+namespace {
+
+struct Smem {
+    int failed;
+    float red[32];
+};
+
+__device__ __forceinline__ uint32_t* flag_slot(uint32_t* base, int phase, int cta, int src) {
+    return base + ((size_t)(phase * MGW_MAX_CTAS + cta) * MGW_MAX_RANKS + src);
+}
+
+// CTA-to-CTA barrier across ranks.  Threads 0..world-1 each signal one peer and wait for that peer.
+__device__ __forceinline__ bool rank_barrier(const MgwAllreduceArgs& a, int phase, uint32_t e, Smem* sm) {
+    __syncthreads();                                   // this CTA's earlier stores are issued
+    const int t = threadIdx.x;
+    if (t < a.world) {
+        __threadfence_system();
+        mgw_st_release_sys(flag_slot(a.flags[t], phase, blockIdx.x, a.rank), e);
+        uint32_t seen = 0;
+        if (!mgw_wait_flag(flag_slot(a.flags[a.rank], phase, blockIdx.x, t), e, a.timeout_ns, &seen)) {
+            mgw_report(a.status, MGW_STATUS_TIMEOUT, t, (int)e, (int)seen);
+            sm->failed = 1;
+        }
+    }
+    __syncthreads();
+    return sm->failed == 0;
+}
+
+__device__ __forceinline__ float4 add4(float4 a, float4 b) {
+    return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w);
+}
+
+__device__ __forceinline__ float4 scale4(float4 a, float s) {
+    return make_float4(a.x * s, a.y * s, a.z * s, a.w * s);
+}
+
+__device__ __forceinline__ float4 multimem_ld_reduce(const float4* mc) {
+    float4 v;
+    asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(mc) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void multimem_st(float4* mc, float4 v) {
+    asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+                 ::"l"(mc), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+// W > 0: world size known at compile time (loops unroll); W == 0: read it from the arguments.
+template <int W, int ALGO>
+__global__ void __launch_bounds__(512) mgw_allreduce_kernel(const MgwAllreduceArgs a) {
+    __shared__ Smem sm;
+    const int world = W > 0 ? W : a.world;
+    const int tid = threadIdx.x, nthr = blockDim.x, b = blockIdx.x;
+    if (tid == 0) sm.failed = 0;
+    const uint32_t e = a.epoch[b] + 1u;
+    const MgwGroup& g = a.group;
+    const float inv = 1.f / (float)world;
+
+    // chunk of this CTA, a multiple of `world` slots so that sub-chunks are equal
+    int per = (g.n_vec + gridDim.x - 1) / gridDim.x;
+    per = (per + world - 1) / world * world;
+    const int c0 = min(g.n_vec, b * per);
+    const int c1 = min(g.n_vec, c0 + per);
+    int hint_l = -1, hint_c = -1;
+    float sumsq = 0.f;
+    bool ok = true;
+
+    if (ALGO == MGW_ALGO_ONESHOT) {
+        const size_t row = (size_t)a.inbox_stride;
+        const size_t parity_base = (size_t)(e & 1u) * world * row;
+        for (int v = c0 + tid; v < c1; v += nthr) {
+            const float4 x = mgw_load_grad(g, v, hint_l, 1.f);
+#pragma unroll
+            for (int i = 0; i < (W > 0 ? W : MGW_MAX_RANKS); ++i) {
+                if (i < world) {
+                    int q = a.rank + 1 + i;
+                    if (q >= world) q -= world;
+                    float4* inbox = reinterpret_cast<float4*>(a.stage[q]) + parity_base + (size_t)a.rank * row;
+                    mgw_st_peer(inbox + v, x);
+                }
+            }
+        }
+        ok = rank_barrier(a, 0, e, &sm);
+        if (ok) {
+            const float4* mine = reinterpret_cast<const float4*>(a.stage[a.rank]) + parity_base;
+            for (int v = c0 + tid; v < c1; v += nthr) {
+                float4 acc = mgw_ld_peer(mine + v);
+#pragma unroll
+                for (int s = 1; s < (W > 0 ? W : MGW_MAX_RANKS); ++s)
+                    if (s < world) acc = add4(acc, mgw_ld_peer(mine + (size_t)s * row + v));
+                mgw_consume(g, v, scale4(acc, inv), a.mode, a.hyper, a.first_step, hint_c, sumsq);
+            }
+        }
+    } else {
+        float4* local = reinterpret_cast<float4*>(a.stage[a.rank]);
+        for (int v = c0 + tid; v < c1; v += nthr) mgw_st_peer(local + v, mgw_load_grad(g, v, hint_l, 1.f));
+        ok = rank_barrier(a, 0, e, &sm);
+        if (ok) {
+            const int sub = per / world;
+            const int s0 = min(c1, c0 + a.rank * sub);
+            const int s1 = min(c1, s0 + sub);
+            if (ALGO == MGW_ALGO_NVLS) {
+                float4* mc = reinterpret_cast<float4*>(a.mc_stage);
+                for (int v = s0 + tid; v < s1; v += nthr) multimem_st(mc + v, scale4(multimem_ld_reduce(mc + v), inv));
+            } else {
+                for (int v = s0 + tid; v < s1; v += nthr) {
+                    float4 x[W > 0 ? W : MGW_MAX_RANKS];
+#pragma unroll
+                    for (int q = 0; q < (W > 0 ? W : MGW_MAX_RANKS); ++q)
+                        if (q < world) x[q] = mgw_ld_peer(reinterpret_cast<const float4*>(a.stage[q]) + v);
+                    float4 acc = x[0];
+#pragma unroll
+                    for (int q = 1; q < (W > 0 ? W : MGW_MAX_RANKS); ++q)
+                        if (q < world) acc = add4(acc, x[q]);
+                    acc = scale4(acc, inv);
+#pragma unroll
+                    for (int i = 0; i < (W > 0 ? W : MGW_MAX_RANKS); ++i) {
+                        if (i < world) {
+                            int q = a.rank + 1 + i;
+                            if (q >= world) q -= world;
+                            mgw_st_peer(reinterpret_cast<float4*>(a.stage[q]) + v, acc);
+                        }
+                    }
+                }
+            }
+            ok = rank_barrier(a, 1, e, &sm);
+        }
+        if (ok) {
+            for (int v = c0 + tid; v < c1; v += nthr)
+                mgw_consume(g, v, mgw_ld_peer(local + v), a.mode, a.hyper, a.first_step, hint_c, sumsq);
+        }
+    }
+
+    if (a.mode & MGW_MODE_SUMSQ) {
+        const float r = mgw_block_sum(ok ? sumsq : 0.f, sm.red);
+        if (tid == 0) a.sumsq_partials[b] = r;
+    }
+    __syncthreads();
+    if (tid == 0) a.epoch[b] = e;          // advance even after a timeout: the launch counter stays in step
+}
+
+template <int ALGO>
+cudaError_t launch_world(const MgwAllreduceArgs& a, cudaStream_t s) {
+    dim3 grid(a.n_ctas), block(a.n_threads);
+    switch (a.world) {
+        case 2: mgw_allreduce_kernel<2, ALGO><<<grid, block, 0, s>>>(a); break;
+        case 4: mgw_allreduce_kernel<4, ALGO><<<grid, block, 0, s>>>(a); break;
+        case 8: mgw_allreduce_kernel<8, ALGO><<<grid, block, 0, s>>>(a); break;
+        default: mgw_allreduce_kernel<0, ALGO><<<grid, block, 0, s>>>(a); break;
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace
+
+extern "C" size_t mgw_flag_block_bytes(void) {
+    return sizeof(uint32_t) * 2 * MGW_MAX_CTAS * MGW_MAX_RANKS;
+}
+
+extern "C" size_t mgw_stage_bytes(int algo, int n_vec, int world) {
+    const size_t one = (size_t)n_vec * sizeof(float4);
+    return algo == MGW_ALGO_ONESHOT ? one * 2 * (size_t)world : one;
+}
+
+extern "C" int mgw_allreduce_group(const MgwAllreduceArgs* args, void* stream) {
+    if (args == nullptr) return MGW_ERR_ARG;
+    const MgwAllreduceArgs& a = *args;
+    if (a.world < 1 || a.world > MGW_MAX_RANKS || a.rank < 0 || a.rank >= a.world) return MGW_ERR_ARG;
+    if (a.n_ctas < 1 || a.n_ctas > MGW_MAX_CTAS) return MGW_ERR_ARG;
+    if (a.n_threads < 32 || a.n_threads > 512 || (a.n_threads & 31) || a.n_threads < a.world) return MGW_ERR_ARG;
+    if (a.group.n_vec < 0 || a.epoch == nullptr) return MGW_ERR_ARG;
+    if ((a.mode & MGW_MODE_SUMSQ) && a.sumsq_partials == nullptr) return MGW_ERR_ARG;
+    if ((a.mode & MGW_MODE_UPDATE) && a.hyper == nullptr) return MGW_ERR_ARG;
+    if (a.algo == MGW_ALGO_NVLS && a.mc_stage == nullptr) return MGW_ERR_ARG;
+    if (a.algo == MGW_ALGO_ONESHOT && a.inbox_stride < a.group.n_vec) return MGW_ERR_ARG;
+    for (int r = 0; r < a.world; ++r)
+        if (a.stage[r] == nullptr || a.flags[r] == nullptr) return MGW_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    cudaError_t err;
+    switch (a.algo) {
+        case MGW_ALGO_ONESHOT: err = launch_world<MGW_ALGO_ONESHOT>(a, s); break;
+        case MGW_ALGO_TWOSHOT: err = launch_world<MGW_ALGO_TWOSHOT>(a, s); break;
+        case MGW_ALGO_NVLS: err = launch_world<MGW_ALGO_NVLS>(a, s); break;
+        default: return MGW_ERR_ARG;
+    }
+    MGW_CUDA_CHECK(err);
+    return MGW_OK;
+}

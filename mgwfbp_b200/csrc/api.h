@@ -1,0 +1,63 @@
+// C ABI of libmgwfbp_b200.so.  Every entry point returns MGW_OK (0) or an MGW_ERR_* code;
+// mgw_last_error() gives the text of the most recent failure on the calling thread.
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+#include "common.cuh"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* mgw_last_error(void);
+int mgw_version(void);
+
+// ---- symmetric heap (symm_heap.cu): one cudaMalloc region per rank, mapped into every peer --------
+int mgw_heap_create(size_t bytes, void** base_out);
+int mgw_heap_export(void* base, void* handle64_out);                 // 64-byte IPC handle
+int mgw_heap_open(const void* handle64, void** peer_base_out);      // enables peer access lazily
+int mgw_heap_close(void* peer_base);
+int mgw_heap_destroy(void* base);
+int mgw_host_status_alloc(int n_ints, int** host_ptr_out);           // pinned, device-visible status block
+int mgw_host_status_free(int* host_ptr);
+
+// ---- fused all-reduce (+ SGD update) of one merged group (allreduce_fused.cu) ---------------------
+#define MGW_ALGO_ONESHOT 0
+#define MGW_ALGO_TWOSHOT 1
+#define MGW_ALGO_NVLS 2
+
+typedef struct {
+    MgwGroup group;
+    float* stage[MGW_MAX_RANKS];        // every rank's staging area of this group (own rank included)
+    uint32_t* flags[MGW_MAX_RANKS];     // every rank's flag block
+    uint32_t* epoch;                    // this rank's per-CTA launch counters [MGW_MAX_CTAS]
+    float* mc_stage;                    // NVSwitch multicast address of the staging area, or null
+    const MgwHyper* hyper;
+    float* sumsq_partials;              // [n_ctas] or null
+    int* status;                        // 8 ints, host-visible
+    int rank, world;
+    int algo, n_ctas, n_threads;
+    int mode, first_step;
+    int inbox_stride;                   // one-shot: float4 slots between consecutive inbox rows (>= n_vec)
+    int reserved;
+    unsigned long long timeout_ns;
+} MgwAllreduceArgs;
+
+int mgw_allreduce_group(const MgwAllreduceArgs* args, void* stream);
+size_t mgw_flag_block_bytes(void);
+// staging bytes one rank needs for a group of n_vec float4 slots under `algo`
+size_t mgw_stage_bytes(int algo, int n_vec, int world);
+
+// ---- standalone multi-tensor SGD (multi_tensor_sgd.cu) ----------------------------------------------
+// grad_scale multiplies every gradient first; clip_coef (device pointer, may be null) multiplies it too.
+int mgw_multi_tensor_sgd(const MgwGroup* group, const MgwHyper* hyper, const float* clip_coef, float grad_scale,
+                         int first_step, int mode, float* sumsq_partials, int n_ctas, void* stream);
+// Sum `n` partial sums of squares in a fixed order; writes total norm to out[0] and
+// min(1, max_norm / (norm + 1e-6)) to out[1].
+int mgw_clip_coef(const float* partials, int n, float max_norm, float* out2, void* stream);
+// Sum of squares of the gradients of a group (one partial per CTA, deterministic).
+int mgw_group_sumsq(const MgwGroup* group, float* partials, int n_ctas, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,61 @@
+// Multi-tensor momentum SGD: one launch updates every parameter of a model (or of one merged
+// group).  Replaces the per-tensor elementwise launches of torch.optim.SGD.step on the 1-GPU
+// path, after gradient accumulation, and after a global-norm clip (the clip coefficient is read
+// from device memory, so no host round trip separates the norm from the update).
+#include "api.h"
+
+__global__ void __launch_bounds__(512)
+mgw_multi_tensor_sgd_kernel(MgwGroup g, const MgwHyper* __restrict__ hyper, const float* __restrict__ clip_coef,
+                            float grad_scale, int first_step, int mode, float* __restrict__ sumsq_partials) {
+    __shared__ float red[32];
+    float scale = grad_scale;
+    if (clip_coef != nullptr) scale *= *clip_coef;
+    const int per = (g.n_vec + gridDim.x - 1) / gridDim.x;
+    const int c0 = blockIdx.x * per;
+    const int c1 = min(g.n_vec, c0 + per);
+    int hint_l = -1, hint_c = -1;
+    float sumsq = 0.f;
+    for (int v = c0 + threadIdx.x; v < c1; v += blockDim.x) {
+        float4 x = mgw_load_grad(g, v, hint_l, scale);
+        mgw_consume(g, v, x, mode, hyper, first_step, hint_c, sumsq);
+    }
+    if (mode & MGW_MODE_SUMSQ) {
+        float r = mgw_block_sum(sumsq, red);
+        if (threadIdx.x == 0) sumsq_partials[blockIdx.x] = r;
+    }
+}
+
+__global__ void mgw_clip_coef_kernel(const float* __restrict__ partials, int n, float max_norm, float* __restrict__ out2) {
+    // single warp, fixed order: lane i sums partials i, i+32, ... then a fixed shuffle tree
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += 32) s += partials[i];
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+    if (threadIdx.x == 0) {
+        const float norm = sqrtf(s);
+        out2[0] = norm;
+        const float c = max_norm / (norm + 1e-6f);
+        out2[1] = c < 1.f ? c : 1.f;
+    }
+}
+
+extern "C" int mgw_multi_tensor_sgd(const MgwGroup* group, const MgwHyper* hyper, const float* clip_coef, float grad_scale,
+                                    int first_step, int mode, float* sumsq_partials, int n_ctas, void* stream) {
+    if (group == nullptr || group->n_vec < 0 || n_ctas <= 0) return MGW_ERR_ARG;
+    if ((mode & MGW_MODE_SUMSQ) && sumsq_partials == nullptr) return MGW_ERR_ARG;
+    if (group->n_vec == 0) return MGW_OK;
+    mgw_multi_tensor_sgd_kernel<<<n_ctas, 512, 0, (cudaStream_t)stream>>>(*group, hyper, clip_coef, grad_scale, first_step,
+                                                                           mode, sumsq_partials);
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}
+
+extern "C" int mgw_group_sumsq(const MgwGroup* group, float* partials, int n_ctas, void* stream) {
+    return mgw_multi_tensor_sgd(group, nullptr, nullptr, 1.f, 0, MGW_MODE_SUMSQ, partials, n_ctas, stream);
+}
+
+extern "C" int mgw_clip_coef(const float* partials, int n, float max_norm, float* out2, void* stream) {
+    if (partials == nullptr || out2 == nullptr || n <= 0) return MGW_ERR_ARG;
+    mgw_clip_coef_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(partials, n, max_norm, out2);
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}

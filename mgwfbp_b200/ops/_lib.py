@@ -1,0 +1,107 @@
+# -*- coding: utf-8 -*-
+"""ctypes binding of ``libmgwfbp_b200.so`` (the package's CUDA kernels and symmetric heap).
+
+The library is built in-tree by :mod:`mgwfbp_b200.ops.build`.  On a machine with a GPU a missing
+library is an error (operations never fall back silently to eager PyTorch); without a GPU the
+loader may build it on demand so that import-time checks still work.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional
+
+from .build import LIB_PATH, build
+
+MAX_RANKS = 16
+MAX_CTAS = 64
+MAX_PARAM_GROUPS = 16
+
+MODE_UPDATE, MODE_WRITEBACK, MODE_SUMSQ = 1, 2, 4
+ALGO_ONESHOT, ALGO_TWOSHOT, ALGO_NVLS = 0, 1, 2
+ALGO_NAMES = {'oneshot': ALGO_ONESHOT, 'twoshot': ALGO_TWOSHOT, 'nvls': ALGO_NVLS}
+
+
+class MgwGroup(C.Structure):
+    _fields_ = [('tensors', C.c_void_p), ('grads', C.c_void_p), ('voff', C.c_void_p),
+                ('n_tensors', C.c_int), ('n_vec', C.c_int)]
+
+
+class MgwAllreduceArgs(C.Structure):
+    _fields_ = [('group', MgwGroup),
+                ('stage', C.c_void_p * MAX_RANKS),
+                ('flags', C.c_void_p * MAX_RANKS),
+                ('epoch', C.c_void_p),
+                ('mc_stage', C.c_void_p),
+                ('hyper', C.c_void_p),
+                ('sumsq_partials', C.c_void_p),
+                ('status', C.c_void_p),
+                ('rank', C.c_int), ('world', C.c_int),
+                ('algo', C.c_int), ('n_ctas', C.c_int), ('n_threads', C.c_int),
+                ('mode', C.c_int), ('first_step', C.c_int),
+                ('inbox_stride', C.c_int), ('reserved', C.c_int),
+                ('timeout_ns', C.c_ulonglong)]
+
+
+_lib: Optional[C.CDLL] = None
+
+
+class NativeLibraryError(RuntimeError):
+    pass
+
+
+def _declare(lib: C.CDLL) -> None:
+    lib.mgw_last_error.restype = C.c_char_p
+    lib.mgw_version.restype = C.c_int
+    lib.mgw_heap_create.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
+    lib.mgw_heap_export.argtypes = [C.c_void_p, C.c_void_p]
+    lib.mgw_heap_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    lib.mgw_heap_close.argtypes = [C.c_void_p]
+    lib.mgw_heap_destroy.argtypes = [C.c_void_p]
+    lib.mgw_host_status_alloc.argtypes = [C.c_int, C.POINTER(C.POINTER(C.c_int))]
+    lib.mgw_host_status_free.argtypes = [C.POINTER(C.c_int)]
+    lib.mgw_allreduce_group.argtypes = [C.POINTER(MgwAllreduceArgs), C.c_void_p]
+    lib.mgw_flag_block_bytes.restype = C.c_size_t
+    lib.mgw_stage_bytes.restype = C.c_size_t
+    lib.mgw_stage_bytes.argtypes = [C.c_int, C.c_int, C.c_int]
+    lib.mgw_multi_tensor_sgd.argtypes = [C.POINTER(MgwGroup), C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int,
+                                         C.c_void_p, C.c_int, C.c_void_p]
+    lib.mgw_clip_coef.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
+    lib.mgw_group_sumsq.argtypes = [C.POINTER(MgwGroup), C.c_void_p, C.c_int, C.c_void_p]
+    for name in ('mgw_bn_relu_fwd', 'mgw_bn_relu_bwd', 'mgw_lstm_cell_fwd', 'mgw_lstm_cell_bwd',
+                 'mgw_wgrad_gemm', 'mgw_wgrad_gemm_supported', 'mgw_allgather_rows'):
+        if hasattr(lib, name):
+            getattr(lib, name).restype = C.c_int
+
+
+def load(allow_build: Optional[bool] = None) -> C.CDLL:
+    """Return the loaded library, building it first when that is allowed and needed."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.isfile(LIB_PATH):
+        if allow_build is None:
+            allow_build = os.environ.get('MGWFBP_BUILD_ON_IMPORT', '1') != '0'
+        if not allow_build:
+            raise NativeLibraryError('%s is missing; run `python -m mgwfbp_b200.ops.build`' % LIB_PATH)
+        try:
+            build()
+        except Exception as e:
+            raise NativeLibraryError('could not build %s: %s' % (LIB_PATH, e)) from e
+    try:
+        lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+    except OSError as e:
+        raise NativeLibraryError('could not load %s: %s' % (LIB_PATH, e)) from e
+    _declare(lib)
+    _lib = lib
+    return lib
+
+
+def check(code: int, what: str = 'native call') -> None:
+    if code != 0:
+        msg = load().mgw_last_error()
+        raise NativeLibraryError('%s failed with code %d: %s' % (what, code, (msg or b'').decode(errors='replace')))
+
+
+def is_loaded() -> bool:
+    return _lib is not None

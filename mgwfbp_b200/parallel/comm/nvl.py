@@ -1,0 +1,449 @@
+# -*- coding: utf-8 -*-
+"""``NvlComm``: the NVLink / NVSwitch data plane with the fused all-reduce + SGD kernels.
+
+Replaces what Horovod's C++ core does for the reference (coordinator thread, name negotiation,
+tensor queue, NCCL launch; see ``distributed_optimizer.py:21-26,339,375``) with:
+
+* a **symmetric heap**: one device allocation per rank, mapped into every peer with CUDA IPC
+  (``csrc/symm_heap.cu``); handles are exchanged once over the gloo control plane;
+* **flag rows** inside the heap for CTA-to-CTA barriers between ranks (bounded waits);
+* one **kernel launch per merged group** on a high-priority side stream
+  (``csrc/allreduce_fused.cu``): pack through a pointer table, reduce over peer memory, average,
+  and -- for plain SGD -- update the weights in the same pass;
+* no negotiation: every rank launches groups in the order their gradients complete, which is the
+  same on every rank because the schedule digest was compared at construction.
+
+Optional NVLS path: when ``MGWFBP_HEAP=torch`` the heap comes from
+``torch.distributed._symmetric_memory`` (allocation and rendezvous only), which also provides an
+NVSwitch multicast address; the ``nvls`` algorithm then reduces with ``multimem.ld_reduce`` /
+``multimem.st``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ... import settings
+from ...ops import _lib, counters
+from ...ops.tables import GroupTable, HyperTable, ensure_momentum_buffers, param_group_index
+from ...settings import logger
+from .. import runtime
+from .base import CommTimeoutError, Communicator
+
+_ALIGN = 256
+
+
+def _env_int(name: str, default: int) -> int:
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+class IpcHeap:
+    """One symmetric region: same size and layout on every rank, all peers mapped locally."""
+
+    def __init__(self, lib, nbytes: int):
+        self.lib = lib
+        self.nbytes = int((nbytes + _ALIGN - 1) // _ALIGN * _ALIGN)
+        self.rank, self.world = runtime.rank(), runtime.size()
+        base = C.c_void_p()
+        _lib.check(lib.mgw_heap_create(self.nbytes, C.byref(base)), 'heap_create')
+        self.base = int(base.value)
+        handle = C.create_string_buffer(64)
+        _lib.check(lib.mgw_heap_export(self.base, handle), 'heap_export')
+        handles = runtime.allgather_object(bytes(handle.raw))
+        self.peer_base: List[int] = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                self.peer_base.append(self.base)
+                continue
+            p = C.c_void_p()
+            _lib.check(lib.mgw_heap_open(C.create_string_buffer(h, 64), C.byref(p)), 'heap_open(rank %d)' % r)
+            self.peer_base.append(int(p.value))
+        self.mc_base = 0
+        self._top = 0
+        runtime.barrier()
+
+    def alloc(self, nbytes: int) -> int:
+        off = self._top
+        self._top = (off + int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
+        if self._top > self.nbytes:
+            raise MemoryError('symmetric heap exhausted')
+        return off
+
+    def close(self) -> None:
+        if self.base:
+            runtime.barrier()
+            for r, p in enumerate(self.peer_base):
+                if r != self.rank:
+                    self.lib.mgw_heap_close(p)
+            self.lib.mgw_heap_destroy(self.base)
+            self.base = 0
+
+
+class TorchSymmHeap:
+    """Same interface on top of ``torch.distributed._symmetric_memory`` (adds a multicast address)."""
+
+    def __init__(self, lib, nbytes: int):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+        self.lib = lib
+        self.nbytes = int((nbytes + _ALIGN - 1) // _ALIGN * _ALIGN)
+        self.rank, self.world = runtime.rank(), runtime.size()
+        dev = torch.device('cuda', torch.cuda.current_device())
+        self._tensor = symm.empty(self.nbytes, dtype=torch.uint8, device=dev)
+        self._handle = symm.rendezvous(self._tensor, dist.group.WORLD.group_name)
+        self._tensor.zero_()
+        torch.cuda.synchronize()
+        self.peer_base = [int(p) for p in self._handle.buffer_ptrs]
+        self.base = self.peer_base[self.rank]
+        self.mc_base = int(getattr(self._handle, 'multicast_ptr', 0) or 0)
+        self._top = 0
+        runtime.barrier()
+
+    alloc = IpcHeap.alloc
+
+    def close(self) -> None:
+        self._tensor = None
+        self._handle = None
+        self.base = 0
+
+
+def make_heap(lib, nbytes: int):
+    kind = os.environ.get('MGWFBP_HEAP', 'ipc').lower()
+    if kind == 'torch':
+        return TorchSymmHeap(lib, nbytes)
+    return IpcHeap(lib, nbytes)
+
+
+class _GroupPlan:
+    __slots__ = ('table', 'params', 'algo', 'n_ctas', 'stage_off', 'args', 'partials_off', 'heap')
+
+
+class NvlComm(Communicator):
+    fused = True
+    _shared: Optional['NvlComm'] = None
+
+    # ------------------------------------------------------------------ construction
+    def __init__(self):
+        if not torch.cuda.is_available():
+            raise RuntimeError('NvlComm needs a CUDA device')
+        self.lib = _lib.load(allow_build=False)
+        self._rank, self._world = runtime.rank(), runtime.size()
+        self.device = torch.device('cuda', torch.cuda.current_device())
+        self.stream = torch.cuda.Stream(device=self.device, priority=-1)
+        self.timeout_ns = int(float(os.environ.get('MGWFBP_COMM_TIMEOUT_S', '10')) * 1e9)
+        self.oneshot_max_bytes = _env_int('MGWFBP_ONESHOT_MAX_BYTES', 512 * 1024)
+        self.max_ctas_oneshot = min(_env_int('MGWFBP_ONESHOT_CTAS', 8), _lib.MAX_CTAS)
+        self.max_ctas_twoshot = min(_env_int('MGWFBP_TWOSHOT_CTAS', 32), _lib.MAX_CTAS)
+        self.n_threads = _env_int('MGWFBP_COMM_THREADS', 512)
+        # control block: flag rows + per-CTA launch counters, in a heap of its own
+        self._flag_bytes = int(self.lib.mgw_flag_block_bytes())
+        self._ctl = make_heap(self.lib, self._flag_bytes + 4 * _lib.MAX_CTAS + _ALIGN)
+        self._flag_off = self._ctl.alloc(self._flag_bytes)
+        self._epoch_off = self._ctl.alloc(4 * _lib.MAX_CTAS)
+        status = C.POINTER(C.c_int)()
+        _lib.check(self.lib.mgw_host_status_alloc(8, C.byref(status)), 'status_alloc')
+        self._status = status
+        self._heaps: List[object] = []
+        self._scratch = None            # (heap, stage_off, capacity_vec) for allreduce_async_
+        self._scratch_tables: Dict[Tuple[int, int], GroupTable] = {}
+        self._done_event = torch.cuda.Event()
+        self._plans: Dict[int, List[_GroupPlan]] = {}
+        self._hyper: Dict[int, HyperTable] = {}
+        self._keepalive: List[object] = []
+        self.nvls_available = bool(self._ctl.mc_base)
+        self.launches = 0
+
+    @classmethod
+    def shared(cls) -> 'NvlComm':
+        if cls._shared is None:
+            cls._shared = cls()
+        return cls._shared
+
+    def size(self) -> int:
+        return self._world
+
+    def rank(self) -> int:
+        return self._rank
+
+    def close(self) -> None:
+        torch.cuda.synchronize()
+        for h in self._heaps + [self._ctl]:
+            h.close()
+        self._heaps = []
+        if self._status:
+            self.lib.mgw_host_status_free(self._status)
+            self._status = None
+        if NvlComm._shared is self:
+            NvlComm._shared = None
+
+    # ------------------------------------------------------------------ status
+    def status(self) -> Tuple[int, int, int, int, int]:
+        s = self._status
+        return (s[0], s[1], s[2], s[3], s[4])
+
+    def check_status(self, synchronize: bool = False) -> None:
+        """Raise :class:`CommTimeoutError` if a kernel gave up waiting for a peer."""
+        if synchronize:
+            torch.cuda.synchronize()
+        code, peer, expected, observed, cta = self.status()
+        if code != 0:
+            raise CommTimeoutError('communication kernel on rank %d gave up (code %d): waited for rank %d, '
+                                   'expected launch %d, saw %d (CTA %d)' % (self._rank, code, peer, expected, observed, cta))
+
+    def clear_status(self) -> None:
+        for i in range(8):
+            self._status[i] = 0
+
+    # ------------------------------------------------------------------ planning
+    def choose(self, n_vec: int) -> Tuple[int, int]:
+        """Algorithm and CTA count for a message of ``n_vec`` float4 slots (same answer on every rank)."""
+        nbytes = n_vec * 16
+        forced = settings.COMM_ALGO.lower()
+        if forced in _lib.ALGO_NAMES and not (forced == 'nvls' and not self.nvls_available):
+            algo = _lib.ALGO_NAMES[forced]
+        elif nbytes <= self.oneshot_max_bytes:
+            algo = _lib.ALGO_ONESHOT
+        else:
+            algo = _lib.ALGO_NVLS if self.nvls_available else _lib.ALGO_TWOSHOT
+        if algo == _lib.ALGO_ONESHOT:
+            n_ctas = max(1, min(self.max_ctas_oneshot, (n_vec + 1023) // 1024))
+        else:
+            n_ctas = max(1, min(self.max_ctas_twoshot, (n_vec + 4095) // 4096))
+        return algo, n_ctas
+
+    def _fill_args(self, plan: _GroupPlan, heap, hyper_ptr: int, partials_ptr: int,
+                   inbox_stride: Optional[int] = None) -> None:
+        a = _lib.MgwAllreduceArgs()
+        a.group = plan.table.struct
+        for r in range(self._world):
+            a.stage[r] = heap.peer_base[r] + plan.stage_off
+            a.flags[r] = self._ctl.peer_base[r] + self._flag_off
+        a.epoch = self._ctl.base + self._epoch_off
+        a.mc_stage = (heap.mc_base + plan.stage_off) if heap.mc_base else None
+        a.hyper = hyper_ptr or None
+        a.sumsq_partials = partials_ptr or None
+        a.status = C.cast(self._status, C.c_void_p).value
+        a.rank, a.world = self._rank, self._world
+        a.algo, a.n_ctas, a.n_threads = plan.algo, plan.n_ctas, self.n_threads
+        a.mode, a.first_step = 0, 0
+        a.inbox_stride = plan.table.n_vec if inbox_stride is None else inbox_stride
+        a.timeout_ns = self.timeout_ns
+        plan.args = a
+
+    def attach(self, opt) -> None:
+        """Lay out staging memory and descriptor tables for every group of ``opt``'s schedule."""
+        key = id(opt)
+        named = opt._named_parameters
+        momenta_created = False
+        plans: List[_GroupPlan] = []
+        total = 0
+        sizes = []
+        for names in opt._groups:
+            params = [named[n] for n in names]
+            n_vec = sum((p.numel() + 3) // 4 for p in params)
+            algo, n_ctas = self.choose(n_vec)
+            nbytes = int(self.lib.mgw_stage_bytes(algo, n_vec, self._world))
+            sizes.append((algo, n_ctas, nbytes))
+            total += (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
+        heap = make_heap(self.lib, total + _ALIGN)
+        self._heaps.append(heap)
+        if heap.mc_base:
+            self.nvls_available = True
+        hyper = HyperTable(self.device)
+        self._hyper[key] = hyper
+        n_partials = sum(s[1] for s in sizes)
+        partials = torch.zeros(max(n_partials, 1), dtype=torch.float32, device=self.device)
+        clip_out = torch.ones(2, dtype=torch.float32, device=self.device)
+        opt._nvl_partials, opt._nvl_clip_out = partials, clip_out
+        p_off = 0
+        for names, (algo, n_ctas, nbytes) in zip(opt._groups, sizes):
+            params = [named[n] for n in names]
+            if opt._base_is_sgd:
+                momenta, created = ensure_momentum_buffers(opt, params)
+                momenta_created = momenta_created or created
+                pgi = param_group_index(opt, params)
+            else:
+                momenta, pgi = [None] * len(params), [0] * len(params)
+            plan = _GroupPlan()
+            plan.params = params
+            plan.table = GroupTable(params, pgi, momenta, self.device)
+            plan.algo, plan.n_ctas = algo, n_ctas
+            plan.stage_off = heap.alloc(nbytes)
+            plan.partials_off = p_off
+            plan.heap = heap
+            self._fill_args(plan, heap, hyper.data_ptr(), partials.data_ptr() + 4 * p_off)
+            p_off += n_ctas
+            plans.append(plan)
+        self._plans[key] = plans
+        opt._nvl_first_step = momenta_created
+        opt._nvl_all = None
+        if opt._base_is_sgd:
+            allp = [p for g in opt.param_groups for p in g['params'] if p.requires_grad]
+            mom, _ = ensure_momentum_buffers(opt, allp)
+            opt._nvl_all = GroupTable(allp, param_group_index(opt, allp), mom, self.device)
+        mode = 0
+        if opt._fused_update:
+            mode |= _lib.MODE_UPDATE
+            if settings.WRITE_BACK_GRADS:
+                mode |= _lib.MODE_WRITEBACK
+        else:
+            mode |= _lib.MODE_WRITEBACK
+            if opt._norm_clip is not None:
+                mode |= _lib.MODE_SUMSQ
+        opt._nvl_mode = mode
+        opt._nvl_held = []
+        algos = {0: 0, 1: 0, 2: 0}
+        for pl in plans:
+            algos[pl.algo] += 1
+        logger.info('NvlComm: %d groups (%d one-shot, %d two-shot, %d nvls), %.1f MB staging, fused update: %s',
+                    len(plans), algos[0], algos[1], algos[2], total / 1e6, opt._fused_update)
+
+    # ------------------------------------------------------------------ hot path
+    def launch_group(self, opt, gi: int) -> None:
+        plan = self._plans[id(opt)][gi]
+        grads = [p.grad for p in plan.params]
+        for g, p in zip(grads, plan.params):
+            if g.stride() != p.stride():
+                raise RuntimeError('gradient layout differs from parameter layout; fused kernels need them equal')
+        compute = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(compute)
+        self.stream.wait_event(ready)
+        plan.table.refresh_grads(grads, self.stream)
+        if not opt._groups_pending and not torch.cuda.is_current_stream_capturing():
+            # first group of this iteration: hyper-parameters may have moved (inside a graph capture the
+            # table is refreshed by the caller before every replay instead)
+            self._hyper[id(opt)].sync(opt.param_groups, self.stream)
+        a = plan.args
+        a.mode = opt._nvl_mode
+        a.first_step = int(opt._nvl_first_step)
+        _lib.check(self.lib.mgw_allreduce_group(C.byref(a), self.stream.cuda_stream), 'allreduce_group')
+        opt._nvl_held.append(grads)
+        self.launches += 1
+        counters.bump('allreduce_fused')
+
+    def wait_groups(self, opt, pending: Sequence[int]) -> None:
+        self._done_event.record(self.stream)
+        torch.cuda.current_stream().wait_event(self._done_event)
+        opt._nvl_held = []
+        if opt._fused_update:
+            opt._nvl_first_step = False
+        self.check_status()
+
+    def finish_step(self, opt, closure=None):
+        loss = closure() if closure is not None else None
+        if opt._fused_update:
+            return loss
+        if opt._base_is_sgd and opt._nvl_all is not None:
+            table: GroupTable = opt._nvl_all
+            grads = [p.grad for p in table.params]
+            if all(g is not None and g.stride() == p.stride() for g, p in zip(grads, table.params)):
+                table.refresh_grads(grads)
+                if not torch.cuda.is_current_stream_capturing():
+                    self._hyper[id(opt)].sync(opt.param_groups)
+                s = torch.cuda.current_stream().cuda_stream
+                clip_ptr = None
+                if opt._norm_clip is not None:
+                    part = opt._nvl_partials
+                    _lib.check(self.lib.mgw_clip_coef(part.data_ptr(), part.numel(), float(opt._norm_clip),
+                                                      opt._nvl_clip_out.data_ptr(), s), 'clip_coef')
+                    clip_ptr = opt._nvl_clip_out.data_ptr() + 4
+                    counters.bump('clip_coef')
+                n_ctas = max(1, min(592, (table.n_vec + 2047) // 2048))
+                _lib.check(self.lib.mgw_multi_tensor_sgd(C.byref(table.struct), self._hyper[id(opt)].data_ptr(), clip_ptr,
+                                                         1.0, int(opt._nvl_first_step), _lib.MODE_UPDATE, None, n_ctas, s),
+                           'multi_tensor_sgd')
+                opt._nvl_first_step = False
+                self.launches += 1
+                counters.bump('multi_tensor_sgd')
+                return loss
+        if opt._norm_clip is not None:
+            torch.nn.utils.clip_grad_norm_([p for p in opt._requires_update], opt._norm_clip)
+        opt._base_cls.step(opt)
+        return loss
+
+    def sync_hyper(self, opt) -> None:
+        """Upload ``opt``'s current learning rates etc. (call before replaying a captured step)."""
+        self._hyper[id(opt)].sync(opt.param_groups, self.stream)
+
+    # ------------------------------------------------------------------ generic tensor all-reduce
+    def _ensure_scratch(self, n_vec: int) -> None:
+        """Scratch staging for :meth:`allreduce_async_`: a one-shot inbox with a fixed row stride and
+        a separate two-shot buffer.  The two regions never overlap: a peer may still be reading its
+        two-shot buffer when the next launch's one-shot stores arrive."""
+        sc = self._scratch
+        if sc is not None and sc['ts_cap'] >= n_vec:
+            return
+        ts_cap = max(n_vec, 1 << 16)
+        os_cap = self.oneshot_max_bytes // 16 + 1
+        os_bytes = int(self.lib.mgw_stage_bytes(_lib.ALGO_ONESHOT, os_cap, self._world))
+        ts_bytes = int(self.lib.mgw_stage_bytes(_lib.ALGO_TWOSHOT, ts_cap, self._world))
+        heap = make_heap(self.lib, os_bytes + ts_bytes + 2 * _ALIGN)
+        self._heaps.append(heap)
+        if heap.mc_base:
+            self.nvls_available = True
+        self._scratch = dict(heap=heap, os_off=heap.alloc(os_bytes), os_cap=os_cap, ts_off=heap.alloc(ts_bytes), ts_cap=ts_cap)
+
+    def allreduce_async_(self, tensor: torch.Tensor, average: bool = True, name: Optional[str] = None,
+                         algo: Optional[str] = None, n_ctas: Optional[int] = None):
+        """In-place all-reduce of an arbitrary dense float32 CUDA tensor (collective: every rank
+        must call it with the same shape).  Horovod-shaped; used by the communication profiler."""
+        if tensor.dtype != torch.float32 or not tensor.is_cuda:
+            raise ValueError('NvlComm.allreduce_async_ needs a float32 CUDA tensor')
+        flat = tensor.view(-1)
+        n_vec = (flat.numel() + 3) // 4
+        self._ensure_scratch(n_vec)
+        sc = self._scratch
+        key = (flat.data_ptr(), flat.numel())
+        table = self._scratch_tables.get(key)
+        if table is None:
+            if len(self._scratch_tables) > 256:
+                self._scratch_tables.clear()
+            table = GroupTable([flat], [0], [None], self.device)
+            self._scratch_tables[key] = table
+        plan = _GroupPlan()
+        plan.table, plan.params, plan.heap = table, [flat], sc['heap']
+        plan.algo, plan.n_ctas = self.choose(n_vec)
+        if algo is not None:
+            plan.algo = _lib.ALGO_NAMES[algo]
+            plan.n_ctas = self.choose(n_vec)[1]
+        if plan.algo == _lib.ALGO_ONESHOT and n_vec > sc['os_cap']:
+            raise ValueError('message of %d bytes is too large for the one-shot inbox' % (n_vec * 16))
+        if n_ctas is not None:
+            plan.n_ctas = n_ctas
+        plan.stage_off = sc['os_off'] if plan.algo == _lib.ALGO_ONESHOT else sc['ts_off']
+        self._fill_args(plan, sc['heap'], 0, 0, inbox_stride=sc['os_cap'])
+        compute = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(compute)
+        self.stream.wait_event(ready)
+        table.refresh_grads([flat], self.stream)
+        plan.args.mode = _lib.MODE_WRITEBACK
+        _lib.check(self.lib.mgw_allreduce_group(C.byref(plan.args), self.stream.cuda_stream), 'allreduce_group')
+        self.launches += 1
+        counters.bump('allreduce_fused')
+        done = torch.cuda.Event()
+        done.record(self.stream)
+        return (done, tensor, None if average else float(self._world))
+
+    def synchronize(self, handle):
+        first, tensor, extra = handle
+        if isinstance(first, torch.cuda.Event):
+            torch.cuda.current_stream().wait_event(first)
+            if extra is not None:
+                tensor.mul_(extra)
+        elif first is not None:
+            first.wait()
+        return tensor
+
+    def broadcast_async_(self, tensor, root_rank, name=None):
+        import torch.distributed as dist
+        work = dist.broadcast(tensor, src=root_rank, group=runtime.data_group(), async_op=True)
+        return (work, tensor, None)

@@ -115,7 +115,10 @@ class _DistributedMixin:
         self._hook_checked_idx = 0
         self._groups_pending: List[int] = []
         self._synchronized = True
-        if self._world > 1:
+        # An explicitly supplied fused communicator is also used on a single GPU (the update then
+        # overlaps with backward); otherwise one worker behaves like the plain optimizer.
+        self._active = self._world > 1 or (self._fused_comm and comm is not None)
+        if self._active:
             self._verify_schedule_agreement()
             self._register_hooks()
             if self._fused_comm:
@@ -296,7 +299,7 @@ class _DistributedMixin:
         data plane is used with ``settings.WRITE_BACK_GRADS`` off and the update fused, the
         gradients have already been consumed and ``p.grad`` keeps the local values).
         """
-        if self._world == 1 or self._synchronized:
+        if not self._active or self._synchronized:
             return
         if self._fused_comm:
             self._comm.wait_groups(self, self._groups_pending)
@@ -307,13 +310,6 @@ class _DistributedMixin:
                 out = self._comm.synchronize(handle)
                 if self._profiling:
                     self._allreduce_timers.setdefault(self._group_keys[gi], []).append(time.time() - t0)
-                if self._norm_clip is not None:
-                    # per-buffer clip with the reference's sqrt(1/P) scaling (:380-387)
-                    limit = math.sqrt(1.0 / self._world) * self._norm_clip
-                    total = float(out.norm(2.0))
-                    coef = limit / (total + 1e-6)
-                    if coef < 1:
-                        out.mul_(coef)
                 if not self._one_tensor_per_group:
                     key = self._group_keys[gi]
                     for name, off in zip(self._groups[gi], self._merged_parameter_offsets[key]):
@@ -326,11 +322,24 @@ class _DistributedMixin:
         self.train_iter += 1
 
     def step(self, closure=None):
-        if self._world > 1 and not self.local:
+        if self._active and not self.local:
             self.synchronize()
             if self._fused_comm:
                 return self._comm.finish_step(self, closure)
+        if self._norm_clip is not None and not self.local and getattr(self, '_fast_sgd', None) is None:
+            # global L2-norm clip of the averaged gradient (the reference's loop calls
+            # clip_grad_norm_ between synchronize() and step(), dist_trainer.py:89-94)
+            params = [p for g in self.param_groups for p in g['params'] if p.grad is not None]
+            torch.nn.utils.clip_grad_norm_(params, self._norm_clip)
         return self._local_step(closure)
+
+    def sync_hyper(self) -> None:
+        """Push the current ``param_groups`` hyper-parameters to the device tables of the fused
+        kernels.  Needed only by callers that replay a captured CUDA graph of the training step."""
+        if self._active and self._fused_comm:
+            self._comm.sync_hyper(self)
+        elif getattr(self, '_fast_sgd', None) is not None:
+            self._fast_sgd.sync_hyper(self)
 
     def _local_step(self, closure=None):
         fast = getattr(self, '_fast_sgd', None)
@@ -346,7 +355,7 @@ class _DistributedMixin:
         plane gradients are dropped (autograd hands over fresh tensors, whose addresses the
         kernels pick up from a pointer table).
         """
-        if self._world > 1 and not self._fused_comm and not set_to_none:
+        if self._active and not self._fused_comm and not set_to_none:
             if self._merged_parameters:
                 for buf in self._merged_parameters.values():
                     buf.zero_()
@@ -419,7 +428,7 @@ def DistributedOptimizer(optimizer, named_parameters=None, compression=None, den
     obj.state.update(optimizer.state)
     obj._dist_init(optimizer, named_parameters, compression, seq_layernames, layerwise_times, norm_clip,
                    threshold, writer, gradient_path, comm, cost_model, fused_update)
-    if obj._world == 1 and obj._base_is_sgd:
+    if not obj._active and obj._base_is_sgd:
         first = next(iter(obj._named_parameters.values()), None)
         if first is not None and first.is_cuda:
             from ..ops.sgd import FastSGD

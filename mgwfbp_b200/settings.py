@@ -54,6 +54,11 @@ FAKE_DATA = _env_flag('FAKE_DATA', False)
 # for optimizers other than plain SGD and whenever ``norm_clip`` is requested.
 FUSED_UPDATE = _env_flag('FUSED_UPDATE', True)
 
+# Swap BatchNorm+ReLU pairs and LSTMs for this package's fused CUDA modules when a model is built on a GPU.
+FUSE_MODULES = _env_flag('FUSE', True)
+# Keep convolutional models and their inputs in channels-last (NHWC) memory format on the GPU.
+CHANNELS_LAST = _env_flag('CHANNELS_LAST', True)
+
 # After the fused kernels ran, leave the averaged gradient readable in ``p.grad``.
 WRITE_BACK_GRADS = _env_flag('WRITE_BACK_GRADS', True)
 

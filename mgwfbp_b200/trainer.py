@@ -56,8 +56,8 @@ class DLTrainer:
         self.data_dir = data_dir
         self.is_cuda = ngpus > 0 and torch.cuda.is_available()
         self.device = torch.device('cuda', torch.cuda.current_device()) if self.is_cuda else torch.device('cpu')
-        self.fuse = self.is_cuda if fuse is None else bool(fuse)
-        self.channels_last = self.is_cuda if channels_last is None else bool(channels_last)
+        self.fuse = (self.is_cuda and settings.FUSE_MODULES) if fuse is None else bool(fuse)
+        self.channels_last = (self.is_cuda and settings.CHANNELS_LAST) if channels_last is None else bool(channels_last)
         if seed is not None:
             torch.manual_seed(seed)
         self.train_sampler = None

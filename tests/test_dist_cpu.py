@@ -17,13 +17,14 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, fn, args, out_dir):
+def _worker(rank, world, port, fn, args, out_dir, use_cuda=False):
     os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR='127.0.0.1',
                       MASTER_PORT=str(port), MGWFBP_CONNECTION='10GbE')
     sys.path.insert(0, ROOT)
     torch.set_num_threads(1)
+    os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
     import mgwfbp_b200 as hvd
-    hvd.init(timeout_s=120)
+    hvd.init(timeout_s=120, device='cuda' if use_cuda else 'cpu')
     try:
         result = fn(rank, world, *args)
         torch.save(result, os.path.join(out_dir, 'rank%d.pt' % rank))
@@ -31,9 +32,11 @@ def _worker(rank, world, port, fn, args, out_dir):
         hvd.shutdown()
 
 
-def run_ranks(fn, args=(), world=2):
+def run_ranks(fn, args=(), world=2, use_cuda=None):
+    if use_cuda is None:
+        use_cuda = fn.__module__ != __name__ and torch.cuda.is_available()
     with tempfile.TemporaryDirectory() as d:
-        mp.spawn(_worker, args=(world, _free_port(), fn, args, d), nprocs=world, join=True)
+        mp.spawn(_worker, args=(world, _free_port(), fn, args, d, use_cuda), nprocs=world, join=True)
         return [torch.load(os.path.join(d, 'rank%d.pt' % r), weights_only=False) for r in range(world)]
 
 

@@ -1,0 +1,157 @@
+"""Single-GPU numerics of the native kernels against plain PyTorch fp32 references."""
+import ctypes as C
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope='module')
+def lib():
+    from mgwfbp_b200.ops import _lib
+    return _lib.load(allow_build=False)
+
+
+def _ref_sgd(params, grads, bufs, lr, wd, momentum, dampening, nesterov, first):
+    for p, g, b in zip(params, grads, bufs):
+        g = g.clone()
+        if wd != 0:
+            g = g + wd * p
+        if momentum != 0:
+            if first:
+                b.copy_(g)
+            else:
+                b.mul_(momentum).add_(g, alpha=1 - dampening)
+            g = g + momentum * b if nesterov else b
+        p.add_(g, alpha=-lr)
+
+
+@pytest.mark.parametrize('sizes', [[1], [3, 5, 1000], [4, 64, 1000, 2359296, 7, 513], [1 << 20]])
+@pytest.mark.parametrize('momentum,nesterov,wd', [(0.9, False, 1e-4), (0.0, False, 0.0), (0.9, True, 5e-4)])
+def test_fast_sgd_matches_torch(sizes, momentum, nesterov, wd):
+    import mgwfbp_b200 as hvd
+    torch.manual_seed(0)
+    dev = torch.device('cuda')
+    params = [torch.nn.Parameter(torch.randn(n, device=dev)) for n in sizes]
+    ref_params = [torch.nn.Parameter(p.detach().clone()) for p in params]
+    half = max(len(params) // 2, 1)
+    mk = lambda ps: torch.optim.SGD([{'params': ps[:half], 'weight_decay': 0.0}, {'params': ps[half:], 'weight_decay': wd}]
+                                    if len(ps) > 1 else [{'params': ps, 'weight_decay': wd}],
+                                    lr=0.1, momentum=momentum, nesterov=nesterov)
+    opt = hvd.DistributedOptimizer(mk(params), named_parameters=[('p%d' % i, p) for i, p in enumerate(params)])
+    assert getattr(opt, '_fast_sgd', None) is not None, 'native SGD path is not active'
+    ref = mk(ref_params)
+    for step in range(4):
+        for p, r in zip(params, ref_params):
+            g = torch.randn_like(p)
+            p.grad, r.grad = g.clone(), g.clone()
+        for group, rgroup in zip(opt.param_groups, ref.param_groups):
+            group['lr'] = rgroup['lr'] = 0.1 / (step + 1)
+        opt.step()
+        ref.step()
+    for p, r in zip(params, ref_params):
+        torch.testing.assert_close(p, r, rtol=1e-5, atol=1e-6)
+    if momentum:
+        for p, r in zip(params, ref_params):
+            torch.testing.assert_close(opt.state[p]['momentum_buffer'], ref.state[r]['momentum_buffer'], rtol=1e-5, atol=1e-6)
+
+
+def test_fast_sgd_global_norm_clip():
+    import mgwfbp_b200 as hvd
+    torch.manual_seed(1)
+    dev = torch.device('cuda')
+    sizes = [1000, 33, 70000]
+    params = [torch.nn.Parameter(torch.randn(n, device=dev)) for n in sizes]
+    ref_params = [torch.nn.Parameter(p.detach().clone()) for p in params]
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(params, lr=0.5), named_parameters=[('p%d' % i, p) for i, p in enumerate(params)],
+                                   norm_clip=0.25)
+    ref = torch.optim.SGD(ref_params, lr=0.5)
+    for _ in range(2):
+        for p, r in zip(params, ref_params):
+            g = torch.randn_like(p)
+            p.grad, r.grad = g.clone(), g.clone()
+        opt.step()
+        total = torch.nn.utils.clip_grad_norm_(ref_params, 0.25)
+        ref.step()
+        torch.testing.assert_close(opt._fast_sgd.grad_norm(), total, rtol=1e-4, atol=1e-5)
+    for p, r in zip(params, ref_params):
+        torch.testing.assert_close(p, r, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize('algo', ['oneshot', 'twoshot'])
+@pytest.mark.parametrize('numel', [1, 5, 4096, 100003])
+def test_allreduce_kernel_single_rank_is_identity(algo, numel):
+    """World size 1: the kernel still packs, stages, passes its (self) barriers and writes back."""
+    from mgwfbp_b200.parallel.comm.nvl import NvlComm
+    comm = NvlComm.shared()
+    x = torch.randn(numel, device='cuda')
+    want = x.clone()
+    h = comm.allreduce_async_(x, average=True, algo=algo)
+    comm.synchronize(h)
+    torch.cuda.synchronize()
+    comm.check_status()
+    assert torch.equal(x, want)
+
+
+def test_fused_update_in_hooks_single_rank():
+    """The complete fused path (hooks -> side stream kernel -> in-kernel SGD) on one GPU must equal
+    torch.optim.SGD on the same gradients."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200.parallel.comm.nvl import NvlComm
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(37, 64), torch.nn.ReLU(), torch.nn.Linear(64, 10)).cuda()
+    ref = torch.nn.Sequential(torch.nn.Linear(37, 64), torch.nn.ReLU(), torch.nn.Linear(64, 10)).cuda()
+    ref.load_state_dict(net.state_dict())
+    mk = lambda m: torch.optim.SGD(m.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-3)
+    opt = hvd.DistributedOptimizer(mk(net), named_parameters=net.named_parameters(), threshold=3000, comm=NvlComm.shared())
+    assert opt._fused_update
+    ropt = mk(ref)
+    for _ in range(5):
+        x = torch.randn(16, 37, device='cuda')
+        opt.zero_grad()
+        net(x).pow(2).mean().backward()
+        opt.step()
+        ropt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        ropt.step()
+    torch.cuda.synchronize()
+    for a, b in zip(net.parameters(), ref.parameters()):
+        torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    # the averaged gradient stays readable in p.grad
+    for a, b in zip(net.parameters(), ref.parameters()):
+        torch.testing.assert_close(a.grad, b.grad, rtol=1e-5, atol=1e-7)
+
+
+def test_bounded_wait_reports_timeout_without_hanging(lib):
+    """A flag that nobody sets: the kernel must give up after its limit and report through the
+    status block, leaving the context usable."""
+    from mgwfbp_b200.ops import _lib
+    from mgwfbp_b200.ops.tables import GroupTable
+    dev = torch.device('cuda')
+    x = torch.ones(1024, device=dev)
+    table = GroupTable([x], [0], [None], dev)
+    table.refresh_grads([x])
+    stage = torch.zeros(4 * 1024 * 4, device=dev)
+    flags = torch.zeros(lib.mgw_flag_block_bytes() // 4, dtype=torch.int32, device=dev)
+    epoch = torch.zeros(64, dtype=torch.int32, device=dev)
+    status = C.POINTER(C.c_int)()
+    _lib.check(lib.mgw_host_status_alloc(8, C.byref(status)))
+    a = _lib.MgwAllreduceArgs()
+    a.group = table.struct
+    # pretend to be rank 0 of 2; "rank 1" points at the same memory but never signals
+    for r in range(2):
+        a.stage[r] = stage.data_ptr()
+        a.flags[r] = flags.data_ptr()
+    a.epoch = epoch.data_ptr()
+    a.status = C.cast(status, C.c_void_p).value
+    a.rank, a.world, a.algo, a.n_ctas, a.n_threads = 0, 2, _lib.ALGO_TWOSHOT, 1, 128
+    a.mode, a.first_step, a.inbox_stride = _lib.MODE_WRITEBACK, 0, table.n_vec
+    a.timeout_ns = 50_000_000        # 50 ms
+    _lib.check(lib.mgw_allreduce_group(C.byref(a), torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert status[0] == 1 and status[1] == 1, 'timeout on peer 1 expected, got %s' % [status[i] for i in range(5)]
+    assert int(epoch[0]) == 1
+    y = torch.ones(8, device=dev) * 2          # the context still works
+    assert float(y.sum()) == 16.0
+    _lib.check(lib.mgw_host_status_free(status))

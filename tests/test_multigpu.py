@@ -1,0 +1,149 @@
+"""Multi-GPU tests of the NVLink data plane (one process per GPU, 2..4 GPUs of one box)."""
+import os
+import sys
+
+import pytest
+import torch
+
+from test_dist_cpu import run_ranks
+
+pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
+
+
+def _world():
+    return min(torch.cuda.device_count(), 4)
+
+
+def _allreduce_sweep(rank, world):
+    from mgwfbp_b200.parallel.comm.nvl import NvlComm
+    comm = NvlComm.shared()
+    out = {}
+    for algo in ('oneshot', 'twoshot'):
+        for numel in (1, 7, 1024, 32771, 1 << 17, (1 << 22) + 3):
+            if algo == 'oneshot' and numel * 4 > comm.oneshot_max_bytes:
+                continue
+            g = torch.Generator(device='cuda').manual_seed(1000 * rank + numel % 997)
+            x = torch.randn(numel, device='cuda', generator=g)
+            mine = x.clone()
+            comm.synchronize(comm.allreduce_async_(x, average=True, algo=algo))
+            again = mine.clone()
+            comm.synchronize(comm.allreduce_async_(again, average=True, algo=algo))
+            torch.cuda.synchronize()
+            comm.check_status()
+            out[(algo, numel)] = (mine.cpu(), x.cpu(), bool(torch.equal(x, again)))
+    return out
+
+
+def test_allreduce_matches_cpu_sum_and_is_deterministic():
+    world = _world()
+    res = run_ranks(_allreduce_sweep, (), world=world)
+    for key in res[0]:
+        want = sum(r[key][0].double() for r in res) / world
+        for r in res:
+            torch.testing.assert_close(r[key][1].double(), want, rtol=1e-6, atol=1e-6, msg=lambda m: '%s: %s' % (key, m))
+            assert torch.equal(r[key][1], res[0][key][1]), 'ranks differ bitwise for %s' % (key,)
+            assert r[key][2], 'repeat differs for %s' % (key,)
+
+
+def _fused_training(rank, world, policy, fused):
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
+    settings.ADAPTIVE_MERGE = False
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.ReLU(), torch.nn.Linear(256, 256), torch.nn.ReLU(),
+                              torch.nn.Linear(256, 10)).cuda()
+    ref = torch.nn.Sequential(torch.nn.Linear(64, 256), torch.nn.ReLU(), torch.nn.Linear(256, 256), torch.nn.ReLU(),
+                              torch.nn.Linear(256, 10)).cuda()
+    hvd.broadcast_parameters(net.state_dict(), 0)
+    ref.load_state_dict(net.state_dict())
+    mk = lambda m: torch.optim.SGD(m.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+    threshold = {'wfbp': 0, 'single': 524288000, 'bucket': 20000}[policy]
+    opt = hvd.DistributedOptimizer(mk(net), named_parameters=net.named_parameters(), threshold=threshold, fused_update=fused)
+    assert opt._fused_comm and opt._fused_update == fused
+    ropt = mk(ref)
+    crit = torch.nn.CrossEntropyLoss()
+    g = torch.Generator().manual_seed(5)
+    for _ in range(6):
+        x = torch.randn(world * 16, 64, generator=g).cuda()
+        y = torch.randint(0, 10, (world * 16,), generator=g).cuda()
+        opt.zero_grad()
+        crit(net(x[rank * 16:(rank + 1) * 16]), y[rank * 16:(rank + 1) * 16]).backward()
+        opt.step()
+        ropt.zero_grad()
+        crit(ref(x), y).backward()
+        ropt.step()
+    torch.cuda.synchronize()
+    opt.communicator.check_status()
+    return {'dp': [p.detach().cpu() for p in net.parameters()], 'ref': [p.detach().cpu() for p in ref.parameters()]}
+
+
+@pytest.mark.parametrize('policy,fused', [('wfbp', True), ('single', True), ('bucket', True), ('bucket', False)])
+def test_fused_data_parallel_equals_large_batch(policy, fused):
+    res = run_ranks(_fused_training, (policy, fused), world=_world())
+    for dp, ref in zip(res[0]['dp'], res[0]['ref']):
+        torch.testing.assert_close(dp, ref, rtol=2e-4, atol=2e-5)
+    for r in res[1:]:
+        for a, b in zip(res[0]['dp'], r['dp']):
+            assert torch.equal(a, b), 'replicas diverged'
+
+
+def _clip_path(rank, world):
+    import mgwfbp_b200 as hvd
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.Tanh(), torch.nn.Linear(64, 8)).cuda()
+    ref = torch.nn.Sequential(torch.nn.Linear(32, 64), torch.nn.Tanh(), torch.nn.Linear(64, 8)).cuda()
+    hvd.broadcast_parameters(net.state_dict(), 0)
+    ref.load_state_dict(net.state_dict())
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(net.parameters(), lr=1.0), named_parameters=net.named_parameters(),
+                                   threshold=1000, norm_clip=0.05)
+    ropt = torch.optim.SGD(ref.parameters(), lr=1.0)
+    g = torch.Generator().manual_seed(3)
+    for _ in range(3):
+        x = torch.randn(world * 8, 32, generator=g).cuda()
+        opt.zero_grad()
+        net(x[rank * 8:(rank + 1) * 8]).pow(2).mean().backward()
+        opt.step()
+        ropt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.05)
+        ropt.step()
+    torch.cuda.synchronize()
+    return {'dp': [p.detach().cpu() for p in net.parameters()], 'ref': [p.detach().cpu() for p in ref.parameters()]}
+
+
+def test_global_norm_clip_without_host_sync():
+    res = run_ranks(_clip_path, (), world=_world())
+    for dp, ref in zip(res[0]['dp'], res[0]['ref']):
+        torch.testing.assert_close(dp, ref, rtol=2e-4, atol=2e-5)
+    for a, b in zip(res[0]['dp'], res[1]['dp']):
+        assert torch.equal(a, b)
+
+
+def _missing_peer(rank, world):
+    """Rank 1 never launches its group: rank 0's kernel must time out and report, not hang.
+    The failure is injected on the host (a skipped launch); no GPU is faulted."""
+    os.environ['MGWFBP_COMM_TIMEOUT_S'] = '0.2'
+    from mgwfbp_b200.parallel.comm.base import CommTimeoutError
+    from mgwfbp_b200.parallel.comm.nvl import NvlComm
+    import mgwfbp_b200 as hvd
+    comm = NvlComm.shared()
+    x = torch.ones(4096, device='cuda')
+    comm.synchronize(comm.allreduce_async_(x.clone()))          # a healthy round first
+    torch.cuda.synchronize()
+    err = None
+    if rank == 0:
+        comm.synchronize(comm.allreduce_async_(x))
+        torch.cuda.synchronize()
+        try:
+            comm.check_status()
+        except CommTimeoutError as e:
+            err = str(e)
+    hvd.barrier()
+    alive = float((torch.ones(4, device='cuda') * 3).sum())
+    return {'err': err, 'alive': alive}
+
+
+def test_missing_peer_is_reported_not_hung():
+    res = run_ranks(_missing_peer, (), world=2)
+    assert res[0]['err'] and 'gave up' in res[0]['err']
+    assert res[0]['alive'] == 12.0 and res[1]['alive'] == 12.0

@@ -1,0 +1,388 @@
+// Fused training-mode BatchNorm (+ residual add) (+ ReLU), forward and backward, for activations
+// stored as a dense [M, C] matrix with channels innermost: channels-last 4-D tensors
+// (M = N*H*W) and 2-D inputs of BatchNorm1d (M = batch).
+//
+// Forward = two streaming passes instead of cuDNN BatchNorm + add + ReLU (two extra passes over the
+// activation):
+//   bn_stats_kernel        : per-channel sum / sum of squares, one deterministic partial per row split
+//   bn_fwd_finalize_kernel : (tiny) combines the partials in double, saves mean / inv-std, updates the
+//                            running statistics and num_batches_tracked
+//   bn_apply_kernel        : y = relu(x * scale + shift (+ residual))
+// Backward:
+//   bn_bwd_reduce_kernel   : dz = dy * (y > 0); partial sums of dz and dz * xhat; writes dz
+//   bn_bwd_finalize_kernel : (tiny) dgamma, dbeta
+//   bn_bwd_apply_kernel    : dx = scale * (dz - (dbeta + xhat * dgamma) / M)
+// dz doubles as the gradient of the residual input.
+//
+// Thread layout: a block is TX lanes along channels (each lane owns VEC consecutive channels, one
+// 16-byte access when VEC = 4) by TY rows; grid.x tiles the channels, grid.y splits the rows.
+// All of it is bandwidth-bound; the second pass of each direction re-reads tensors that the first
+// pass just streamed, which the 126 MB L2 serves for the smaller layers.
+#include "api.h"
+
+namespace {
+
+constexpr int kThreads = 512;
+
+template <int VEC> struct Vec;
+template <> struct Vec<4> { using T = float4; };
+template <> struct Vec<1> { using T = float; };
+
+template <int VEC>
+__device__ __forceinline__ void load_vec(const float* p, float (&v)[VEC]) {
+    if (VEC == 4) {
+        const float4 t = *reinterpret_cast<const float4*>(p);
+        v[0] = t.x; v[1 % VEC] = t.y; v[2 % VEC] = t.z; v[3 % VEC] = t.w;
+    } else {
+        v[0] = *p;
+    }
+}
+
+template <int VEC>
+__device__ __forceinline__ void store_vec(float* p, const float (&v)[VEC]) {
+    if (VEC == 4) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1 % VEC], v[2 % VEC], v[3 % VEC]);
+    } else {
+        *p = v[0];
+    }
+}
+
+struct Tiling {
+    int tx, ty, grid_x, grid_y, rows_per_split;
+};
+
+Tiling make_tiling(long long M, int C, int vec) {
+    Tiling t;
+    const int lanes = (C + vec - 1) / vec;
+    int tx = 1;
+    while (tx < lanes && tx < 32) tx <<= 1;
+    t.tx = tx;
+    t.ty = kThreads / tx;
+    t.grid_x = (lanes + tx - 1) / tx;
+    const int target_blocks = 148 * 4;
+    long long max_splits = (M + t.ty - 1) / t.ty;
+    long long gy = (target_blocks + t.grid_x - 1) / t.grid_x;
+    if (gy > max_splits) gy = max_splits;
+    if (gy > 1024) gy = 1024;
+    if (gy < 1) gy = 1;
+    t.grid_y = (int)gy;
+    long long rps = (M + gy - 1) / gy;
+    rps = (rps + t.ty - 1) / t.ty * t.ty;
+    t.rows_per_split = (int)rps;
+    t.grid_y = (int)((M + rps - 1) / rps);
+    return t;
+}
+
+// Sum `a` and `b` over the TY rows of the block in a fixed order; valid in threads with ty == 0.
+template <int VEC>
+__device__ __forceinline__ void block_reduce_rows(float (&a)[VEC], float (&b)[VEC], float* smem, int tx, int ty, int TX, int TY) {
+    float* sa = smem;
+    float* sb = smem + kThreads * VEC;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        sa[(ty * TX + tx) * VEC + k] = a[k];
+        sb[(ty * TX + tx) * VEC + k] = b[k];
+    }
+    __syncthreads();
+    if (ty == 0) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            float ra = 0.f, rb = 0.f;
+            for (int r = 0; r < TY; ++r) {
+                ra += sa[(r * TX + tx) * VEC + k];
+                rb += sb[(r * TX + tx) * VEC + k];
+            }
+            a[k] = ra;
+            b[k] = rb;
+        }
+    }
+    __syncthreads();
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int rows_per_split, float* __restrict__ partials) {
+    extern __shared__ float smem[];
+    const int TY = kThreads / TX;
+    const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
+    const int c0 = (blockIdx.x * TX + tx) * VEC;
+    const bool active = c0 < C;
+    float s[VEC], q[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) s[k] = q[k] = 0.f;
+    const long long r0 = (long long)blockIdx.y * rows_per_split;
+    const long long r1 = min(M, r0 + rows_per_split);
+    if (active) {
+        for (long long r = r0 + ty; r < r1; r += TY) {
+            float v[VEC];
+            load_vec<VEC>(x + r * C + c0, v);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                s[k] += v[k];
+                q[k] = fmaf(v[k], v[k], q[k]);
+            }
+        }
+    }
+    block_reduce_rows<VEC>(s, q, smem, tx, ty, TX, TY);
+    if (ty == 0 && active) {
+        float* ps = partials + (size_t)blockIdx.y * 2 * C;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            if (c0 + k < C) {
+                ps[c0 + k] = s[k];
+                ps[C + c0 + k] = q[k];
+            }
+        }
+    }
+}
+
+// Sum the per-split partials of 32 channels per block (16-way split over the partial rows, combined
+// in double in a fixed order).  out_a / out_b receive the two totals of every channel.
+__device__ __forceinline__ void finalize_sums(const float* __restrict__ partials, int n_splits, int C, double& a, double& b,
+                                              double (*sm)[16][32]) {
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    double ra = 0.0, rb = 0.0;
+    if (c < C) {
+        for (int s = threadIdx.y; s < n_splits; s += 16) {
+            const float* ps = partials + (size_t)s * 2 * C;
+            ra += (double)ps[c];
+            rb += (double)ps[C + c];
+        }
+    }
+    sm[0][threadIdx.y][threadIdx.x] = ra;
+    sm[1][threadIdx.y][threadIdx.x] = rb;
+    __syncthreads();
+    a = b = 0.0;
+    if (threadIdx.y == 0) {
+        for (int r = 0; r < 16; ++r) {
+            a += sm[0][r][threadIdx.x];
+            b += sm[1][r][threadIdx.x];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(512)
+bn_fwd_finalize_kernel(const float* __restrict__ partials, int n_splits, long long M, int C, float* running_mean, float* running_var,
+                       long long* num_batches_tracked, float momentum, float eps, float* __restrict__ save_mean,
+                       float* __restrict__ save_invstd) {
+    __shared__ double sm[2][16][32];
+    double sum, sq;
+    finalize_sums(partials, n_splits, C, sum, sq, sm);
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    if (threadIdx.y == 0 && c < C) {
+        const double mean = sum / (double)M;
+        double var = sq / (double)M - mean * mean;
+        if (var < 0.0) var = 0.0;
+        save_mean[c] = (float)mean;
+        save_invstd[c] = (float)(1.0 / sqrt(var + (double)eps));
+        if (running_mean) {
+            const double unbiased = M > 1 ? var * (double)M / (double)(M - 1) : var;
+            running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * (float)mean;
+            running_var[c] = (1.f - momentum) * running_var[c] + momentum * (float)unbiased;
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0 && threadIdx.y == 0 && num_batches_tracked) *num_batches_tracked += 1;
+}
+
+__global__ void __launch_bounds__(512)
+bn_bwd_finalize_kernel(const float* __restrict__ partials, int n_splits, int C, float* __restrict__ dgamma, float* __restrict__ dbeta) {
+    __shared__ double sm[2][16][32];
+    double a, b;
+    finalize_sums(partials, n_splits, C, a, b, sm);
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    if (threadIdx.y == 0 && c < C) {
+        dbeta[c] = (float)a;
+        dgamma[c] = (float)b;
+    }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ residual, float* __restrict__ y, long long M, int C,
+                int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta, int relu,
+                const float* __restrict__ save_mean, const float* __restrict__ save_invstd) {
+    const int TY = kThreads / TX;
+    const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
+    const int c0 = (blockIdx.x * TX + tx) * VEC;
+    if (c0 >= C) return;
+    float sc[VEC], sh[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        const bool in = c0 + k < C;
+        const float g = (in && gamma) ? gamma[c0 + k] : 1.f;
+        const float b = (in && beta) ? beta[c0 + k] : 0.f;
+        sc[k] = in ? g * save_invstd[c0 + k] : 0.f;
+        sh[k] = in ? b - save_mean[c0 + k] * sc[k] : 0.f;
+    }
+    const long long r0 = (long long)blockIdx.y * rows_per_split;
+    const long long r1 = min(M, r0 + rows_per_split);
+    for (long long r = r0 + ty; r < r1; r += TY) {
+        float v[VEC], o[VEC];
+        load_vec<VEC>(x + r * C + c0, v);
+        if (residual) {
+            float rr[VEC];
+            load_vec<VEC>(residual + r * C + c0, rr);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) o[k] = fmaf(v[k], sc[k], sh[k]) + rr[k];
+        } else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) o[k] = fmaf(v[k], sc[k], sh[k]);
+        }
+        if (relu) {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) o[k] = fmaxf(o[k], 0.f);
+        }
+        store_vec<VEC>(y + r * C + c0, o);
+    }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, const float* __restrict__ x, float* __restrict__ dz,
+                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ save_mean,
+                     const float* __restrict__ save_invstd, int relu, float* __restrict__ partials) {
+    extern __shared__ float smem[];
+    const int TY = kThreads / TX;
+    const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
+    const int c0 = (blockIdx.x * TX + tx) * VEC;
+    const bool active = c0 < C;
+    float s[VEC], q[VEC], mean[VEC], istd[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        s[k] = q[k] = 0.f;
+        mean[k] = (active && c0 + k < C) ? save_mean[c0 + k] : 0.f;
+        istd[k] = (active && c0 + k < C) ? save_invstd[c0 + k] : 0.f;
+    }
+    const long long r0 = (long long)blockIdx.y * rows_per_split;
+    const long long r1 = min(M, r0 + rows_per_split);
+    if (active) {
+        for (long long r = r0 + ty; r < r1; r += TY) {
+            float g[VEC], xv[VEC];
+            load_vec<VEC>(dy + r * C + c0, g);
+            load_vec<VEC>(x + r * C + c0, xv);
+            if (relu) {
+                float yv[VEC];
+                load_vec<VEC>(y + r * C + c0, yv);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) g[k] = yv[k] > 0.f ? g[k] : 0.f;
+            }
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) {
+                s[k] += g[k];
+                q[k] = fmaf(g[k], (xv[k] - mean[k]) * istd[k], q[k]);
+            }
+            if (dz) store_vec<VEC>(dz + r * C + c0, g);
+        }
+    }
+    block_reduce_rows<VEC>(s, q, smem, tx, ty, TX, TY);
+    if (ty == 0 && active) {
+        float* ps = partials + (size_t)blockIdx.y * 2 * C;
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            if (c0 + k < C) {
+                ps[c0 + k] = s[k];
+                ps[C + c0 + k] = q[k];
+            }
+        }
+    }
+}
+
+template <int VEC>
+__global__ void __launch_bounds__(kThreads)
+bn_bwd_apply_kernel(const float* __restrict__ dz, const float* __restrict__ x, float* __restrict__ dx, long long M, int C, int TX,
+                    int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ save_mean,
+                    const float* __restrict__ save_invstd, const float* __restrict__ dgamma, const float* __restrict__ dbeta) {
+    const int TY = kThreads / TX;
+    const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
+    const int c0 = (blockIdx.x * TX + tx) * VEC;
+    if (c0 >= C) return;
+    const float inv_m = 1.f / (float)M;
+    float mean[VEC], istd[VEC], sc[VEC], db[VEC], dg[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        const bool in = c0 + k < C;
+        mean[k] = in ? save_mean[c0 + k] : 0.f;
+        istd[k] = in ? save_invstd[c0 + k] : 0.f;
+        sc[k] = in ? (gamma ? gamma[c0 + k] : 1.f) * istd[k] : 0.f;
+        db[k] = in ? dbeta[c0 + k] * inv_m : 0.f;
+        dg[k] = in ? dgamma[c0 + k] * inv_m : 0.f;
+    }
+    const long long r0 = (long long)blockIdx.y * rows_per_split;
+    const long long r1 = min(M, r0 + rows_per_split);
+    for (long long r = r0 + ty; r < r1; r += TY) {
+        float g[VEC], xv[VEC], o[VEC];
+        load_vec<VEC>(dz + r * C + c0, g);
+        load_vec<VEC>(x + r * C + c0, xv);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            const float xhat = (xv[k] - mean[k]) * istd[k];
+            o[k] = sc[k] * (g[k] - db[k] - xhat * dg[k]);
+        }
+        store_vec<VEC>(dx + r * C + c0, o);
+    }
+}
+
+}  // namespace
+
+extern "C" {
+
+// Number of floats the caller must provide in `partials` for an [M, C] problem.
+size_t mgw_bn_partials_floats(long long M, int C) {
+    const Tiling t = make_tiling(M, C, (C % 4 == 0) ? 4 : 1);
+    return (size_t)t.grid_y * 2 * (size_t)C;
+}
+
+int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M, int C, const float* gamma, const float* beta,
+                    float* running_mean, float* running_var, long long* num_batches_tracked, float momentum, float eps,
+                    int relu, float* save_mean, float* save_invstd, float* partials, void* stream) {
+    if (x == nullptr || y == nullptr || M <= 0 || C <= 0 || save_mean == nullptr || save_invstd == nullptr || partials == nullptr)
+        return MGW_ERR_ARG;
+    const int vec = (C % 4 == 0) ? 4 : 1;
+    const Tiling t = make_tiling(M, C, vec);
+    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
+    const dim3 fgrid((C + 31) / 32), fblock(32, 16);
+    if (vec == 4) {
+        bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
+        bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
+                                                        momentum, eps, save_mean, save_invstd);
+        bn_apply_kernel<4><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd);
+    } else {
+        bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
+        bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
+                                                        momentum, eps, save_mean, save_invstd);
+        bn_apply_kernel<1><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd);
+    }
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}
+
+// dz: [M, C] scratch that receives dy masked by the ReLU (also the gradient of the residual input).
+// dx may alias dz.
+int mgw_bn_relu_bwd(const float* dy, const float* y, const float* x, float* dz, float* dx, long long M, int C, const float* gamma,
+                    const float* save_mean, const float* save_invstd, int relu, float* dgamma, float* dbeta, float* partials,
+                    void* stream) {
+    if (dy == nullptr || x == nullptr || dz == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
+    if (dgamma == nullptr || dbeta == nullptr) return MGW_ERR_ARG;
+    if (relu && y == nullptr) return MGW_ERR_ARG;
+    const int vec = (C % 4 == 0) ? 4 : 1;
+    const Tiling t = make_tiling(M, C, vec);
+    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
+    const dim3 fgrid((C + 31) / 32), fblock(32, 16);
+    if (vec == 4) {
+        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, save_mean, save_invstd, relu, partials);
+        bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
+        bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(dz, x, dx, M, C, t.tx, t.rows_per_split, gamma, save_mean, save_invstd, dgamma, dbeta);
+    } else {
+        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, save_mean, save_invstd, relu, partials);
+        bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
+        bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(dz, x, dx, M, C, t.tx, t.rows_per_split, gamma, save_mean, save_invstd, dgamma, dbeta);
+    }
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,142 @@
+# -*- coding: utf-8 -*-
+"""Fused BatchNorm (+ residual add) (+ ReLU) for channels-last activations (``csrc/bn_relu.cu``).
+
+``FusedBatchNorm2d`` / ``FusedBatchNorm1d`` are drop-in subclasses of the torch modules: same
+parameters, buffers and ``state_dict`` keys (``weight, bias, running_mean, running_var,
+num_batches_tracked``), same numerics (biased variance for normalisation, unbiased for the running
+estimate, momentum and eps as configured).  In training mode on a CUDA device with a dense
+channels-innermost input they run this package's kernels; ``forward(x, residual=None)`` optionally
+adds a residual before the ReLU, which covers the tail of a ResNet block in one pass.  The
+reference gets the same math from separate cuDNN BatchNorm, add and ReLU kernels
+(``models/resnet.py:29-39``, torchvision ``Bottleneck``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import _lib, counters
+
+
+def _as_rows(x: torch.Tensor):
+    """View a dense channels-innermost tensor as (M, C); returns None when the layout does not fit."""
+    if x.dim() == 2:
+        return (x.shape[0], x.shape[1]) if x.is_contiguous() else None
+    if x.dim() == 4 and x.is_contiguous(memory_format=torch.channels_last):
+        n, c, h, w = x.shape
+        return n * h * w, c
+    return None
+
+
+_declared = False
+
+
+def _declare(lib) -> None:
+    global _declared
+    if _declared:
+        return
+    lib.mgw_bn_partials_floats.restype = C.c_size_t
+    lib.mgw_bn_partials_floats.argtypes = [C.c_longlong, C.c_int]
+    lib.mgw_bn_relu_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p,
+                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_void_p,
+                                    C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.mgw_bn_relu_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
+                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
+                                    C.c_void_p]
+    _declared = True
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+class _BNReLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, running_mean, running_var, num_batches_tracked, residual, relu, momentum, eps):
+        lib = _lib.load(allow_build=False)
+        _declare(lib)
+        M, Cc = _as_rows(x)
+        y = torch.empty_like(x)
+        mean = torch.empty(Cc, dtype=torch.float32, device=x.device)
+        invstd = torch.empty(Cc, dtype=torch.float32, device=x.device)
+        partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.mgw_bn_relu_fwd(x.data_ptr(), _ptr(residual), y.data_ptr(), M, Cc, _ptr(weight), _ptr(bias),
+                                       _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
+                                       float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
+                                       partials.data_ptr(), s), 'bn_relu_fwd')
+        counters.bump('bn_relu_fwd', 3)
+        ctx.save_for_backward(x, y if relu else None, weight, mean, invstd)
+        ctx.relu, ctx.has_residual, ctx.rows = bool(relu), residual is not None, (M, Cc)
+        ctx.mark_non_differentiable(*[t for t in (running_mean, running_var, num_batches_tracked) if t is not None])
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        lib = _lib.load(allow_build=False)
+        x, y, weight, mean, invstd = ctx.saved_tensors
+        M, Cc = ctx.rows
+        if _as_rows(dy) is None or dy.stride() != x.stride():
+            dy = dy.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else dy.contiguous()
+        dz = torch.empty_like(x)
+        dx = torch.empty_like(x) if ctx.has_residual else dz       # without a residual dx overwrites dz in place
+        dgamma = torch.empty(Cc, dtype=torch.float32, device=x.device)
+        dbeta = torch.empty(Cc, dtype=torch.float32, device=x.device)
+        partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(y), x.data_ptr(), dz.data_ptr(), dx.data_ptr(), M, Cc,
+                                       _ptr(weight), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
+                                       dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), s), 'bn_relu_bwd')
+        counters.bump('bn_relu_bwd', 3)
+        need = ctx.needs_input_grad
+        return (dx if need[0] else None, dgamma if (weight is not None and need[1]) else None,
+                dbeta if need[2] else None, None, None, None, dz if (ctx.has_residual and need[6]) else None,
+                None, None, None)
+
+
+def bn_relu(x, weight, bias, running_mean, running_var, num_batches_tracked, residual=None, relu=True,
+            momentum=0.1, eps=1e-5):
+    """Functional form: training-mode batch norm over all but the channel dimension, optional
+    residual add, optional ReLU.  ``x`` must be CUDA float32, dense, channels innermost."""
+    if not x.is_cuda or x.dtype != torch.float32 or _as_rows(x) is None:
+        raise ValueError('bn_relu needs a dense channels-last (or 2-D) float32 CUDA tensor')
+    if residual is not None and (residual.shape != x.shape or residual.stride() != x.stride()):
+        residual = residual.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else residual.contiguous()
+    return _BNReLU.apply(x, weight, bias, running_mean, running_var, num_batches_tracked, residual, relu, momentum, eps)
+
+
+class _FusedBNMixin:
+    fused_relu = False
+
+    def _native_ok(self, x: torch.Tensor) -> bool:
+        return (self.training and x.is_cuda and x.dtype == torch.float32 and self.momentum is not None
+                and self.track_running_stats and _as_rows(x) is not None and x.numel() > 0)
+
+    def forward(self, x, residual=None):
+        if self._native_ok(x):
+            return bn_relu(x, self.weight, self.bias, self.running_mean, self.running_var, self.num_batches_tracked,
+                           residual, self.fused_relu, self.momentum, self.eps)
+        if x.is_cuda and x.dim() == 4 and self.training and not x.is_contiguous(memory_format=torch.channels_last) \
+                and x.dtype == torch.float32 and self.momentum is not None and self.track_running_stats:
+            # keep the native path: one layout conversion is cheaper than leaving the fused kernels
+            return self.forward(x.contiguous(memory_format=torch.channels_last),
+                                None if residual is None else residual.contiguous(memory_format=torch.channels_last))
+        out = super().forward(x)
+        if residual is not None:
+            out = out + residual
+        return F.relu(out) if self.fused_relu else out
+
+    def extra_repr(self):
+        return super().extra_repr() + ', fused_relu=%s' % self.fused_relu
+
+
+class FusedBatchNorm2d(_FusedBNMixin, nn.BatchNorm2d):
+    pass
+
+
+class FusedBatchNorm1d(_FusedBNMixin, nn.BatchNorm1d):
+    pass

@@ -155,3 +155,93 @@ def test_bounded_wait_reports_timeout_without_hanging(lib):
     y = torch.ones(8, device=dev) * 2          # the context still works
     assert float(y.sum()) == 16.0
     _lib.check(lib.mgw_host_status_free(status))
+
+
+# ----------------------------------------------------------------------------- BatchNorm + ReLU
+def _bn_reference(x, w, b, rm, rv, residual, relu, momentum, eps):
+    y = torch.nn.functional.batch_norm(x, rm, rv, w, b, True, momentum, eps)
+    if residual is not None:
+        y = y + residual
+    return torch.relu(y) if relu else y
+
+
+@pytest.mark.parametrize('shape', [(4, 64, 14, 14), (3, 16, 8, 8), (2, 6, 5, 7), (8, 256, 7, 7), (64, 96)])
+@pytest.mark.parametrize('relu,use_res', [(True, False), (True, True), (False, False)])
+def test_bn_relu_matches_pytorch(shape, relu, use_res):
+    from mgwfbp_b200.ops.bn_relu import bn_relu
+    torch.manual_seed(0)
+    dev = torch.device('cuda')
+    C_ = shape[1]
+    fmt = torch.channels_last if len(shape) == 4 else torch.contiguous_format
+    x = (torch.randn(shape, device=dev) * 2 + 0.5).contiguous(memory_format=fmt).requires_grad_(True)
+    res = torch.randn(shape, device=dev).contiguous(memory_format=fmt).requires_grad_(True) if use_res else None
+    w = (torch.rand(C_, device=dev) + 0.5).requires_grad_(True)
+    b = torch.randn(C_, device=dev).requires_grad_(True)
+    rm, rv, nbt = torch.zeros(C_, device=dev), torch.ones(C_, device=dev), torch.zeros((), dtype=torch.long, device=dev)
+    x2, w2, b2 = x.detach().clone().requires_grad_(True), w.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
+    res2 = res.detach().clone().requires_grad_(True) if use_res else None
+    rm2, rv2 = rm.clone(), rv.clone()
+    y = bn_relu(x, w, b, rm, rv, nbt, res, relu, 0.1, 1e-5)
+    y2 = _bn_reference(x2, w2, b2, rm2, rv2, res2, relu, 0.1, 1e-5)
+    torch.testing.assert_close(y, y2, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(rm, rm2, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(rv, rv2, rtol=1e-4, atol=1e-5)
+    assert int(nbt) == 1
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    y2.backward(dy)
+    torch.testing.assert_close(x.grad, x2.grad, rtol=1e-3, atol=2e-4)
+    torch.testing.assert_close(w.grad, w2.grad, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(b.grad, b2.grad, rtol=1e-3, atol=1e-3)
+    if use_res:
+        torch.testing.assert_close(res.grad, res2.grad, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize('dnn,shape,classes', [('resnet20', (8, 3, 32, 32), 10), ('resnet50', (4, 3, 64, 64), 1000)])
+def test_fused_model_matches_unfused(dnn, shape, classes):
+    from mgwfbp_b200.models import create_net
+    torch.manual_seed(0)
+    a, _ = create_net(classes, dnn)
+    b, _ = create_net(classes, dnn, fuse=True, channels_last=True)
+    b.load_state_dict(a.state_dict())
+    a, b = a.cuda(), b.cuda()
+    x = torch.randn(shape, device='cuda')
+    ya, yb = a(x), b(x.contiguous(memory_format=torch.channels_last))
+    torch.testing.assert_close(yb, ya, rtol=2e-2, atol=2e-2)         # TF32 convolutions on both sides
+    ya.square().mean().backward()
+    yb.square().mean().backward()
+    ga = torch.cat([p.grad.reshape(-1) for p in a.parameters()])
+    gb = torch.cat([p.grad.reshape(-1) for p in b.parameters()])
+    assert torch.nn.functional.cosine_similarity(ga, gb, dim=0) > 0.99
+    for (k, va), vb in zip(a.state_dict().items(), b.state_dict().values()):
+        if 'running_' in k or 'num_batches' in k:
+            torch.testing.assert_close(vb, va, rtol=1e-2, atol=1e-2)
+
+
+# ----------------------------------------------------------------------------- LSTM
+def test_fused_lstm_matches_cudnn_lstm():
+    from mgwfbp_b200.ops.lstm import FusedLSTM
+    torch.manual_seed(0)
+    T, B, I, H = 7, 5, 48, 64
+    ref = torch.nn.LSTM(I, H, 2).cuda()
+    mine = FusedLSTM(I, H, 2).cuda()
+    mine.load_state_dict(ref.state_dict())
+    x = torch.randn(T, B, I, device='cuda')
+    hx = (torch.randn(2, B, H, device='cuda'), torch.randn(2, B, H, device='cuda'))
+    x1, x2 = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        y1, (h1, c1) = ref(x1, hx)
+        y2, (h2, c2) = mine(x2, hx)
+        torch.testing.assert_close(y2, y1, rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(h2, h1, rtol=1e-4, atol=1e-5)
+        torch.testing.assert_close(c2, c1, rtol=1e-4, atol=1e-5)
+        w = torch.randn_like(y1)
+        (y1 * w).sum().backward()
+        (y2 * w).sum().backward()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    torch.testing.assert_close(x2.grad, x1.grad, rtol=1e-3, atol=1e-4)
+    for (n, p1), p2 in zip(ref.named_parameters(), mine.parameters()):
+        torch.testing.assert_close(p2.grad, p1.grad, rtol=1e-3, atol=1e-4, msg=lambda m: '%s: %s' % (n, m))

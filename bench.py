@@ -171,8 +171,9 @@ def run_ours(args):
     barrier = hvd.barrier
     for i in range(max(args.warmup, 3)):
         step_device(i)
-    for i in range(3):
-        step_e2e(i)
+    if not args.skip_e2e:
+        for i in range(3):
+            step_e2e(i)
     step.drain()
     torch.cuda.synchronize()
 
@@ -180,7 +181,11 @@ def run_ours(args):
     if sampler:
         sampler.start()
     counters.reset()
+    if args.profiler_range:
+        torch.cuda.profiler.start()
     ms_dev = _time_steps(torch, world > 1, step_device, args.steps, barrier)
+    if args.profiler_range:
+        torch.cuda.profiler.stop()
     launches = counters.total()
     clocks = sampler.stop() if sampler else None
     del loss_host[:]
@@ -189,7 +194,7 @@ def run_ours(args):
         step_e2e(i)
         if i == args.steps - 1:
             step.drain()           # the last step's loss is read inside the timed region too
-    ms_e2e = _time_steps(torch, world > 1, e2e_all, args.steps, barrier)
+    ms_e2e = _time_steps(torch, world > 1, e2e_all, args.steps, barrier) if not args.skip_e2e else float('nan')
     ms_dev = hvd.parallel.runtime.max_over_ranks(ms_dev) if world > 1 else ms_dev
     ms_e2e = hvd.parallel.runtime.max_over_ranks(ms_e2e) if world > 1 else ms_e2e
     final_loss = step.last_loss()
@@ -352,6 +357,9 @@ def main():
     ap.add_argument('--batch-size', type=int, default=None, help='per-GPU batch (default: the workload\'s)')
     ap.add_argument('--policy', choices=['mgwfbp', 'wfbp', 'single'], default='mgwfbp')
     ap.add_argument('--no-graph', action='store_true', help='do not capture the training step in a CUDA graph')
+    ap.add_argument('--skip-e2e', action='store_true', help='profiling aid: time only the device-resident loop')
+    ap.add_argument('--profiler-range', action='store_true',
+                    help='profiling aid: bracket the timed device loop with cudaProfilerStart/Stop (ncu --profile-from-start off)')
     ap.add_argument('--no-comm-fit', action='store_true', help='skip the alpha-beta sweep; use the built-in NVLink table')
     args = ap.parse_args()
     if args.impl == 'reference':

@@ -1,0 +1,396 @@
+// Weight-gradient GEMM for large fully-connected / LSTM layers on Blackwell tensor cores:
+//
+//     dW[M, N] = sum_k  dY[k, m] * X[k, n]        (M = out features, N = in features, K = batch rows)
+//
+// with dY stored [K, M] and X stored [K, N] row-major, i.e. BOTH operands are "MN-major": K is the
+// slow dimension of both.  K is small (64 rows per GPU for the VGG classifier, 700 for the PTB
+// LSTM), so the kernel is bound by its output, not by math: a 128x128 fp32 tile is 64 KB of result
+// for 2*128*128*K flops.  That is why the epilogue does the optimizer work in place: instead of
+// writing dW and having an all-reduce and an SGD kernel read it back, the tile leaves tensor memory
+// once and is applied to the weights and momentum directly (optionally also stored as a gradient).
+//
+// Data-parallel use: every rank first all-gathers the K-rows of dY and X of all ranks into local
+// buffers (mgw_allgather_rows below: peer loads over NVLink, bounded flag waits).  That moves
+// W*B*(M+N) floats instead of all-reducing M*N of them (7.4 MB instead of 411 MB for the
+// 25088 -> 4096 VGG layer on 8 GPUs), and every rank then runs this same GEMM over K = W*B rows in
+// the same order, so replicas stay bit-identical.
+//
+// Structure of one CTA (192 threads, one 128x128 output tile, two CTAs per SM):
+//   warp 0   : TMA producer.  Per K-block of 32 rows: four 2-D tiled bulk-tensor loads of
+//              [32 rows x 32 floats] for each operand, 128-byte swizzle, completing on an mbarrier.
+//   warp 1   : allocates 128 tensor-memory columns, then one lane issues tcgen05.mma kind::tf32
+//              (M=128, N=128, K=8 per instruction, both operands MN-major from shared memory) and
+//              commits each stage back to the producer and the finished tile to the epilogue.
+//   warps 2-5: epilogue.  tcgen05.ld (32 lanes x 32 columns per warp) -> swizzled shared-memory
+//              slab -> coalesced 128-byte row segments of W / momentum / gradient in global memory.
+// Every mbarrier wait is bounded; on expiry the CTA records an error, lets its outstanding bulk
+// copies land (bounded as well), frees its tensor memory and returns.
+#include <cuda.h>
+#include "api.h"
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 32;
+constexpr int kStages = 2;
+constexpr int kAtomFloats = 32;                       // 128-byte swizzle atom = 32 floats along M or N
+constexpr int kRegionBytes = BK * 128;                // one [BK x 32 floats] box
+constexpr int kAStageBytes = (BM / kAtomFloats) * kRegionBytes;   // 16 KB
+constexpr int kBStageBytes = (BN / kAtomFloats) * kRegionBytes;   // 16 KB
+constexpr int kStageBytes = kAStageBytes + kBStageBytes;
+constexpr int kSlabCols = 32;
+constexpr int kSlabBytes = BM * kSlabCols * 4;        // 16 KB
+constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kSlabBytes + 256;
+constexpr int kTmemCols = 128;
+constexpr uint32_t kWaitSpins = 1u << 22;
+
+#define WG_MODE_STORE 1      // write dW * scale to `grad_out`
+#define WG_MODE_SGD 2        // apply dW * scale to (weight, momentum) with the hyper-parameters of `pg`
+
+struct Params {
+    float* weight;
+    float* mom;
+    float* grad_out;
+    const MgwHyper* hyper;
+    int* status;
+    int M, N, K;
+    int mode, pg, first_step;
+    float scale;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+// Bounded parity wait.  Returns false when the phase did not complete within the spin budget.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (uint32_t spin = 0; spin < kWaitSpins; ++spin) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+        if (spin > 1024) __nanosleep(32);
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+
+// Shared-memory matrix descriptor: MN-major operand, 128-byte swizzle.  `lbo` = bytes between
+// consecutive 32-float atoms along M/N, `sbo` = bytes between consecutive 8-row K atoms.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+    d |= 1ull << 46;                 // descriptor version for this architecture
+    d |= 2ull << 61;                 // 128-byte swizzle
+    return d;
+}
+
+// Instruction descriptor: D = F32, A = B = TF32, both operands MN-major, M = 128, N = 128.
+__device__ __forceinline__ uint32_t make_instr_desc() {
+    return (1u << 4) | (2u << 7) | (2u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0), "r"(0), "r"(0), "r"(0) : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__device__ __forceinline__ void report(int* status, int code) {
+    if (status) atomicCAS(status, 0, code);
+}
+
+__global__ void __launch_bounds__(192)
+wgrad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* stages = smem;                                           // kStages x (A | B), 1024-byte aligned
+    float4* slab = reinterpret_cast<float4*>(smem + kStages * kStageBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + kSlabBytes);
+    uint64_t* full = bars;                     // [kStages]
+    uint64_t* empty = bars + kStages;          // [kStages]
+    uint64_t* acc_ready = bars + 2 * kStages;  // [1]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kStages + 1);
+    volatile int* failed = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int num_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        mbar_init(acc_ready, 1);
+        *failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const int s = kb % kStages;
+                const uint32_t ph = (kb / kStages) & 1;
+                if (!mbar_wait(&empty[s], ph ^ 1)) { report(p.status, 11); *failed = 1; break; }
+                if (*failed) break;
+                uint8_t* a_dst = stages + s * kStageBytes;
+                uint8_t* b_dst = a_dst + kAStageBytes;
+                mbar_expect_tx(&full[s], kStageBytes);
+#pragma unroll
+                for (int j = 0; j < BM / kAtomFloats; ++j) tma_load_2d(a_dst + j * kRegionBytes, &map_a, m0 + j * kAtomFloats, kb * BK, &full[s]);
+#pragma unroll
+                for (int j = 0; j < BN / kAtomFloats; ++j) tma_load_2d(b_dst + j * kRegionBytes, &map_b, n0 + j * kAtomFloats, kb * BK, &full[s]);
+                issued = kb + 1;
+            }
+            if (*failed) {
+                // let copies that were already issued land before the CTA gives up its shared memory
+                for (int kb = max(0, issued - kStages); kb < issued; ++kb) (void)mbar_wait(&full[kb % kStages], (kb / kStages) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_instr_desc();
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % kStages;
+                const uint32_t ph = (kb / kStages) & 1;
+                if (!mbar_wait(&full[s], ph) || *failed) { report(p.status, 12); *failed = 1; ok = false; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a_addr = smem_u32(stages + s * kStageBytes);
+                const uint32_t b_addr = a_addr + kAStageBytes;
+#pragma unroll
+                for (int kk = 0; kk < BK / 8; ++kk) {
+                    const uint64_t adesc = make_smem_desc(a_addr + kk * 1024, kRegionBytes, 1024);
+                    const uint64_t bdesc = make_smem_desc(b_addr + kk * 1024, kRegionBytes, 1024);
+                    umma_tf32(tmem_base, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
+                }
+                umma_commit(&empty[s]);          // the stage may be refilled once these MMAs have read it
+            }
+            umma_commit(acc_ready);              // arrives when every MMA issued above has completed
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int q = warp & 3;                  // tensor-memory lane quarter this warp may read
+        const int et = threadIdx.x - 64;         // 0..127
+        bool ok = mbar_wait(acc_ready, 0);
+        if (!ok) { report(p.status, 13); *failed = 1; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        MgwHyper h;
+        if (p.mode & WG_MODE_SGD) h = p.hyper[p.pg];
+        for (int sc = 0; sc < BN / kSlabCols; ++sc) {
+            if (ok && !*failed) {
+                float v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(sc * kSlabCols), v);
+                const int r = q * 32 + lane;     // row of the tile held by this thread
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    slab[r * 8 + (c ^ (r & 7))] = make_float4(v[4 * c] * p.scale, v[4 * c + 1] * p.scale, v[4 * c + 2] * p.scale, v[4 * c + 3] * p.scale);
+            }
+            epilogue_bar();
+            if (ok && !*failed) {
+                const int c = et & 7;
+                const int n = n0 + sc * kSlabCols + 4 * c;
+#pragma unroll 4
+                for (int r = et >> 3; r < BM; r += 16) {
+                    const int m = m0 + r;
+                    if (m < p.M && n < p.N) {
+                        float4 g = slab[r * 8 + (c ^ (r & 7))];
+                        const size_t off = (size_t)m * p.N + n;
+                        if (p.mode & WG_MODE_STORE) *reinterpret_cast<float4*>(p.grad_out + off) = g;
+                        if (p.mode & WG_MODE_SGD) {
+                            float4 w = *reinterpret_cast<float4*>(p.weight + off);
+                            const bool use_m = p.mom != nullptr && h.momentum != 0.f;
+                            float4 mo = make_float4(0.f, 0.f, 0.f, 0.f);
+                            if (use_m && !p.first_step) mo = *reinterpret_cast<float4*>(p.mom + off);
+                            mgw_sgd_scalar(g.x, w.x, use_m ? &mo.x : nullptr, h, p.first_step);
+                            mgw_sgd_scalar(g.y, w.y, use_m ? &mo.y : nullptr, h, p.first_step);
+                            mgw_sgd_scalar(g.z, w.z, use_m ? &mo.z : nullptr, h, p.first_step);
+                            mgw_sgd_scalar(g.w, w.w, use_m ? &mo.w : nullptr, h, p.first_step);
+                            *reinterpret_cast<float4*>(p.weight + off) = w;
+                            if (use_m) *reinterpret_cast<float4*>(p.mom + off) = mo;
+                        }
+                    }
+                }
+            }
+            epilogue_bar();
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---- all-gather of K-row blocks over NVLink -----------------------------------------------------------
+// Every rank contributes `rows` x `cols` floats (its block lives at offset rank*rows*cols of its own
+// symmetric buffer); afterwards every rank holds all W blocks in rank order.  Pull design: signal
+// "my block is in place", wait for each peer (bounded), copy the peer's block with 16-byte loads.
+__global__ void __launch_bounds__(512)
+allgather_rows_kernel(float* const* bufs, uint32_t* const* flags, uint32_t* epoch, int* status, int rank, int world,
+                      long long block_floats, unsigned long long timeout_ns) {
+    __shared__ int failed;
+    const int b = blockIdx.x;
+    const uint32_t e = epoch[b] + 1u;
+    if (threadIdx.x == 0) failed = 0;
+    __syncthreads();
+    if (threadIdx.x < world) {
+        __threadfence_system();
+        mgw_st_release_sys(flags[threadIdx.x] + (size_t)b * MGW_MAX_RANKS + rank, e);
+        uint32_t seen = 0;
+        if (!mgw_wait_flag(flags[rank] + (size_t)b * MGW_MAX_RANKS + threadIdx.x, e, timeout_ns, &seen)) {
+            mgw_report(status, MGW_STATUS_TIMEOUT, threadIdx.x, (int)e, (int)seen);
+            failed = 1;
+        }
+    }
+    __syncthreads();
+    if (!failed) {
+        const long long nvec = block_floats / 4;
+        const long long per = (nvec + gridDim.x - 1) / gridDim.x;
+        const long long v0 = (long long)b * per, v1 = min(nvec, v0 + per);
+        for (int i = 1; i < world; ++i) {
+            int q = rank + i;
+            if (q >= world) q -= world;
+            const float4* src = reinterpret_cast<const float4*>(bufs[q] + (size_t)q * block_floats);
+            float4* dst = reinterpret_cast<float4*>(bufs[rank] + (size_t)q * block_floats);
+            for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) dst[v] = mgw_ld_peer(src + v);
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) epoch[b] = e;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    }
+    return fn;
+}
+
+// [K rows, inner floats] row-major operand -> boxes of [BK rows x 32 floats], 128-byte swizzle.
+bool make_map(CUtensorMap* map, const float* base, int K, int inner) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)K};
+    cuuint64_t strides[1] = {(cuuint64_t)inner * sizeof(float)};
+    cuuint32_t box[2] = {(cuuint32_t)kAtomFloats, (cuuint32_t)BK};
+    cuuint32_t elem[2] = {1, 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+extern "C" {
+
+// 1 when the shapes meet the kernel's alignment rules (16-byte aligned bases, M and N multiples of 4).
+int mgw_wgrad_gemm_supported(const void* dy, const void* x, int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return 0;
+    if ((M & 3) || (N & 3)) return 0;
+    if ((reinterpret_cast<uintptr_t>(dy) & 15) || (reinterpret_cast<uintptr_t>(x) & 15)) return 0;
+    return 1;
+}
+
+// dy: [K, M], x: [K, N] row-major fp32.  mode bit 1: grad_out[M, N] = scale * dy^T x;
+// mode bit 2: momentum-SGD on (weight, mom) with hyper[pg].  status: one device-visible int (0 = ok).
+int mgw_wgrad_gemm(const float* dy, const float* x, int M, int N, int K, float scale, int mode, float* grad_out, float* weight,
+                   float* mom, const MgwHyper* hyper, int pg, int first_step, int* status, void* stream) {
+    if (!mgw_wgrad_gemm_supported(dy, x, M, N, K)) return MGW_ERR_ARG;
+    if ((mode & WG_MODE_STORE) && grad_out == nullptr) return MGW_ERR_ARG;
+    if ((mode & WG_MODE_SGD) && (weight == nullptr || hyper == nullptr)) return MGW_ERR_ARG;
+    if ((mode & (WG_MODE_STORE | WG_MODE_SGD)) == 0) return MGW_ERR_ARG;
+    CUtensorMap map_a, map_b;
+    if (!make_map(&map_a, dy, K, M) || !make_map(&map_b, x, K, N)) {
+        mgw_set_last_error(cudaErrorUnknown, "cuTensorMapEncodeTiled", __FILE__, __LINE__);
+        return MGW_ERR_CUDA;
+    }
+    static bool configured = false;
+    if (!configured) {
+        MGW_CUDA_CHECK(cudaFuncSetAttribute(wgrad_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        configured = true;
+    }
+    Params p;
+    p.weight = weight; p.mom = mom; p.grad_out = grad_out; p.hyper = hyper; p.status = status;
+    p.M = M; p.N = N; p.K = K; p.mode = mode; p.pg = pg; p.first_step = first_step; p.scale = scale;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    wgrad_gemm_kernel<<<grid, 192, kSmemBytes, (cudaStream_t)stream>>>(map_a, map_b, p);
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}
+
+// flags: every rank's [n_ctas][MGW_MAX_RANKS] flag rows of this collective; epoch: local [n_ctas] counters.
+int mgw_allgather_rows(float* const* bufs_dev, uint32_t* const* flags_dev, uint32_t* epoch, int* status, int rank, int world,
+                       long long block_floats, int n_ctas, unsigned long long timeout_ns, void* stream) {
+    if (bufs_dev == nullptr || flags_dev == nullptr || epoch == nullptr) return MGW_ERR_ARG;
+    if (world < 1 || world > MGW_MAX_RANKS || rank < 0 || rank >= world || n_ctas < 1 || n_ctas > MGW_MAX_CTAS) return MGW_ERR_ARG;
+    if (block_floats <= 0 || (block_floats & 3)) return MGW_ERR_ARG;
+    allgather_rows_kernel<<<n_ctas, 512, 0, (cudaStream_t)stream>>>(bufs_dev, flags_dev, epoch, status, rank, world, block_floats, timeout_ns);
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}
+
+}  // extern "C"

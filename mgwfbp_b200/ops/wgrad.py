@@ -1,0 +1,96 @@
+# -*- coding: utf-8 -*-
+"""Tensor-core weight-gradient GEMM with an optimizer epilogue (``csrc/wgrad_gemm_sm100.cu``).
+
+``wgrad_gemm(dy, x)`` returns ``dy^T @ x`` (TF32 inputs, fp32 accumulation in tensor memory).
+``wgrad_sgd_(dy, x, weight, momentum_buffer, hyper, ...)`` applies the same product straight to the
+weights: the gradient tile never makes a round trip through HBM.  ``GatheredWgradLinear`` uses it
+for data-parallel training of large fully-connected layers whose batch is small: ranks exchange
+their activations and output gradients (a few MB) instead of all-reducing the weight gradient
+(hundreds of MB for the 25088 -> 4096 VGG layer, ``torchvision vgg16.classifier``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib, counters
+
+MODE_STORE, MODE_SGD = 1, 2
+_declared = False
+
+
+def _lib_ready():
+    global _declared
+    lib = _lib.load(allow_build=False)
+    if not _declared:
+        lib.mgw_wgrad_gemm_supported.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+        lib.mgw_wgrad_gemm.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_int, C.c_void_p,
+                                       C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
+        lib.mgw_allgather_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_longlong,
+                                           C.c_int, C.c_ulonglong, C.c_void_p]
+        _declared = True
+    return lib
+
+
+_status_cache = {}
+
+
+def _status(device) -> torch.Tensor:
+    t = _status_cache.get(device)
+    if t is None:
+        t = _status_cache[device] = torch.zeros(1, dtype=torch.int32, device=device)
+    return t
+
+
+def supported(dy: torch.Tensor, x: torch.Tensor) -> bool:
+    if not (dy.is_cuda and x.is_cuda and dy.dtype == torch.float32 and x.dtype == torch.float32):
+        return False
+    if dy.dim() != 2 or x.dim() != 2 or dy.shape[0] != x.shape[0] or not dy.is_contiguous() or not x.is_contiguous():
+        return False
+    return bool(_lib_ready().mgw_wgrad_gemm_supported(dy.data_ptr(), x.data_ptr(), dy.shape[1], x.shape[1], dy.shape[0]))
+
+
+def check_status(device=None) -> None:
+    """Raise if a GEMM CTA gave up on one of its bounded waits (synchronises the device)."""
+    for dev, t in _status_cache.items():
+        if device is None or dev == device:
+            code = int(t.item())
+            if code != 0:
+                t.zero_()
+                raise RuntimeError('wgrad_gemm kernel reported wait failure code %d' % code)
+
+
+def wgrad_gemm(dy: torch.Tensor, x: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``scale * dy^T @ x`` for ``dy [K, M]`` and ``x [K, N]`` (row-major fp32)."""
+    if not supported(dy, x):
+        raise ValueError('wgrad_gemm needs contiguous fp32 CUDA matrices with M and N multiples of 4')
+    lib = _lib_ready()
+    K, M = dy.shape
+    N = x.shape[1]
+    if out is None:
+        out = torch.empty(M, N, dtype=torch.float32, device=dy.device)
+    _lib.check(lib.mgw_wgrad_gemm(dy.data_ptr(), x.data_ptr(), M, N, K, float(scale), MODE_STORE, out.data_ptr(), None, None,
+                                  None, 0, 0, _status(dy.device).data_ptr(), torch.cuda.current_stream().cuda_stream), 'wgrad_gemm')
+    counters.bump('wgrad_gemm_sm100')
+    return out
+
+
+def wgrad_sgd_(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, momentum_buffer: Optional[torch.Tensor],
+               hyper_ptr: int, pg: int = 0, scale: float = 1.0, first_step: bool = False,
+               grad_out: Optional[torch.Tensor] = None, stream: Optional[torch.cuda.Stream] = None) -> None:
+    """In-place SGD update of ``weight [M, N]`` with the gradient ``scale * dy^T @ x``; the
+    hyper-parameters are read from the device table at ``hyper_ptr`` (entry ``pg``)."""
+    if not supported(dy, x) or not weight.is_contiguous() or tuple(weight.shape) != (dy.shape[1], x.shape[1]):
+        raise ValueError('wgrad_sgd_ needs contiguous fp32 CUDA operands of matching shapes')
+    lib = _lib_ready()
+    K, M = dy.shape
+    N = x.shape[1]
+    mode = MODE_SGD | (MODE_STORE if grad_out is not None else 0)
+    s = (stream or torch.cuda.current_stream()).cuda_stream
+    _lib.check(lib.mgw_wgrad_gemm(dy.data_ptr(), x.data_ptr(), M, N, K, float(scale), mode,
+                                  None if grad_out is None else grad_out.data_ptr(), weight.data_ptr(),
+                                  None if momentum_buffer is None else momentum_buffer.data_ptr(), hyper_ptr, pg,
+                                  int(first_step), _status(dy.device).data_ptr(), s), 'wgrad_gemm(sgd)')
+    counters.bump('wgrad_gemm_sm100')

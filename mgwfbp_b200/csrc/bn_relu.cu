@@ -9,10 +9,12 @@
 //                            running statistics and num_batches_tracked
 //   bn_apply_kernel        : y = relu(x * scale + shift (+ residual))
 // Backward:
-//   bn_bwd_reduce_kernel   : dz = dy * (y > 0); partial sums of dz and dz * xhat; writes dz
+//   bn_bwd_reduce_kernel   : dz = dy * relu'(.); partial sums of dz and dz * xhat
 //   bn_bwd_finalize_kernel : (tiny) dgamma, dbeta
 //   bn_bwd_apply_kernel    : dx = scale * (dz - (dbeta + xhat * dgamma) / M)
-// dz doubles as the gradient of the residual input.
+// With a residual input dz is materialised (it is the residual's gradient) and the ReLU mask is read
+// from the saved output; without one neither y nor dz is touched: the mask is recomputed from x, so
+// the backward pass is 4 reads + 1 write of the activation instead of 5 + 2.
 //
 // Thread layout: a block is TX lanes along channels (each lane owns VEC consecutive channels, one
 // 16-byte access when VEC = 4) by TY rows; grid.x tiles the channels, grid.y splits the rows.
@@ -236,23 +238,54 @@ bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ residual,
     }
 }
 
+// Gradient entering the normalisation for one vector of channels: dy, masked by the ReLU.
+// mask_mode 0: no ReLU; 1: mask from the saved output y; 2: mask recomputed from x (bitwise the same
+// fused multiply-add as the forward pass, so the sign test agrees with what the forward pass clipped).
+template <int VEC>
+__device__ __forceinline__ void masked_grad(float (&g)[VEC], const float (&xv)[VEC], const float* __restrict__ y_row, int mask_mode,
+                                            const float (&sc)[VEC], const float (&sh)[VEC]) {
+    if (mask_mode == 1) {
+        float yv[VEC];
+        load_vec<VEC>(y_row, yv);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) g[k] = yv[k] > 0.f ? g[k] : 0.f;
+    } else if (mask_mode == 2) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) g[k] = fmaf(xv[k], sc[k], sh[k]) > 0.f ? g[k] : 0.f;
+    }
+}
+
+template <int VEC>
+__device__ __forceinline__ void load_channel_consts(int c0, int C, const float* __restrict__ gamma, const float* __restrict__ beta,
+                                                    const float* __restrict__ save_mean, const float* __restrict__ save_invstd,
+                                                    float (&mean)[VEC], float (&istd)[VEC], float (&sc)[VEC], float (&sh)[VEC]) {
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) {
+        const bool in = c0 + k < C;
+        mean[k] = in ? save_mean[c0 + k] : 0.f;
+        istd[k] = in ? save_invstd[c0 + k] : 0.f;
+        const float g = (in && gamma) ? gamma[c0 + k] : 1.f;
+        const float b = (in && beta) ? beta[c0 + k] : 0.f;
+        sc[k] = in ? g * istd[k] : 0.f;
+        sh[k] = in ? b - mean[k] * sc[k] : 0.f;
+    }
+}
+
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
 bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, const float* __restrict__ x, float* __restrict__ dz,
-                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ save_mean,
-                     const float* __restrict__ save_invstd, int relu, float* __restrict__ partials) {
+                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
+                     const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
+                     float* __restrict__ partials) {
     extern __shared__ float smem[];
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int c0 = (blockIdx.x * TX + tx) * VEC;
     const bool active = c0 < C;
-    float s[VEC], q[VEC], mean[VEC], istd[VEC];
+    float s[VEC], q[VEC], mean[VEC], istd[VEC], sc[VEC], sh[VEC];
 #pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-        s[k] = q[k] = 0.f;
-        mean[k] = (active && c0 + k < C) ? save_mean[c0 + k] : 0.f;
-        istd[k] = (active && c0 + k < C) ? save_invstd[c0 + k] : 0.f;
-    }
+    for (int k = 0; k < VEC; ++k) s[k] = q[k] = 0.f;
+    load_channel_consts<VEC>(active ? c0 : C, C, gamma, beta, save_mean, save_invstd, mean, istd, sc, sh);
     const long long r0 = (long long)blockIdx.y * rows_per_split;
     const long long r1 = min(M, r0 + rows_per_split);
     if (active) {
@@ -260,12 +293,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, 
             float g[VEC], xv[VEC];
             load_vec<VEC>(dy + r * C + c0, g);
             load_vec<VEC>(x + r * C + c0, xv);
-            if (relu) {
-                float yv[VEC];
-                load_vec<VEC>(y + r * C + c0, yv);
-#pragma unroll
-                for (int k = 0; k < VEC; ++k) g[k] = yv[k] > 0.f ? g[k] : 0.f;
-            }
+            masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0 : nullptr, mask_mode, sc, sh);
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
                 s[k] += g[k];
@@ -287,23 +315,23 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, 
     }
 }
 
+// gsrc is dz (mask already applied, mask_mode 0) or dy (mask applied here again, mask_mode 1 / 2).
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
-bn_bwd_apply_kernel(const float* __restrict__ dz, const float* __restrict__ x, float* __restrict__ dx, long long M, int C, int TX,
-                    int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ save_mean,
-                    const float* __restrict__ save_invstd, const float* __restrict__ dgamma, const float* __restrict__ dbeta) {
+bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ y, const float* __restrict__ x, float* __restrict__ dx,
+                    long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
+                    const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
+                    const float* __restrict__ dgamma, const float* __restrict__ dbeta) {
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int c0 = (blockIdx.x * TX + tx) * VEC;
     if (c0 >= C) return;
     const float inv_m = 1.f / (float)M;
-    float mean[VEC], istd[VEC], sc[VEC], db[VEC], dg[VEC];
+    float mean[VEC], istd[VEC], sc[VEC], sh[VEC], db[VEC], dg[VEC];
+    load_channel_consts<VEC>(c0, C, gamma, beta, save_mean, save_invstd, mean, istd, sc, sh);
 #pragma unroll
     for (int k = 0; k < VEC; ++k) {
         const bool in = c0 + k < C;
-        mean[k] = in ? save_mean[c0 + k] : 0.f;
-        istd[k] = in ? save_invstd[c0 + k] : 0.f;
-        sc[k] = in ? (gamma ? gamma[c0 + k] : 1.f) * istd[k] : 0.f;
         db[k] = in ? dbeta[c0 + k] * inv_m : 0.f;
         dg[k] = in ? dgamma[c0 + k] * inv_m : 0.f;
     }
@@ -311,8 +339,9 @@ bn_bwd_apply_kernel(const float* __restrict__ dz, const float* __restrict__ x, f
     const long long r1 = min(M, r0 + rows_per_split);
     for (long long r = r0 + ty; r < r1; r += TY) {
         float g[VEC], xv[VEC], o[VEC];
-        load_vec<VEC>(dz + r * C + c0, g);
+        load_vec<VEC>(gsrc + r * C + c0, g);
         load_vec<VEC>(x + r * C + c0, xv);
+        masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0 : nullptr, mask_mode, sc, sh);
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
             const float xhat = (xv[k] - mean[k]) * istd[k];
@@ -358,14 +387,18 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
     return MGW_OK;
 }
 
-// dz: [M, C] scratch that receives dy masked by the ReLU (also the gradient of the residual input).
-// dx may alias dz.
+// Backward.  With dz != null the masked gradient dy * (y > 0) is written there (it is also the gradient
+// of the residual input) and the ReLU mask comes from y; dx may alias dz.  With dz == null nothing is
+// materialised: both passes read dy and x and rebuild the mask from x (gamma / beta must be the forward
+// values), which saves one read and one write of the activation.
 int mgw_bn_relu_bwd(const float* dy, const float* y, const float* x, float* dz, float* dx, long long M, int C, const float* gamma,
-                    const float* save_mean, const float* save_invstd, int relu, float* dgamma, float* dbeta, float* partials,
-                    void* stream) {
-    if (dy == nullptr || x == nullptr || dz == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
-    if (dgamma == nullptr || dbeta == nullptr) return MGW_ERR_ARG;
-    if (relu && y == nullptr) return MGW_ERR_ARG;
+                    const float* beta, const float* save_mean, const float* save_invstd, int relu, float* dgamma, float* dbeta,
+                    float* partials, void* stream) {
+    if (dy == nullptr || x == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
+    if (dgamma == nullptr || dbeta == nullptr || save_mean == nullptr || save_invstd == nullptr) return MGW_ERR_ARG;
+    const int mask1 = !relu ? 0 : (y != nullptr ? 1 : 2);          // mask used by the reduce pass
+    const int mask2 = dz != nullptr ? 0 : mask1;                   // apply pass: dz already carries the mask
+    const float* gsrc = dz != nullptr ? dz : dy;
     const int vec = (C % 4 == 0) ? 4 : 1;
     const Tiling t = make_tiling(M, C, vec);
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
@@ -373,13 +406,13 @@ int mgw_bn_relu_bwd(const float* dy, const float* y, const float* x, float* dz, 
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 16);
     if (vec == 4) {
-        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, save_mean, save_invstd, relu, partials);
+        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(dz, x, dx, M, C, t.tx, t.rows_per_split, gamma, save_mean, save_invstd, dgamma, dbeta);
+        bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(gsrc, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta);
     } else {
-        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, save_mean, save_invstd, relu, partials);
+        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(dz, x, dx, M, C, t.tx, t.rows_per_split, gamma, save_mean, save_invstd, dgamma, dbeta);
+        bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(gsrc, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;

@@ -45,8 +45,8 @@ def _declare(lib) -> None:
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p]
     lib.mgw_bn_relu_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
-                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p,
-                                    C.c_void_p]
+                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
+                                    C.c_void_p, C.c_void_p]
     _declared = True
 
 
@@ -70,7 +70,8 @@ class _BNReLU(torch.autograd.Function):
                                        float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
                                        partials.data_ptr(), s), 'bn_relu_fwd')
         counters.bump('bn_relu_fwd', 3)
-        ctx.save_for_backward(x, y if relu else None, weight, mean, invstd)
+        # the output is only needed to rebuild the ReLU mask when a residual was added
+        ctx.save_for_backward(x, y if (relu and residual is not None) else None, weight, bias, mean, invstd)
         ctx.relu, ctx.has_residual, ctx.rows = bool(relu), residual is not None, (M, Cc)
         ctx.mark_non_differentiable(*[t for t in (running_mean, running_var, num_batches_tracked) if t is not None])
         return y
@@ -78,18 +79,18 @@ class _BNReLU(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         lib = _lib.load(allow_build=False)
-        x, y, weight, mean, invstd = ctx.saved_tensors
+        x, y, weight, bias, mean, invstd = ctx.saved_tensors
         M, Cc = ctx.rows
         if _as_rows(dy) is None or dy.stride() != x.stride():
             dy = dy.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else dy.contiguous()
-        dz = torch.empty_like(x)
-        dx = torch.empty_like(x) if ctx.has_residual else dz       # without a residual dx overwrites dz in place
+        dz = torch.empty_like(x) if ctx.has_residual else None     # only a residual needs the masked gradient itself
+        dx = torch.empty_like(x)
         dgamma = torch.empty(Cc, dtype=torch.float32, device=x.device)
         dbeta = torch.empty(Cc, dtype=torch.float32, device=x.device)
         partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
         s = torch.cuda.current_stream().cuda_stream
-        _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(y), x.data_ptr(), dz.data_ptr(), dx.data_ptr(), M, Cc,
-                                       _ptr(weight), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
+        _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
+                                       _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
                                        dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), s), 'bn_relu_bwd')
         counters.bump('bn_relu_bwd', 3)
         need = ctx.needs_input_grad

@@ -59,3 +59,43 @@ extern "C" int mgw_clip_coef(const float* partials, int n, float max_norm, float
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
 }
+
+// ---- allocation-free variant (declared in noalloc.h) ---------------------------------------------------
+#include "noalloc.h"
+#include <cstdio>
+
+// Scratch for the per-CTA partial sums.  In host code this name is only a handle for
+// cudaGetSymbolAddress(); the kernels receive the device address obtained from it.
+static __device__ __align__(256) float g_static_partials[MGW_STATIC_MAX_PARTIALS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_partials_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int mgw_grad_clip_coef_static(const MgwGroup* group, float max_norm, float* out2, int n_ctas, void* stream) {
+    if (group == nullptr || out2 == nullptr || group->n_vec < 0 || n_ctas < 1) return MGW_ERR_ARG;
+    if (n_ctas > MGW_STATIC_MAX_PARTIALS) {
+        static thread_local char msg[160];
+        snprintf(msg, sizeof(msg), "n_ctas = %d exceeds the built-in scratch of %d partial sums", n_ctas, MGW_STATIC_MAX_PARTIALS);
+        mgw_set_last_error(cudaErrorInvalidValue, msg, __FILE__, __LINE__);
+        return MGW_ERR_TOO_LARGE;
+    }
+    int dev = -1;
+    MGW_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return MGW_ERR_ARG;
+    if (g_static_partials_addr[dev] == nullptr) {
+        // once per device, with that device current: translate the symbol into this device's address
+        float* p = nullptr;
+        MGW_CUDA_CHECK(cudaGetSymbolAddress((void**)&p, g_static_partials));
+        g_static_partials_addr[dev] = p;
+    }
+    float* partials = g_static_partials_addr[dev];
+    cudaStream_t s = (cudaStream_t)stream;
+    if (group->n_vec == 0) n_ctas = 1;
+    mgw_multi_tensor_sgd_kernel<<<n_ctas, 512, 0, s>>>(*group, nullptr, nullptr, 1.f, 0, MGW_MODE_SUMSQ, partials);
+    MGW_CUDA_CHECK(cudaGetLastError());
+    mgw_clip_coef_kernel<<<1, 32, 0, s>>>(partials, n_ctas, max_norm, out2);
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}

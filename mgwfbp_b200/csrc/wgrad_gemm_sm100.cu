@@ -17,7 +17,8 @@
 //
 // Structure of one CTA (192 threads, one 128x128 output tile, two CTAs per SM):
 //   warp 0   : TMA producer.  Per K-block of 32 rows: four 2-D tiled bulk-tensor loads of
-//              [32 rows x 32 floats] for each operand, 128-byte swizzle, completing on an mbarrier.
+//              [32 rows x 32 floats] for each operand (128-byte swizzle with 32-byte atoms), completing
+//              on an mbarrier.
 //   warp 1   : allocates 128 tensor-memory columns, then one lane issues tcgen05.mma kind::tf32
 //              (M=128, N=128, K=8 per instruction, both operands MN-major from shared memory) and
 //              commits each stage back to the producer and the finished tile to the epilogue.
@@ -32,7 +33,7 @@ namespace {
 
 constexpr int BM = 128, BN = 128, BK = 32;
 constexpr int kStages = 2;
-constexpr int kAtomFloats = 32;                       // 128-byte swizzle atom = 32 floats along M or N
+constexpr int kAtomFloats = 32;                       // swizzle atom = 32 floats (128 bytes) along M or N
 constexpr int kRegionBytes = BK * 128;                // one [BK x 32 floats] box
 constexpr int kAStageBytes = (BM / kAtomFloats) * kRegionBytes;   // 16 KB
 constexpr int kBStageBytes = (BN / kAtomFloats) * kRegionBytes;   // 16 KB
@@ -52,6 +53,7 @@ struct Params {
     float* grad_out;
     const MgwHyper* hyper;
     int* status;
+    float* debug;              // optional dump of stage 0 and raw accumulators of tile (0,0); null in production
     int M, N, K;
     int mode, pg, first_step;
     float scale;
@@ -89,15 +91,18 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
         ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
 }
 
-// Shared-memory matrix descriptor: MN-major operand, 128-byte swizzle.  `lbo` = bytes between
-// consecutive 32-float atoms along M/N, `sbo` = bytes between consecutive 8-row K atoms.
+// Shared-memory matrix descriptor for an MN-major 32-bit operand.  The only shared-memory layout the
+// tensor cores accept for that case is the 128-byte swizzle with 32-byte granularity: an atom is
+// 32 floats along M/N by 4 rows of K (512 bytes), 32-byte chunks of a row are permuted by the row
+// index mod 4.  `lbo` = bytes between consecutive atoms along M/N, `sbo` = bytes between consecutive
+// 4-row atoms along K.  The bulk-tensor loads use the matching swizzle mode.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
     uint64_t d = 0;
     d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
     d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
     d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
     d |= 1ull << 46;                 // descriptor version for this architecture
-    d |= 2ull << 61;                 // 128-byte swizzle
+    d |= 1ull << 61;                 // 128-byte swizzle, 32-byte base
     return d;
 }
 
@@ -213,8 +218,8 @@ wgrad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
                 const uint32_t b_addr = a_addr + kAStageBytes;
 #pragma unroll
                 for (int kk = 0; kk < BK / 8; ++kk) {
-                    const uint64_t adesc = make_smem_desc(a_addr + kk * 1024, kRegionBytes, 1024);
-                    const uint64_t bdesc = make_smem_desc(b_addr + kk * 1024, kRegionBytes, 1024);
+                    const uint64_t adesc = make_smem_desc(a_addr + kk * 1024, kRegionBytes, 512);
+                    const uint64_t bdesc = make_smem_desc(b_addr + kk * 1024, kRegionBytes, 512);
                     umma_tf32(tmem_base, adesc, bdesc, idesc, (kb > 0 || kk > 0) ? 1u : 0u);
                 }
                 umma_commit(&empty[s]);          // the stage may be refilled once these MMAs have read it
@@ -230,6 +235,14 @@ wgrad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         MgwHyper h;
         if (p.mode & WG_MODE_SGD) h = p.hyper[p.pg];
+        if (p.debug != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
+            if (et == 0) { p.debug[0] = __uint_as_float(tmem_base); p.debug[1] = (float)num_kb; }
+            const float* st = reinterpret_cast<const float*>(stages);
+            for (int i = et; i < kStageBytes / 4; i += 128) p.debug[16 + i] = st[i];
+            float v[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16), v);
+            for (int j = 0; j < 8; ++j) p.debug[16 + kStageBytes / 4 + (q * 32 + lane) * 8 + j] = v[j];
+        }
         for (int sc = 0; sc < BN / kSlabCols; ++sc) {
             if (ok && !*failed) {
                 float v[32];
@@ -330,7 +343,7 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// [K rows, inner floats] row-major operand -> boxes of [BK rows x 32 floats], 128-byte swizzle.
+// [K rows, inner floats] row-major operand -> boxes of [BK rows x 32 floats], 128-byte swizzle with 32-byte atoms.
 bool make_map(CUtensorMap* map, const float* base, int K, int inner) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return false;
@@ -339,7 +352,7 @@ bool make_map(CUtensorMap* map, const float* base, int K, int inner) {
     cuuint32_t box[2] = {(cuuint32_t)kAtomFloats, (cuuint32_t)BK};
     cuuint32_t elem[2] = {1, 1};
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(base), dims, strides, box, elem,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
@@ -355,10 +368,12 @@ int mgw_wgrad_gemm_supported(const void* dy, const void* x, int M, int N, int K)
     return 1;
 }
 
+// `debug` (may be null): >= 16 + 8192 + 1024 floats that receive tile (0,0)'s first operand stage and raw
+// accumulator columns, for bring-up.
 // dy: [K, M], x: [K, N] row-major fp32.  mode bit 1: grad_out[M, N] = scale * dy^T x;
 // mode bit 2: momentum-SGD on (weight, mom) with hyper[pg].  status: one device-visible int (0 = ok).
-int mgw_wgrad_gemm(const float* dy, const float* x, int M, int N, int K, float scale, int mode, float* grad_out, float* weight,
-                   float* mom, const MgwHyper* hyper, int pg, int first_step, int* status, void* stream) {
+int mgw_wgrad_gemm_debug(const float* dy, const float* x, int M, int N, int K, float scale, int mode, float* grad_out, float* weight,
+                         float* mom, const MgwHyper* hyper, int pg, int first_step, int* status, float* debug, void* stream) {
     if (!mgw_wgrad_gemm_supported(dy, x, M, N, K)) return MGW_ERR_ARG;
     if ((mode & WG_MODE_STORE) && grad_out == nullptr) return MGW_ERR_ARG;
     if ((mode & WG_MODE_SGD) && (weight == nullptr || hyper == nullptr)) return MGW_ERR_ARG;
@@ -374,12 +389,17 @@ int mgw_wgrad_gemm(const float* dy, const float* x, int M, int N, int K, float s
         configured = true;
     }
     Params p;
-    p.weight = weight; p.mom = mom; p.grad_out = grad_out; p.hyper = hyper; p.status = status;
+    p.weight = weight; p.mom = mom; p.grad_out = grad_out; p.hyper = hyper; p.status = status; p.debug = debug;
     p.M = M; p.N = N; p.K = K; p.mode = mode; p.pg = pg; p.first_step = first_step; p.scale = scale;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     wgrad_gemm_kernel<<<grid, 192, kSmemBytes, (cudaStream_t)stream>>>(map_a, map_b, p);
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
+}
+
+int mgw_wgrad_gemm(const float* dy, const float* x, int M, int N, int K, float scale, int mode, float* grad_out, float* weight,
+                   float* mom, const MgwHyper* hyper, int pg, int first_step, int* status, void* stream) {
+    return mgw_wgrad_gemm_debug(dy, x, M, N, K, scale, mode, grad_out, weight, mom, hyper, pg, first_step, status, nullptr, stream);
 }
 
 // flags: every rank's [n_ctas][MGW_MAX_RANKS] flag rows of this collective; epoch: local [n_ctas] counters.

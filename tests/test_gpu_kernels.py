@@ -234,8 +234,9 @@ def test_fused_lstm_matches_cudnn_lstm():
     x = torch.randn(T, B, I, device='cuda')
     hx = (torch.randn(2, B, H, device='cuda'), torch.randn(2, B, H, device='cuda'))
     x1, x2 = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
-    prev = torch.backends.cuda.matmul.allow_tf32
-    torch.backends.cuda.matmul.allow_tf32 = False
+    prev, prev_cudnn = torch.backends.cuda.matmul.allow_tf32, torch.backends.cudnn.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False      # fp32 GEMMs on both sides (cuDNN's LSTM obeys the cudnn flag)
+    torch.backends.cudnn.allow_tf32 = False
     try:
         y1, (h1, c1) = ref(x1, hx)
         y2, (h2, c2) = mine(x2, hx)
@@ -247,6 +248,7 @@ def test_fused_lstm_matches_cudnn_lstm():
         (y2 * w).sum().backward()
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev
+        torch.backends.cudnn.allow_tf32 = prev_cudnn
     torch.testing.assert_close(x2.grad, x1.grad, rtol=1e-3, atol=1e-4)
     for (n, p1), p2 in zip(ref.named_parameters(), mine.parameters()):
         torch.testing.assert_close(p2.grad, p1.grad, rtol=1e-3, atol=1e-4, msg=lambda m: '%s: %s' % (n, m))

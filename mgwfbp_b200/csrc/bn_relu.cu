@@ -4,13 +4,14 @@
 //
 // Forward = two streaming passes instead of cuDNN BatchNorm + add + ReLU (two extra passes over the
 // activation):
-//   bn_stats_kernel      : per-channel sum / sum of squares, one deterministic partial per row split; the
-//                          block that finishes last for a channel tile combines the partials in double,
-//                          saves mean / inv-std and updates the running statistics (no extra launch)
-//   bn_apply_kernel      : y = relu(x * scale + shift (+ residual))
+//   bn_stats_kernel        : per-channel sum / sum of squares, one deterministic partial per row split
+//   bn_fwd_finalize_kernel : (tiny) combines the partials in double, saves mean / inv-std, updates the
+//                            running statistics and num_batches_tracked
+//   bn_apply_kernel        : y = relu(x * scale + shift (+ residual))
 // Backward:
-//   bn_bwd_reduce_kernel : dz = dy * relu'(.); partial sums of dz and dz * xhat; last block -> dgamma, dbeta
-//   bn_bwd_apply_kernel  : dx = scale * (dz - (dbeta + xhat * dgamma) / M)
+//   bn_bwd_reduce_kernel   : dz = dy * relu'(.); partial sums of dz and dz * xhat
+//   bn_bwd_finalize_kernel : (tiny) dgamma, dbeta
+//   bn_bwd_apply_kernel    : dx = scale * (dz - (dbeta + xhat * dgamma) / M)
 // With a residual input dz is materialised (it is the residual's gradient) and the ReLU mask is read
 // from the saved output; without one neither y nor dz is touched: the mask is recomputed from x, so
 // the backward pass is 4 reads + 1 write of the activation instead of 5 + 2.
@@ -100,76 +101,10 @@ __device__ __forceinline__ void block_reduce_rows(float (&a)[VEC], float (&b)[VE
     __syncthreads();
 }
 
-// The block that finishes last for its channel tile (ticket counter) combines all row-split partials of
-// that tile: every thread sums a strided subset in double, a shared-memory tree adds the TY subsets
-// in a fixed order.  Result valid in threads with ty == 0.  Returns false in all other blocks.
-template <int VEC>
-__device__ __forceinline__ bool last_block_combine(float* __restrict__ partials, int* __restrict__ counters, int C, int c0, bool active,
-                                                   int tx, int ty, int TX, int TY, void* smem_raw, double (&a)[VEC], double (&b)[VEC]) {
-    __shared__ int s_last;
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) s_last = (atomicAdd(&counters[blockIdx.x], 1) == (int)gridDim.y - 1);
-    __syncthreads();
-    if (!s_last) return false;
-    __threadfence();
-    double* sa = reinterpret_cast<double*>(smem_raw);
-    double* sb = sa + kThreads * VEC;
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) a[k] = b[k] = 0.0;
-    if (active) {
-        for (int sp = ty; sp < (int)gridDim.y; sp += TY) {
-            const float* ps = partials + (size_t)sp * 2 * C;
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                if (c0 + k < C) {
-                    a[k] += (double)__ldcg(ps + c0 + k);
-                    b[k] += (double)__ldcg(ps + C + c0 + k);
-                }
-            }
-        }
-    }
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-        sa[(ty * TX + tx) * VEC + k] = a[k];
-        sb[(ty * TX + tx) * VEC + k] = b[k];
-    }
-    __syncthreads();
-    if (ty == 0) {
-#pragma unroll
-        for (int k = 0; k < VEC; ++k) {
-            double ra = 0.0, rb = 0.0;
-            for (int r = 0; r < TY; ++r) {
-                ra += sa[(r * TX + tx) * VEC + k];
-                rb += sb[(r * TX + tx) * VEC + k];
-            }
-            a[k] = ra;
-            b[k] = rb;
-        }
-    }
-    if (threadIdx.x == 0) counters[blockIdx.x] = 0;        // ready for the next launch on this stream
-    return true;
-}
-
-template <int VEC>
-__device__ __forceinline__ void write_partials(float* __restrict__ partials, int C, int c0, const float (&s)[VEC], const float (&q)[VEC]) {
-    float* ps = partials + (size_t)blockIdx.y * 2 * C;
-#pragma unroll
-    for (int k = 0; k < VEC; ++k) {
-        if (c0 + k < C) {
-            ps[c0 + k] = s[k];
-            ps[C + c0 + k] = q[k];
-        }
-    }
-}
-
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
-bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int rows_per_split, float* __restrict__ partials,
-                int* __restrict__ counters, float* running_mean, float* running_var, long long* num_batches_tracked,
-                float momentum, float eps, float* __restrict__ save_mean, float* __restrict__ save_invstd) {
-    extern __shared__ double smem_d[];
-    float* smem = reinterpret_cast<float*>(smem_d);
+bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int rows_per_split, float* __restrict__ partials) {
+    extern __shared__ float smem[];
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int c0 = (blockIdx.x * TX + tx) * VEC;
@@ -180,23 +115,7 @@ bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int row
     const long long r0 = (long long)blockIdx.y * rows_per_split;
     const long long r1 = min(M, r0 + rows_per_split);
     if (active) {
-        long long r = r0 + ty;
-        for (; r + 3LL * TY < r1; r += 4LL * TY) {            // four independent loads in flight per thread
-            float v0[VEC], v1[VEC], v2[VEC], v3[VEC];
-            load_vec<VEC>(x + r * C + c0, v0);
-            load_vec<VEC>(x + (r + TY) * C + c0, v1);
-            load_vec<VEC>(x + (r + 2LL * TY) * C + c0, v2);
-            load_vec<VEC>(x + (r + 3LL * TY) * C + c0, v3);
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                s[k] += (v0[k] + v1[k]) + (v2[k] + v3[k]);
-                q[k] = fmaf(v0[k], v0[k], q[k]);
-                q[k] = fmaf(v1[k], v1[k], q[k]);
-                q[k] = fmaf(v2[k], v2[k], q[k]);
-                q[k] = fmaf(v3[k], v3[k], q[k]);
-            }
-        }
-        for (; r < r1; r += TY) {
+        for (long long r = r0 + ty; r < r1; r += TY) {
             float v[VEC];
             load_vec<VEC>(x + r * C + c0, v);
 #pragma unroll
@@ -207,28 +126,76 @@ bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int row
         }
     }
     block_reduce_rows<VEC>(s, q, smem, tx, ty, TX, TY);
-    if (ty == 0 && active) write_partials<VEC>(partials, C, c0, s, q);
-    double sum[VEC], sq[VEC];
-    if (!last_block_combine<VEC>(partials, counters, C, c0, active, tx, ty, TX, TY, smem_d, sum, sq)) return;
     if (ty == 0 && active) {
+        float* ps = partials + (size_t)blockIdx.y * 2 * C;
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
-            const int c = c0 + k;
-            if (c < C) {
-                const double mean = sum[k] / (double)M;
-                double var = sq[k] / (double)M - mean * mean;
-                if (var < 0.0) var = 0.0;
-                save_mean[c] = (float)mean;
-                save_invstd[c] = (float)(1.0 / sqrt(var + (double)eps));
-                if (running_mean) {
-                    const double unbiased = M > 1 ? var * (double)M / (double)(M - 1) : var;
-                    running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * (float)mean;
-                    running_var[c] = (1.f - momentum) * running_var[c] + momentum * (float)unbiased;
-                }
+            if (c0 + k < C) {
+                ps[c0 + k] = s[k];
+                ps[C + c0 + k] = q[k];
             }
         }
     }
-    if (blockIdx.x == 0 && threadIdx.x == 0 && num_batches_tracked) *num_batches_tracked += 1;
+}
+
+// Sum the per-split partials of 32 channels per block (32-way split over the partial rows, combined
+// in double in a fixed order).  out_a / out_b receive the two totals of every channel.
+__device__ __forceinline__ void finalize_sums(const float* __restrict__ partials, int n_splits, int C, double& a, double& b,
+                                              double (*sm)[32][32]) {
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    double ra = 0.0, rb = 0.0;
+    if (c < C) {
+        for (int s = threadIdx.y; s < n_splits; s += 32) {
+            const float* ps = partials + (size_t)s * 2 * C;
+            ra += (double)ps[c];
+            rb += (double)ps[C + c];
+        }
+    }
+    sm[0][threadIdx.y][threadIdx.x] = ra;
+    sm[1][threadIdx.y][threadIdx.x] = rb;
+    __syncthreads();
+    a = b = 0.0;
+    if (threadIdx.y == 0) {
+        for (int r = 0; r < 32; ++r) {
+            a += sm[0][r][threadIdx.x];
+            b += sm[1][r][threadIdx.x];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(1024)
+bn_fwd_finalize_kernel(const float* __restrict__ partials, int n_splits, long long M, int C, float* running_mean, float* running_var,
+                       long long* num_batches_tracked, float momentum, float eps, float* __restrict__ save_mean,
+                       float* __restrict__ save_invstd) {
+    __shared__ double sm[2][32][32];
+    double sum, sq;
+    finalize_sums(partials, n_splits, C, sum, sq, sm);
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    if (threadIdx.y == 0 && c < C) {
+        const double mean = sum / (double)M;
+        double var = sq / (double)M - mean * mean;
+        if (var < 0.0) var = 0.0;
+        save_mean[c] = (float)mean;
+        save_invstd[c] = (float)(1.0 / sqrt(var + (double)eps));
+        if (running_mean) {
+            const double unbiased = M > 1 ? var * (double)M / (double)(M - 1) : var;
+            running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * (float)mean;
+            running_var[c] = (1.f - momentum) * running_var[c] + momentum * (float)unbiased;
+        }
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0 && threadIdx.y == 0 && num_batches_tracked) *num_batches_tracked += 1;
+}
+
+__global__ void __launch_bounds__(1024)
+bn_bwd_finalize_kernel(const float* __restrict__ partials, int n_splits, int C, float* __restrict__ dgamma, float* __restrict__ dbeta) {
+    __shared__ double sm[2][32][32];
+    double a, b;
+    finalize_sums(partials, n_splits, C, a, b, sm);
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    if (threadIdx.y == 0 && c < C) {
+        dbeta[c] = (float)a;
+        dgamma[c] = (float)b;
+    }
 }
 
 template <int VEC>
@@ -309,9 +276,8 @@ __global__ void __launch_bounds__(kThreads)
 bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, const float* __restrict__ x, float* __restrict__ dz,
                      long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                      const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
-                     float* __restrict__ partials, int* __restrict__ counters, float* __restrict__ dgamma, float* __restrict__ dbeta) {
-    extern __shared__ double smem_d[];
-    float* smem = reinterpret_cast<float*>(smem_d);
+                     float* __restrict__ partials) {
+    extern __shared__ float smem[];
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int c0 = (blockIdx.x * TX + tx) * VEC;
@@ -324,7 +290,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, 
     const long long r1 = min(M, r0 + rows_per_split);
     if (active) {
         long long r = r0 + ty;
-        for (; r + TY < r1; r += 2LL * TY) {                  // two rows per trip: four to six loads in flight
+        for (; r + TY < r1; r += 2LL * TY) {                  // two rows per trip: more loads in flight
             float g0[VEC], g1[VEC], x0[VEC], x1[VEC];
             load_vec<VEC>(dy + r * C + c0, g0);
             load_vec<VEC>(dy + (r + TY) * C + c0, g1);
@@ -357,15 +323,13 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, 
         }
     }
     block_reduce_rows<VEC>(s, q, smem, tx, ty, TX, TY);
-    if (ty == 0 && active) write_partials<VEC>(partials, C, c0, s, q);
-    double a[VEC], b[VEC];
-    if (!last_block_combine<VEC>(partials, counters, C, c0, active, tx, ty, TX, TY, smem_d, a, b)) return;
     if (ty == 0 && active) {
+        float* ps = partials + (size_t)blockIdx.y * 2 * C;
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
             if (c0 + k < C) {
-                dbeta[c0 + k] = (float)a[k];
-                dgamma[c0 + k] = (float)b[k];
+                ps[c0 + k] = s[k];
+                ps[C + c0 + k] = q[k];
             }
         }
     }
@@ -417,28 +381,26 @@ size_t mgw_bn_partials_floats(long long M, int C) {
     return (size_t)t.grid_y * 2 * (size_t)C;
 }
 
-// Number of ints in the `counters` array (zero before the first call; kernels leave it zero again).
-size_t mgw_bn_counter_ints(void) { return 4096; }
-
 int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M, int C, const float* gamma, const float* beta,
                     float* running_mean, float* running_var, long long* num_batches_tracked, float momentum, float eps,
-                    int relu, float* save_mean, float* save_invstd, float* partials, int* counters, void* stream) {
-    if (x == nullptr || y == nullptr || M <= 0 || C <= 0 || save_mean == nullptr || save_invstd == nullptr || partials == nullptr ||
-        counters == nullptr)
+                    int relu, float* save_mean, float* save_invstd, float* partials, void* stream) {
+    if (x == nullptr || y == nullptr || M <= 0 || C <= 0 || save_mean == nullptr || save_invstd == nullptr || partials == nullptr)
         return MGW_ERR_ARG;
     const int vec = (C % 4 == 0) ? 4 : 1;
     const Tiling t = make_tiling(M, C, vec);
-    if (t.grid_x > 4096) return MGW_ERR_TOO_LARGE;
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_red = sizeof(double) * 2 * kThreads * vec;
+    const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
+    const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     if (vec == 4) {
-        bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials, counters, running_mean, running_var,
-                                                        num_batches_tracked, momentum, eps, save_mean, save_invstd);
+        bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
+        bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
+                                                        momentum, eps, save_mean, save_invstd);
         bn_apply_kernel<4><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd);
     } else {
-        bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials, counters, running_mean, running_var,
-                                                        num_batches_tracked, momentum, eps, save_mean, save_invstd);
+        bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
+        bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
+                                                        momentum, eps, save_mean, save_invstd);
         bn_apply_kernel<1><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
@@ -451,23 +413,25 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
 // values), which saves one read and one write of the activation.
 int mgw_bn_relu_bwd(const float* dy, const float* y, const float* x, float* dz, float* dx, long long M, int C, const float* gamma,
                     const float* beta, const float* save_mean, const float* save_invstd, int relu, float* dgamma, float* dbeta,
-                    float* partials, int* counters, void* stream) {
-    if (dy == nullptr || x == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr || counters == nullptr) return MGW_ERR_ARG;
+                    float* partials, void* stream) {
+    if (dy == nullptr || x == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
     if (dgamma == nullptr || dbeta == nullptr || save_mean == nullptr || save_invstd == nullptr) return MGW_ERR_ARG;
     const int mask1 = !relu ? 0 : (y != nullptr ? 1 : 2);          // mask used by the reduce pass
     const int mask2 = dz != nullptr ? 0 : mask1;                   // apply pass: dz already carries the mask
     const float* gsrc = dz != nullptr ? dz : dy;
     const int vec = (C % 4 == 0) ? 4 : 1;
     const Tiling t = make_tiling(M, C, vec);
-    if (t.grid_x > 4096) return MGW_ERR_TOO_LARGE;
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_red = sizeof(double) * 2 * kThreads * vec;
+    const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
+    const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     if (vec == 4) {
-        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, counters, dgamma, dbeta);
+        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials);
+        bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
         bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(gsrc, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta);
     } else {
-        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, counters, dgamma, dbeta);
+        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials);
+        bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
         bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(gsrc, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta);
     }
     MGW_CUDA_CHECK(cudaGetLastError());

@@ -291,9 +291,27 @@ wgrad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
 }
 
 // ---- all-gather of K-row blocks over NVLink -----------------------------------------------------------
-// Every rank contributes `rows` x `cols` floats (its block lives at offset rank*rows*cols of its own
-// symmetric buffer); afterwards every rank holds all W blocks in rank order.  Pull design: signal
-// "my block is in place", wait for each peer (bounded), copy the peer's block with 16-byte loads.
+// Every rank contributes `block_floats` floats (its block lives at offset rank*block_floats of its own
+// symmetric buffer); afterwards every rank holds all W blocks in rank order.  Pull design with two
+// bounded barriers per CTA: "my block is in place" before the copy, "I am done reading" after it, so a
+// rank may overwrite its block for the next step as soon as its own kernel has finished.
+__device__ __forceinline__ bool gather_barrier(uint32_t* const* flags, int phase, int rank, int world, uint32_t e, int* status,
+                                               unsigned long long timeout_ns, int* failed) {
+    __syncthreads();
+    if (threadIdx.x < world) {
+        __threadfence_system();
+        const size_t slot = ((size_t)phase * MGW_MAX_CTAS + blockIdx.x) * MGW_MAX_RANKS;
+        mgw_st_release_sys(flags[threadIdx.x] + slot + rank, e);
+        uint32_t seen = 0;
+        if (!mgw_wait_flag(flags[rank] + slot + threadIdx.x, e, timeout_ns, &seen)) {
+            mgw_report(status, MGW_STATUS_TIMEOUT, threadIdx.x, (int)e, (int)seen);
+            *failed = 1;
+        }
+    }
+    __syncthreads();
+    return *failed == 0;
+}
+
 __global__ void __launch_bounds__(512)
 allgather_rows_kernel(float* const* bufs, uint32_t* const* flags, uint32_t* epoch, int* status, int rank, int world,
                       long long block_floats, unsigned long long timeout_ns) {
@@ -301,18 +319,7 @@ allgather_rows_kernel(float* const* bufs, uint32_t* const* flags, uint32_t* epoc
     const int b = blockIdx.x;
     const uint32_t e = epoch[b] + 1u;
     if (threadIdx.x == 0) failed = 0;
-    __syncthreads();
-    if (threadIdx.x < world) {
-        __threadfence_system();
-        mgw_st_release_sys(flags[threadIdx.x] + (size_t)b * MGW_MAX_RANKS + rank, e);
-        uint32_t seen = 0;
-        if (!mgw_wait_flag(flags[rank] + (size_t)b * MGW_MAX_RANKS + threadIdx.x, e, timeout_ns, &seen)) {
-            mgw_report(status, MGW_STATUS_TIMEOUT, threadIdx.x, (int)e, (int)seen);
-            failed = 1;
-        }
-    }
-    __syncthreads();
-    if (!failed) {
+    if (gather_barrier(flags, 0, rank, world, e, status, timeout_ns, &failed)) {
         const long long nvec = block_floats / 4;
         const long long per = (nvec + gridDim.x - 1) / gridDim.x;
         const long long v0 = (long long)b * per, v1 = min(nvec, v0 + per);
@@ -323,6 +330,7 @@ allgather_rows_kernel(float* const* bufs, uint32_t* const* flags, uint32_t* epoc
             float4* dst = reinterpret_cast<float4*>(bufs[rank] + (size_t)q * block_floats);
             for (long long v = v0 + threadIdx.x; v < v1; v += blockDim.x) dst[v] = mgw_ld_peer(src + v);
         }
+        (void)gather_barrier(flags, 1, rank, world, e, status, timeout_ns, &failed);
     }
     __syncthreads();
     if (threadIdx.x == 0) epoch[b] = e;
@@ -402,7 +410,7 @@ int mgw_wgrad_gemm(const float* dy, const float* x, int M, int N, int K, float s
     return mgw_wgrad_gemm_debug(dy, x, M, N, K, scale, mode, grad_out, weight, mom, hyper, pg, first_step, status, nullptr, stream);
 }
 
-// flags: every rank's [n_ctas][MGW_MAX_RANKS] flag rows of this collective; epoch: local [n_ctas] counters.
+// flags: every rank's flag block (same layout and size as mgw_flag_block_bytes()); epoch: local [MGW_MAX_CTAS] counters.
 int mgw_allgather_rows(float* const* bufs_dev, uint32_t* const* flags_dev, uint32_t* epoch, int* status, int rank, int world,
                        long long block_floats, int n_ctas, unsigned long long timeout_ns, void* stream) {
     if (bufs_dev == nullptr || flags_dev == nullptr || epoch == nullptr) return MGW_ERR_ARG;

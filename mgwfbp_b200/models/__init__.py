@@ -102,6 +102,10 @@ def create_net(num_classes, dnn='resnet20', fuse=False, channels_last=False, **k
     if fuse and dnn not in ('lstm',):
         from .fuse import fuse_model
         net = fuse_model(net)
+    if fuse:
+        # large fully-connected layers: exchange activations instead of all-reducing the weight gradient
+        from ..ops.wgrad import convert_large_linears
+        convert_large_linears(net)
     if channels_last:
         import torch
         net = net.to(memory_format=torch.channels_last)

@@ -43,25 +43,11 @@ def _declare(lib) -> None:
     lib.mgw_bn_partials_floats.argtypes = [C.c_longlong, C.c_int]
     lib.mgw_bn_relu_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_void_p,
-                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+                                    C.c_void_p, C.c_void_p, C.c_void_p]
     lib.mgw_bn_relu_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
-                                    C.c_void_p, C.c_void_p, C.c_void_p]
-    lib.mgw_bn_counter_ints.restype = C.c_size_t
+                                    C.c_void_p, C.c_void_p]
     _declared = True
-
-
-_counter_cache = {}
-
-
-def _counters(lib, device) -> torch.Tensor:
-    """Ticket counters of the last-block reductions: zero-initialised once per (device, stream); the
-    kernels leave them at zero, and launches on one stream are ordered, so they can be shared."""
-    key = (device, torch.cuda.current_stream().cuda_stream)
-    t = _counter_cache.get(key)
-    if t is None:
-        t = _counter_cache[key] = torch.zeros(lib.mgw_bn_counter_ints(), dtype=torch.int32, device=device)
-    return t
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -82,8 +68,8 @@ class _BNReLU(torch.autograd.Function):
         _lib.check(lib.mgw_bn_relu_fwd(x.data_ptr(), _ptr(residual), y.data_ptr(), M, Cc, _ptr(weight), _ptr(bias),
                                        _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
                                        float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
-                                       partials.data_ptr(), _counters(lib, x.device).data_ptr(), s), 'bn_relu_fwd')
-        counters.bump('bn_relu_fwd', 2)
+                                       partials.data_ptr(), s), 'bn_relu_fwd')
+        counters.bump('bn_relu_fwd', 3)
         # the output is only needed to rebuild the ReLU mask when a residual was added
         ctx.save_for_backward(x, y if (relu and residual is not None) else None, weight, bias, mean, invstd)
         ctx.relu, ctx.has_residual, ctx.rows = bool(relu), residual is not None, (M, Cc)
@@ -105,9 +91,8 @@ class _BNReLU(torch.autograd.Function):
         s = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
                                        _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
-                                       dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(),
-                                       _counters(lib, x.device).data_ptr(), s), 'bn_relu_bwd')
-        counters.bump('bn_relu_bwd', 2)
+                                       dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), s), 'bn_relu_bwd')
+        counters.bump('bn_relu_bwd', 3)
         need = ctx.needs_input_grad
         return (dx if need[0] else None, dgamma if (weight is not None and need[1]) else None,
                 dbeta if need[2] else None, None, None, None, dz if (ctx.has_residual and need[6]) else None,

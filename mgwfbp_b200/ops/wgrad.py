@@ -94,3 +94,64 @@ def wgrad_sgd_(dy: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, momentum
                                   None if momentum_buffer is None else momentum_buffer.data_ptr(), hyper_ptr, pg,
                                   int(first_step), _status(dy.device).data_ptr(), s), 'wgrad_gemm(sgd)')
     counters.bump('wgrad_gemm_sm100')
+
+
+# --------------------------------------------------------------------------------------------------
+# Data-parallel linear layer whose weight gradient is never all-reduced
+# --------------------------------------------------------------------------------------------------
+class _GatheredLinearFn(torch.autograd.Function):
+    """``y = x W^T + b`` whose backward hands ``(dy, x)`` to the communicator instead of forming ``dW``."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, module):
+        ctx.save_for_backward(x, weight)
+        ctx.module = module
+        ctx.has_bias = bias is not None
+        return torch.nn.functional.linear(x, weight, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1])
+        dx = (dy2 @ weight).reshape(x.shape) if ctx.needs_input_grad[0] else None
+        db = dy2.sum(0) if ctx.has_bias else None
+        ctx.module._exchange(ctx.module, dy2.contiguous(), x2.contiguous())     # gather + GEMM + update on the side stream
+        return dx, None, db, None
+
+
+class GatheredWgradLinear(torch.nn.Linear):
+    """``nn.Linear`` (same parameters and ``state_dict`` keys) for large layers fed by small batches.
+
+    Under a fused data-parallel optimizer the weight takes no part in the gradient all-reduce:
+    during backward every rank publishes its ``dy`` and ``x`` rows, pulls the other ranks' rows over
+    NVLink, and applies ``(1/W) * dY_all^T X_all`` to its weights with the tensor-core GEMM whose
+    epilogue is the SGD update.  Traffic is ``W*B*(in+out)`` floats instead of ``in*out``.  Without
+    such an optimizer (single process, CPU, other optimizers) it behaves exactly like ``nn.Linear``.
+    """
+    batch_rows_hint: Optional[int] = None      # rows of x per step and rank, set by the trainer
+
+    def gathered_is_profitable(self, world: int) -> bool:
+        rows = self.batch_rows_hint
+        if rows is None or world < 2:
+            return False
+        m, n = self.out_features, self.in_features
+        return (m % 4 == 0 and n % 4 == 0 and world * rows * (m + n) * 2 <= m * n)
+
+    def forward(self, x):
+        exchange = getattr(self, '_exchange', None)
+        if exchange is not None and self.training and torch.is_grad_enabled() and x.is_cuda:
+            return _GatheredLinearFn.apply(x, self.weight, self.bias, self)
+        return super().forward(x)
+
+
+def convert_large_linears(net: torch.nn.Module, min_params: int = 8 * 1024 * 1024) -> int:
+    """Swap every ``nn.Linear`` with at least ``min_params`` weights for :class:`GatheredWgradLinear`
+    (in place: parameters, buffers and names are untouched).  Returns how many were converted."""
+    n = 0
+    for m in net.modules():
+        if type(m) is torch.nn.Linear and m.in_features * m.out_features >= min_params:
+            m.__class__ = GatheredWgradLinear
+            m.weight._mgw_gathered = m
+            n += 1
+    return n

@@ -114,6 +114,15 @@ class TorchSymmHeap:
         self.base = 0
 
 
+def _wrap_device_memory(ptr: int, n_floats: int, device: torch.device) -> torch.Tensor:
+    """A float32 tensor view of raw device memory that this module owns (symmetric heap)."""
+    class _Mem:
+        pass
+    holder = _Mem()
+    holder.__cuda_array_interface__ = {'shape': (int(n_floats),), 'typestr': '<f4', 'data': (int(ptr), False), 'version': 2}
+    return torch.as_tensor(holder, device=device)
+
+
 def make_heap(lib, nbytes: int):
     kind = os.environ.get('MGWFBP_HEAP', 'ipc').lower()
     if kind == 'torch':
@@ -144,9 +153,12 @@ class NvlComm(Communicator):
         self.n_threads = _env_int('MGWFBP_COMM_THREADS', 512)
         # control block: flag rows + per-CTA launch counters, in a heap of its own
         self._flag_bytes = int(self.lib.mgw_flag_block_bytes())
-        self._ctl = make_heap(self.lib, self._flag_bytes + 4 * _lib.MAX_CTAS + _ALIGN)
+        self._ctl = make_heap(self.lib, 2 * (self._flag_bytes + 4 * _lib.MAX_CTAS + _ALIGN))
         self._flag_off = self._ctl.alloc(self._flag_bytes)
         self._epoch_off = self._ctl.alloc(4 * _lib.MAX_CTAS)
+        self._gflag_off = self._ctl.alloc(self._flag_bytes)          # flag rows / counters of the row all-gather
+        self._gepoch_off = self._ctl.alloc(4 * _lib.MAX_CTAS)
+        self._gather_tables = None
         status = C.POINTER(C.c_int)()
         _lib.check(self.lib.mgw_host_status_alloc(8, C.byref(status)), 'status_alloc')
         self._status = status
@@ -299,6 +311,8 @@ class NvlComm(Communicator):
                 mode |= _lib.MODE_SUMSQ
         opt._nvl_mode = mode
         opt._nvl_held = []
+        if getattr(opt, '_external', None):
+            self._attach_external(opt)
         algos = {0: 0, 1: 0, 2: 0}
         for pl in plans:
             algos[pl.algo] += 1
@@ -368,6 +382,78 @@ class NvlComm(Communicator):
             torch.nn.utils.clip_grad_norm_([p for p in opt._requires_update], opt._norm_clip)
         opt._base_cls.step(opt)
         return loss
+
+    # ------------------------------------------------------------------ gathered weight gradients
+    def _attach_external(self, opt) -> None:
+        """Wire the layers whose weights are updated from gathered activations (opt._external)."""
+        opt._ext_state = {}
+        for name, p, module in opt._external:
+            mom, created = ensure_momentum_buffers(opt, [p])
+            opt._ext_state[id(module)] = dict(name=name, param=p, mom=mom[0], pg=param_group_index(opt, [p])[0],
+                                              first=created, bufs=None)
+            module._exchange = (lambda m, dy, x, _o=opt: self.exchange_external(_o, m, dy, x))
+
+    def _gather_buffers(self, st, rows: int, m: int, n: int):
+        """Symmetric [W*rows, m] and [W*rows, n] buffers of one layer (collective on first use)."""
+        if st['bufs'] is not None and st['bufs']['rows'] == rows:
+            return st['bufs']
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError('gathered weight-gradient buffers must exist before CUDA graph capture (run eager steps first)')
+        w = self._world
+        nbytes = 4 * w * rows * (m + n)
+        heap = make_heap(self.lib, nbytes + 2 * _ALIGN)
+        self._heaps.append(heap)
+        off_dy, off_x = heap.alloc(4 * w * rows * m), heap.alloc(4 * w * rows * n)
+
+        def ptr_table(off):
+            return torch.tensor([heap.peer_base[r] + off for r in range(w)], dtype=torch.int64, device=self.device)
+        flags = torch.tensor([self._ctl.peer_base[r] + self._gflag_off for r in range(w)], dtype=torch.int64, device=self.device)
+        st['bufs'] = dict(rows=rows, heap=heap, off_dy=off_dy, off_x=off_x, tab_dy=ptr_table(off_dy), tab_x=ptr_table(off_x),
+                          flags=flags, dy_all=heap.base + off_dy, x_all=heap.base + off_x)
+        return st['bufs']
+
+    def exchange_external(self, opt, module, dy: torch.Tensor, x: torch.Tensor) -> None:
+        """Called from the layer's backward: all-gather (dy, x) rows over NVLink, then one tensor-core
+        GEMM whose epilogue applies the averaged gradient to the layer's weight and momentum."""
+        from ...ops import wgrad
+        st = opt._ext_state[id(module)]
+        rows, m = dy.shape
+        n = x.shape[1]
+        w, r = self._world, self._rank
+        bufs = self._gather_buffers(st, rows, m, n)
+        lib = wgrad._lib_ready()
+        compute = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(compute)
+        self.stream.wait_event(ready)
+        if not opt._groups_pending and not torch.cuda.is_current_stream_capturing():
+            self._hyper[id(opt)].sync(opt.param_groups, self.stream)
+        s = self.stream.cuda_stream
+        status = C.cast(self._status, C.c_void_p).value
+        epoch = self._ctl.base + self._gepoch_off
+        with torch.cuda.stream(self.stream):
+            for src, base, cols, tab in ((dy, bufs['dy_all'], m, bufs['tab_dy']), (x, bufs['x_all'], n, bufs['tab_x'])):
+                block = rows * cols
+                dst = _wrap_device_memory(base + 4 * r * block, block, self.device)
+                dst.copy_(src.reshape(-1), non_blocking=True)
+                n_ctas = max(1, min(16, block // 16384))
+                _lib.check(lib.mgw_allgather_rows(tab.data_ptr(), bufs['flags'].data_ptr(), epoch, status, r, w, block, n_ctas,
+                                                  self.timeout_ns, s), 'allgather_rows')
+                counters.bump('allgather_rows')
+            dy_all = _wrap_device_memory(bufs['dy_all'], w * rows * m, self.device).view(w * rows, m)
+            x_all = _wrap_device_memory(bufs['x_all'], w * rows * n, self.device).view(w * rows, n)
+            grad_out = None
+            if settings.WRITE_BACK_GRADS:
+                p = st['param']
+                if p.grad is None or p.grad.shape != p.shape:
+                    p.grad = torch.empty_like(p)
+                grad_out = p.grad
+            wgrad.wgrad_sgd_(dy_all, x_all, st['param'].data, st['mom'], self._hyper[id(opt)].data_ptr(), st['pg'],
+                             scale=1.0 / w, first_step=bool(st['first']), grad_out=grad_out, stream=self.stream)
+        st['first'] = False
+        opt._nvl_held.append((dy, x))
+        opt._synchronized = False
+        self.launches += 3
 
     def sync_hyper(self, opt) -> None:
         """Upload ``opt``'s current learning rates etc. (call before replaying a captured step)."""

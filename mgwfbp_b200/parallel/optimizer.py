@@ -69,7 +69,7 @@ class _DistributedMixin:
         self._cost_model = cost_model
         self.train_epoch = 0
         self.train_iter = 0
-        self.local = False
+        self._local = False
         self._allreduce_timers: Dict[str, List[float]] = {}
         self._update_times: Dict[str, List[float]] = {}
         self._compression_timers: Dict[str, List[float]] = {}
@@ -106,6 +106,35 @@ class _DistributedMixin:
         want_fused = settings.FUSED_UPDATE if fused_update is None else bool(fused_update)
         self._fused_comm = bool(getattr(self._comm, 'fused', False))
         self._fused_update = bool(want_fused and self._fused_comm and self._base_is_sgd and norm_clip is None)
+
+        # Large linear layers fed by small batches exchange activations instead of weight gradients
+        # (mgwfbp_b200.ops.wgrad.GatheredWgradLinear); their weights leave the merge schedule.
+        self._external = []
+        if self._fused_update and self._world > 1 and settings.GATHERED_WGRAD:
+            for name, p in list(self._named_parameters.items()):
+                module = getattr(p, '_mgw_gathered', None)
+                if module is not None and module.gathered_is_profitable(self._world):
+                    self._external.append((name, p, module))
+            gone = {name for name, _, _ in self._external}
+            if gone:
+                self._named_parameters = {k: v for k, v in self._named_parameters.items() if k not in gone}
+                self._parameter_names = {v: k for k, v in self._named_parameters.items()}
+                keep = [i for i, k in enumerate(self._sequential_keys) if k not in gone]
+                if self._layerwise_times is not None:
+                    # the removed layer's backward time still elapses before the next gradient is ready
+                    tb = list(self._layerwise_times)
+                    for i, k in enumerate(self._sequential_keys):
+                        if k in gone:
+                            j = next((q for q in range(i - 1, -1, -1) if self._sequential_keys[q] not in gone),
+                                     next((q for q in range(i + 1, len(tb)) if self._sequential_keys[q] not in gone), None))
+                            if j is not None:
+                                tb[j] += tb[i]
+                    self._layerwise_times = [tb[i] for i in keep]
+                self._sequential_keys = [self._sequential_keys[i] for i in keep]
+                if self._seq_layernames is not None:
+                    self._seq_layernames = list(self._sequential_keys)
+                self._seq_index = {k: i for i, k in enumerate(self._sequential_keys)}
+                logger.info('weights updated through gathered activations (no gradient all-reduce): %s', sorted(gone))
 
         self._generate_merged_parameters()
 
@@ -340,6 +369,17 @@ class _DistributedMixin:
             self._comm.sync_hyper(self)
         elif getattr(self, '_fast_sgd', None) is not None:
             self._fast_sgd.sync_hyper(self)
+
+    @property
+    def local(self) -> bool:
+        return self._local
+
+    @local.setter
+    def local(self, value: bool) -> None:
+        if value and getattr(self, '_external', None):
+            raise RuntimeError('gradient accumulation (optimizer.local = True) cannot be combined with gathered '
+                               'weight-gradient layers; construct the model with MGWFBP_GATHERED_WGRAD=0')
+        self._local = bool(value)
 
     def _local_step(self, closure=None):
         fast = getattr(self, '_fast_sgd', None)

@@ -59,6 +59,10 @@ FUSE_MODULES = _env_flag('FUSE', True)
 # Keep convolutional models and their inputs in channels-last (NHWC) memory format on the GPU.
 CHANNELS_LAST = _env_flag('CHANNELS_LAST', True)
 
+# Large nn.Linear layers fed by small batches: exchange activations + output gradients between ranks and run the
+# tensor-core weight-gradient GEMM with the SGD epilogue instead of all-reducing the weight gradient.
+GATHERED_WGRAD = _env_flag('GATHERED_WGRAD', True)
+
 # After the fused kernels ran, leave the averaged gradient readable in ``p.grad``.
 WRITE_BACK_GRADS = _env_flag('WRITE_BACK_GRADS', True)
 

@@ -84,6 +84,10 @@ class DLTrainer:
             if data_dir is not None and dnn == 'lstman4':
                 self.data_prepare()
         self.lr = self.base_lr = lr
+        rows = self.batch_size * (self.num_steps if self.dnn == 'lstm' else 1)
+        for m in self.net.modules():
+            if hasattr(m, 'batch_rows_hint'):
+                m.batch_rows_hint = rows          # rows each rank feeds a linear layer per step
         if self.is_cuda:
             if self.ngpus > 1:
                 self.net = nn.DataParallel(self.net, device_ids=list(range(self.ngpus))).cuda()

@@ -87,6 +87,52 @@ def test_fused_data_parallel_equals_large_batch(policy, fused):
             assert torch.equal(a, b), 'replicas diverged'
 
 
+def _gathered_wgrad(rank, world):
+    """A large linear layer fed by a small batch: its weight is updated from gathered activations by
+    the tensor-core GEMM with the SGD epilogue and never enters the gradient all-reduce."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200.ops.wgrad import convert_large_linears, GatheredWgradLinear
+    torch.manual_seed(0)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    mk_net = lambda: torch.nn.Sequential(torch.nn.Linear(64, 2048), torch.nn.ReLU(), torch.nn.Linear(2048, 4096),
+                                         torch.nn.ReLU(), torch.nn.Linear(4096, 16)).cuda()
+    net, ref = mk_net(), mk_net()
+    assert convert_large_linears(net) == 1 and isinstance(net[2], GatheredWgradLinear)
+    net[2].batch_rows_hint = 8
+    hvd.broadcast_parameters(net.state_dict(), 0)
+    ref.load_state_dict(net.state_dict())
+    mk = lambda m: torch.optim.SGD(m.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
+    opt = hvd.DistributedOptimizer(mk(net), named_parameters=net.named_parameters(), threshold=0)
+    assert [n for n, _, _ in opt._external] == ['2.weight']
+    assert '2.weight' not in opt.merge_schedule.key_groupidx and len(opt.merge_schedule.groups) == 5
+    ropt = mk(ref)
+    g = torch.Generator().manual_seed(11)
+    for _ in range(4):
+        x = torch.randn(world * 8, 64, generator=g).cuda()
+        opt.zero_grad()
+        net(x[rank * 8:(rank + 1) * 8]).pow(2).mean().backward()
+        opt.step()
+        ropt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        ropt.step()
+    torch.cuda.synchronize()
+    opt.communicator.check_status()
+    from mgwfbp_b200.ops import wgrad
+    wgrad.check_status()
+    return {'dp': [p.detach().cpu() for p in net.parameters()], 'ref': [p.detach().cpu() for p in ref.parameters()],
+            'grad': net[2].weight.grad.detach().cpu(), 'ref_grad': ref[2].weight.grad.detach().cpu()}
+
+
+def test_gathered_wgrad_layer_matches_large_batch_sgd():
+    res = run_ranks(_gathered_wgrad, (), world=2)
+    # the GEMM reads its operands as TF32, the reference runs in fp32: compare at TF32 accuracy
+    for dp, ref in zip(res[0]['dp'], res[0]['ref']):
+        torch.testing.assert_close(dp, ref, rtol=5e-3, atol=2e-4)
+    torch.testing.assert_close(res[0]['grad'], res[0]['ref_grad'], rtol=2e-2, atol=1e-5)
+    for a, b in zip(res[0]['dp'], res[1]['dp']):
+        assert torch.equal(a, b), 'replicas diverged'
+
+
 def _clip_path(rank, world):
     import mgwfbp_b200 as hvd
     torch.manual_seed(0)
@@ -147,3 +193,41 @@ def test_missing_peer_is_reported_not_hung():
     res = run_ranks(_missing_peer, (), world=2)
     assert res[0]['err'] and 'gave up' in res[0]['err']
     assert res[0]['alive'] == 12.0 and res[1]['alive'] == 12.0
+
+
+def _nvls_allreduce(rank, world):
+    """NVSwitch multicast path (multimem.ld_reduce / multimem.st) on a heap from torch's symmetric memory.
+    Every rank reaches the final barrier whatever happens, so no rank leaves while peers still use the heap."""
+    os.environ['MGWFBP_HEAP'] = 'torch'
+    import mgwfbp_b200 as hvd
+    out = {'available': False, 'error': None, 'results': {}}
+    try:
+        from mgwfbp_b200.parallel.comm.nvl import NvlComm
+        comm = NvlComm.shared()
+        out['available'] = bool(comm.nvls_available)
+        if comm.nvls_available:
+            for numel in (4096, (1 << 20) + 4):
+                g = torch.Generator(device='cuda').manual_seed(77 * rank + 1)
+                x = torch.randn(numel, device='cuda', generator=g)
+                mine = x.clone()
+                comm.synchronize(comm.allreduce_async_(x, average=True, algo='nvls'))
+                torch.cuda.synchronize()
+                comm.check_status()
+                out['results'][numel] = (mine.cpu(), x.cpu())
+    except Exception as e:            # report instead of leaving early
+        out['error'] = '%s: %s' % (type(e).__name__, e)
+    hvd.barrier()
+    torch.cuda.synchronize()
+    return out
+
+
+def test_nvls_multimem_allreduce_when_available():
+    world = _world()
+    res = run_ranks(_nvls_allreduce, (), world=world)
+    if res[0]['error'] or not res[0]['available']:
+        pytest.skip('NVLS multicast not usable here: %s' % (res[0]['error'] or 'no multicast address'))
+    for numel in res[0]['results']:
+        want = sum(r['results'][numel][0].double() for r in res) / world
+        for r in res:
+            torch.testing.assert_close(r['results'][numel][1].double(), want, rtol=1e-5, atol=1e-5)
+            assert torch.equal(r['results'][numel][1], res[0]['results'][numel][1])

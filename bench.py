@@ -199,6 +199,30 @@ def run_ours(args):
     ms_e2e = hvd.parallel.runtime.max_over_ranks(ms_e2e) if world > 1 else ms_e2e
     final_loss = step.last_loss()
 
+    exposed = comm_ms = None
+    if world > 1 and getattr(optimizer, '_fused_comm', False):
+        # exposed communication = end of the last communication kernel minus end of backward (>= 0), eager steps
+        from mgwfbp_b200.utils.tracing import CommTrace
+        from mgwfbp_b200.engine import _tables_of
+        for tbl in _tables_of(optimizer):
+            tbl.invalidate()
+        vals, totals = [], []
+        for i in range(5 if args.dnn != 'lstm' else 0):
+            trace = CommTrace(optimizer)
+            optimizer.zero_grad()
+            with trace:
+                loss, _o, _l, _h = trainer.forward_loss(dev_batch, None, on_device=True)
+                loss.backward()
+                trace.mark_backward_end()
+                optimizer.step()
+            summ = trace.summary()
+            if i >= 2:
+                vals.append(summ['exposed_comm_ms'])
+                totals.append(summ['comm_ms'])
+        if vals:
+            exposed = hvd.parallel.runtime.max_over_ranks(sum(vals) / len(vals))
+            comm_ms = hvd.parallel.runtime.max_over_ranks(sum(totals) / len(totals))
+
     if rank == 0:
         value = world * bs * per_sample / (ms_dev * 1e-3)
         e2e = world * bs * per_sample / (ms_e2e * 1e-3)
@@ -217,6 +241,7 @@ def run_ours(args):
             'clocks': clocks,
             'e2e': {'value': e2e, 'unit': unit, 'ms_per_step': ms_e2e, 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': 4},
             'gpu_launches': launches, 'final_loss': final_loss,
+            'exposed_comm_ms': exposed, 'comm_kernel_ms': comm_ms,
         }
         print(json.dumps(out))
     hvd.shutdown()
@@ -258,7 +283,8 @@ def run_reference(args):
     if world not in (1, 2, 4, 8, 16) and args.policy == 'mgwfbp':
         print(json.dumps({'impl': 'reference', 'unavailable': 'reference cost tables only cover 2/4/8/16 workers'}))
         return
-    kw = {}
+    if dataset == 'ptb':
+        DLTrainer.vocab_size = 10000      # normally discovered by the PTB reader; no dataset is read here
     trainer = DLTrainer(rank, world, dist=False, batch_size=bs, is_weak_scaling=True, ngpus=1, data_dir=None,
                         dataset=dataset, dnn=args.dnn, lr=lr, nworkers=world, prefix='allreduce', num_steps=35)
     if dataset != 'ptb':
@@ -272,10 +298,16 @@ def run_reference(args):
     elif dataset == 'cifar10':
         shape, classes = (bs, 3, 32, 32), 10
     else:
-        raise SystemExit('reference arm supports the image workloads')
+        shape, classes = (bs, 35), 10000
     g = torch.Generator().manual_seed(rank)
-    ring = [(torch.randn(shape, generator=g).pin_memory(), torch.randint(0, classes, (bs,), generator=g).pin_memory())
-            for _ in range(4)]
+    if dataset == 'ptb':
+        ring = []
+        for _ in range(4):
+            seq = torch.randint(0, classes, (bs, 36), generator=g)
+            ring.append((seq[:, :-1].contiguous().pin_memory(), seq[:, 1:].contiguous().pin_memory()))
+    else:
+        ring = [(torch.randn(shape, generator=g).pin_memory(), torch.randint(0, classes, (bs,), generator=g).pin_memory())
+                for _ in range(4)]
 
     class _Iter(object):           # the reference calls `.next()` on its iterator (Python-2 style)
         def __init__(self):
@@ -306,11 +338,17 @@ def run_reference(args):
         if world > 1:
             torch.distributed.barrier()
     dev_batch = tuple(t.cuda() for t in ring[0])
+    hidden = [trainer.net.init_hidden()] if args.dnn == 'lstm' else None
 
     def step_with(data):
         optimizer.zero_grad()
         optimizer.local = False
-        trainer.train(1, data=data)          # forward, backward (+ hooks), loss.item()
+        if args.dnn == 'lstm':               # loop body of the reference's dist_trainer.py:85-94
+            _, hidden[0] = trainer.train(1, data=data, hidden=hidden[0])
+            optimizer.synchronize()
+            torch.nn.utils.clip_grad_norm_(trainer.net.parameters(), 0.25)
+        else:
+            trainer.train(1, data=data)      # forward, backward (+ hooks), loss.item()
         trainer.update_model()               # synchronize + SGD step
 
     for i in range(max(args.warmup, 3)):

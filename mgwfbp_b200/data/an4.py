@@ -134,3 +134,29 @@ class GreedyDecoder:
     @staticmethod
     def cer(s1: str, s2: str) -> int:
         return _edit_distance(s1.replace(' ', ''), s2.replace(' ', ''))
+
+
+def create_manifest(data_path: str, tag: str, ordered: bool = True, out_dir: str = '.') -> str:
+    """Write ``<tag>_manifest.csv`` listing ``wav_path,txt_path`` for every ``wav/*.wav`` under ``data_path``
+    with its transcript in the sibling ``txt/`` folder (what the reference's ``audio_data/utils.py`` produces
+    after its download step; downloading itself needs network access and is left to the user).
+    ``ordered`` sorts by audio duration, shortest first."""
+    import os
+    wavs = []
+    for root, _dirs, files in os.walk(data_path):
+        for fn in files:
+            if fn.lower().endswith('.wav'):
+                wavs.append(os.path.join(root, fn))
+    if ordered:
+        def duration(p):
+            with wave.open(p, 'rb') as w:
+                return w.getnframes() / float(w.getframerate())
+        wavs.sort(key=duration)
+    else:
+        wavs.sort()
+    out = os.path.join(out_dir, '%s_manifest.csv' % tag)
+    with open(out, 'w') as f:
+        for wav in wavs:
+            txt = wav.replace('/wav/', '/txt/').replace('.wav', '.txt')
+            f.write('%s,%s\n' % (os.path.abspath(wav), os.path.abspath(txt)))
+    return out

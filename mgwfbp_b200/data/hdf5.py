@@ -81,3 +81,29 @@ def create_hdf5(image_root: str, out_file: str, label_csv: str, size: int = 256,
                 with Image.open(fn) as im:
                     imgs[i] = np.asarray(im.convert('RGB').resize((size, size), Image.BICUBIC), dtype=np.uint8)
     return out_file
+
+
+def _main(argv=None):
+    """``python -m mgwfbp_b200.data.hdf5 <image_root> <out.hdf5> <label_csv> [--size 256]`` converts
+    ImageNet folders to the single-file layout (the reference's ``scripts/create_hdf5.py``);
+    ``--show N`` prints the first N labels and image shapes of an existing file instead
+    (``scripts/test_read_hdf5.py`` without the plotting)."""
+    import argparse
+    ap = argparse.ArgumentParser(description=_main.__doc__)
+    ap.add_argument('image_root')
+    ap.add_argument('out_file')
+    ap.add_argument('label_csv', nargs='?')
+    ap.add_argument('--size', type=int, default=256)
+    ap.add_argument('--show', type=int, default=0)
+    a = ap.parse_args(argv)
+    if a.show:
+        ds = DatasetHDF5(a.out_file, 'train')
+        for i in range(min(a.show, len(ds))):
+            img, label = ds[i]
+            print(i, int(label), getattr(img, 'shape', None))
+        return
+    print(create_hdf5(a.image_root, a.out_file, a.label_csv, a.size))
+
+
+if __name__ == '__main__':
+    _main()

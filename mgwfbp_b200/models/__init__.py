@@ -20,6 +20,7 @@ from .cifar_resnet import (resnet20, resnet32, resnet44, resnet56, resnet110,  #
 from .small import (MnistNet, FCN5Net, LinearRegression, LeNet, VGG, caffe_cifar, densenet100_12)  # noqa: F401
 from .inception import googlenet, GoogLeNet, inceptionv4, InceptionV4  # noqa: F401
 from .alexnet_lrn import AlexNet  # noqa: F401
+from .cifar_resnet_tv import ResNet18, ResNet34, ResNet50, ResNet101, ResNet152, model_builder  # noqa: F401
 from .lstm import lstm, repackage_hidden  # noqa: F401
 from .deepspeech import DeepSpeech, create_net as LSTMAN4  # noqa: F401
 

@@ -196,3 +196,41 @@ def test_profiler_returns_measured_order_reversed():
     for h in handles:
         h.remove()
     assert fired == names[::-1]
+
+
+def test_single_gpu_cli_and_evaluate_roundtrip(tmp_path, monkeypatch):
+    """dl_trainer's loop on CPU with synthetic data, a checkpoint at the epoch boundary, then evaluate.py."""
+    monkeypatch.chdir(tmp_path)
+    from mgwfbp_b200.trainer import train_with_single
+    import mgwfbp_b200.data.synthetic as syn
+    monkeypatch.setitem(syn.NOMINAL_LENGTH, 'mnist', (64, 32))       # 4 iterations of 16 per epoch
+    trainer = train_with_single('lenet', 'mnist', 'synthetic', 1, 0.01, 16, 1, 2, max_iters=6)
+    assert trainer.get_train_iter() >= 6 and trainer.get_train_epoch() == 1
+    ckpt_dir = os.path.join(str(tmp_path), 'weights', 'singlegpu', 'lenet-n1-bs16-lr0.0100')
+    assert os.path.isfile(os.path.join(ckpt_dir, 'lenet-rank0-epoch1.pth'))
+    import evaluate
+    best = evaluate.evaluate(ckpt_dir, 'lenet', 'mnist', 'synthetic', nepochs=1, start_epoch=1)
+    assert best is not None and 0.0 <= best <= 100.0
+
+
+def test_train_step_driver_on_cpu():
+    from mgwfbp_b200.engine import TrainStep
+    t = _trainer('lenet', 'mnist', batch_size=8)
+    t.update_optimizer(hvd.DistributedOptimizer(t.optimizer, named_parameters=t.net.named_parameters()))
+    step = TrainStep(t, use_graph=True)           # no GPU: runs eagerly
+    before = [p.detach().clone() for p in t.net.parameters()]
+    for _ in range(3):
+        step.run(t.data_iter())
+    assert not step.graphed and len(step.losses) == 3 and all(l == l for l in step.losses)
+    assert any(not torch.equal(a, b.detach()) for a, b in zip(before, t.net.parameters()))
+    assert t.get_train_iter() == 3
+
+
+def test_extra_models_build():
+    from mgwfbp_b200 import models
+    for ctor in (models.preresnet20, models.resnet_mod20, models.resnext29_8_64, models.caffe_cifar, models.densenet100_12,
+                 models.ResNet18):
+        with torch.device('meta'):
+            net = ctor()
+        assert sum(p.numel() for p in net.parameters()) > 0
+    assert models.resnet20().name == 'resnet20'

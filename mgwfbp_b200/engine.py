@@ -33,7 +33,8 @@ class TrainStep:
         self.trainer = trainer
         self.optimizer = trainer.optimizer
         self.cuda = trainer.is_cuda
-        self.want_graph = bool(use_graph and self.cuda and trainer.dnn not in ('lstm', 'lstman4'))
+        self.want_graph = bool(use_graph and self.cuda and trainer.dnn != 'lstman4')
+        self._static_hidden = None
         self.graphed = False
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._static_batch: Optional[Tuple[torch.Tensor, ...]] = None
@@ -72,11 +73,18 @@ class TrainStep:
         before = counters.snapshot()
         g = torch.cuda.CUDAGraph()
         torch.cuda.synchronize()
+        if t.dnn == 'lstm':
+            # the recurrent state lives in static buffers that the captured step reads and then overwrites
+            start = self._hidden if self._hidden is not None else t.net.init_hidden()
+            self._static_hidden = tuple(h.detach().clone() for h in start)
         with torch.cuda.graph(g):
-            loss, _o, _l, _h = t.forward_loss(self._static_batch, None, on_device=True)
+            loss, _o, _l, hid = t.forward_loss(self._static_batch, self._static_hidden, on_device=True)
             loss.backward()
             t.optimizer.step()
             self._static_loss = loss.detach()
+            if self._static_hidden is not None:
+                for dst, src in zip(self._static_hidden, hid):
+                    dst.copy_(src.detach())
         self._launches_per_replay = counters.diff(before)
         self._graph = g
         self.graphed = True

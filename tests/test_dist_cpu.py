@@ -24,7 +24,7 @@ def _worker(rank, world, port, fn, args, out_dir, use_cuda=False):
     torch.set_num_threads(1)
     os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
     import mgwfbp_b200 as hvd
-    hvd.init(timeout_s=120, device='cuda' if use_cuda else 'cpu')
+    hvd.init(timeout_s=float(os.environ.get('MGWFBP_TEST_TIMEOUT_S', '120')), device='cuda' if use_cuda else 'cpu')
     try:
         result = fn(rank, world, *args)
         torch.save(result, os.path.join(out_dir, 'rank%d.pt' % rank))
@@ -155,6 +155,39 @@ def _cli_run(rank, world, tmp):
     return {'iter': trainer.get_train_iter()}
 
 
+def _replica_guard(rank, world):
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200.utils.consistency import ReplicaDivergenceError, ReplicaGuard, check_replicas
+    torch.manual_seed(0)
+    net = torch.nn.Linear(6, 3)
+    hvd.broadcast_parameters(net.state_dict(), 0)
+    guard = ReplicaGuard(net, every=2)
+    assert guard.step() is False and guard.step() is True          # identical replicas pass
+    with torch.no_grad():
+        if rank == 1:
+            net.bias[1] += 1e-7                                      # one ulp-scale corruption on one rank
+    try:
+        check_replicas(net.named_parameters())
+        return {'caught': None}
+    except ReplicaDivergenceError as e:
+        return {'caught': str(e)}
+
+
+def _absent_rank(rank, world):
+    """Rank 1 never joins the collective: rank 0 must get an exception within the control-plane timeout."""
+    import time
+    import mgwfbp_b200 as hvd
+    t0 = time.time()
+    if rank == 1:
+        time.sleep(6)
+        return {'error': None, 'waited': time.time() - t0}
+    try:
+        hvd.barrier()
+        return {'error': None, 'waited': time.time() - t0}
+    except Exception as e:
+        return {'error': type(e).__name__, 'waited': time.time() - t0}
+
+
 # ----------------------------------------------------------------------------- tests
 @pytest.fixture(scope='module')
 def resnet20_runs():
@@ -219,3 +252,14 @@ def test_mismatched_schedule_is_detected():
 def test_dist_trainer_loop_runs(tmp_path):
     r0, r1 = run_ranks(_cli_run, (str(tmp_path),))
     assert r0['iter'] == 3 and r1['iter'] == 3
+
+
+def test_replica_guard_detects_divergence():
+    r0, r1 = run_ranks(_replica_guard)
+    assert r0['caught'] and 'bias' in r0['caught'] and r1['caught']
+
+
+def test_absent_rank_surfaces_as_timeout_not_hang(monkeypatch):
+    monkeypatch.setenv('MGWFBP_TEST_TIMEOUT_S', '3')
+    r0, r1 = run_ranks(_absent_rank)
+    assert r0['error'] is not None and r0['waited'] < 30

@@ -1,0 +1,88 @@
+# -*- coding: utf-8 -*-
+"""All-reduce sweep of the NVLink data plane against NCCL, one process per GPU.
+
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29650 \
+        -m mgwfbp_b200.parallel.comm.bench [--max-mb 256] [--iters 20]
+
+For every message size: device time (CUDA events on the launching stream, max over ranks) of this
+package's one-shot / two-shot / NVLS kernels (reduce + 1/N + write-back, launched on the side stream)
+and of ``torch.distributed.all_reduce`` (NCCL), the algorithm bandwidth ``S / t`` and the bus
+bandwidth ``2 (N-1)/N * S / t``.  Ends with the fitted ``alpha + beta * bytes`` per algorithm, the
+quantities the MG-WFBP scheduler consumes (the reference hard-codes them for its authors' Ethernet /
+InfiniBand clusters, ``distributed_optimizer.py:166-177``).  Rank 0 prints a JSON document.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from ... import settings
+from .. import runtime
+from ..costmodel import fit_alpha_beta
+
+
+def _time(fn, iters: int, barrier) -> float:
+    for _ in range(3):
+        fn()
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return runtime.max_over_ranks(e0.elapsed_time(e1) / iters)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument('--max-mb', type=float, default=256.0)
+    ap.add_argument('--iters', type=int, default=20)
+    args = ap.parse_args(argv)
+    runtime.init()
+    settings.logger.setLevel('WARNING')
+    from .nvl import NvlComm
+    comm = NvlComm.shared()
+    world, rank = runtime.size(), runtime.rank()
+    sizes = [1 << k for k in range(8, 31) if (1 << k) * 4 <= args.max_mb * 1e6]       # floats
+    rows, samples = [], {}
+    algos = ['oneshot', 'twoshot'] + (['nvls'] if comm.nvls_available else [])
+    for n in sizes:
+        x = torch.randn(n, device='cuda')
+        row = {'bytes': 4 * n}
+        for algo in algos:
+            if algo == 'oneshot' and 4 * n > comm.oneshot_max_bytes:
+                continue
+            ms = _time(lambda: comm.synchronize(comm.allreduce_async_(x, algo=algo)), args.iters, runtime.barrier)
+            row[algo + '_us'] = ms * 1e3
+            samples.setdefault(algo, ([], []))
+            samples[algo][0].append(n)
+            samples[algo][1].append(ms * 1e-3)
+        ms = _time(lambda: dist.all_reduce(x, op=dist.ReduceOp.AVG), args.iters, runtime.barrier)
+        row['nccl_us'] = ms * 1e3
+        samples.setdefault('nccl', ([], []))
+        samples['nccl'][0].append(n)
+        samples['nccl'][1].append(ms * 1e-3)
+        best = min(v for k, v in row.items() if k.endswith('_us') and k != 'nccl_us')
+        row['best_busbw_GBps'] = 2 * (world - 1) / world * 4 * n / (best * 1e-6) / 1e9
+        row['nccl_busbw_GBps'] = 2 * (world - 1) / world * 4 * n / (row['nccl_us'] * 1e-6) / 1e9
+        rows.append(row)
+        comm.check_status(synchronize=True)
+    fits = {}
+    for algo, (ns, ts) in samples.items():
+        if len(ns) >= 2:
+            ab = fit_alpha_beta(ns, ts, 4, algo)
+            fits[algo] = {'alpha_us': ab.alpha * 1e6, 'beta_s_per_byte': ab.beta,
+                          'asymptotic_algbw_GBps': (1e-9 / ab.beta) if ab.beta > 0 else None}
+    if rank == 0:
+        print(json.dumps({'world': world, 'heap': os.environ.get('MGWFBP_HEAP', 'ipc'), 'rows': rows, 'fits': fits}))
+    runtime.shutdown()
+
+
+if __name__ == '__main__':
+    main()

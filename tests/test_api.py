@@ -234,3 +234,25 @@ def test_extra_models_build():
             net = ctor()
         assert sum(p.numel() for p in net.parameters()) > 0
     assert models.resnet20().name == 'resnet20'
+
+
+def test_speech_and_language_model_paths_train_on_synthetic_data():
+    """The AN4 acoustic model (CTC) and the PTB LSTM (hidden state carried, global-norm clip) run end to end."""
+    t = _trainer('lstman4', 'an4', batch_size=2, lr=0.0002)
+    t.update_optimizer(hvd.DistributedOptimizer(t.optimizer, named_parameters=t.net.named_parameters(), norm_clip=400))
+    t.optimizer.zero_grad()
+    t.train(1)
+    t.update_model()
+    assert t.loss == t.loss and t.loss > 0
+    assert 0.0 <= t.test(0)
+    t = _trainer('lstm', 'ptb', batch_size=4, lr=22.0, num_steps=35)
+    t.update_optimizer(hvd.DistributedOptimizer(t.optimizer, named_parameters=t.net.named_parameters(), norm_clip=0.25))
+    hidden = t.net.init_hidden()
+    before = t.net.sm_fc.weight.detach().clone()
+    for _ in range(2):
+        t.optimizer.zero_grad()
+        _, hidden = t.train(1, hidden=hidden)
+        t.update_model()
+    assert t.loss == t.loss and hidden[0].shape == (2, 4, 1500)
+    step = (t.net.sm_fc.weight.detach() - before).norm()
+    assert 0 < float(step) <= 22.0 * 0.25 * 2 + 1e-3       # clipped gradient norm bounds each update

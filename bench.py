@@ -165,8 +165,12 @@ def run_ours(args):
     # ---- end to end: pinned host batch -> device, step, loss back to the host, every step ---------------
     loss_host = []
 
+    upcoming = [trainer.data_iter()]
+
     def step_e2e(i):
-        loss_host.append(step.run(trainer.data_iter()))
+        cur, nxt = upcoming[0], trainer.data_iter()      # the next pinned batch is copied while this step computes
+        upcoming[0] = nxt
+        loss_host.append(step.run(cur, next_host_batch=nxt))
 
     barrier = hvd.barrier
     for i in range(max(args.warmup, 3)):

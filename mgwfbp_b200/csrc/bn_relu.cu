@@ -273,7 +273,8 @@ __device__ __forceinline__ void load_channel_consts(int c0, int C, const float* 
 
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
-bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, const float* __restrict__ x, float* __restrict__ dz,
+bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2, const float* __restrict__ y, const float* __restrict__ x,
+                     float* __restrict__ dz,
                      long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                      const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
                      float* __restrict__ partials) {
@@ -296,6 +297,13 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, 
             load_vec<VEC>(dy + (r + TY) * C + c0, g1);
             load_vec<VEC>(x + r * C + c0, x0);
             load_vec<VEC>(x + (r + TY) * C + c0, x1);
+            if (dy2) {                                           // the output had two consumers: sum their gradients here
+                float h0[VEC], h1[VEC];
+                load_vec<VEC>(dy2 + r * C + c0, h0);
+                load_vec<VEC>(dy2 + (r + TY) * C + c0, h1);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) { g0[k] += h0[k]; g1[k] += h1[k]; }
+            }
             masked_grad<VEC>(g0, x0, mask_mode == 1 ? y + r * C + c0 : nullptr, mask_mode, sc, sh);
             masked_grad<VEC>(g1, x1, mask_mode == 1 ? y + (r + TY) * C + c0 : nullptr, mask_mode, sc, sh);
 #pragma unroll
@@ -313,6 +321,12 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, 
             float g[VEC], xv[VEC];
             load_vec<VEC>(dy + r * C + c0, g);
             load_vec<VEC>(x + r * C + c0, xv);
+            if (dy2) {
+                float h[VEC];
+                load_vec<VEC>(dy2 + r * C + c0, h);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) g[k] += h[k];
+            }
             masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0 : nullptr, mask_mode, sc, sh);
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
@@ -338,7 +352,8 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ y, 
 // gsrc is dz (mask already applied, mask_mode 0) or dy (mask applied here again, mask_mode 1 / 2).
 template <int VEC>
 __global__ void __launch_bounds__(kThreads)
-bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ y, const float* __restrict__ x, float* __restrict__ dx,
+bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gsrc2, const float* __restrict__ y, const float* __restrict__ x,
+                    float* __restrict__ dx,
                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                     const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
                     const float* __restrict__ dgamma, const float* __restrict__ dbeta) {
@@ -361,6 +376,12 @@ bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ y,
         float g[VEC], xv[VEC], o[VEC];
         load_vec<VEC>(gsrc + r * C + c0, g);
         load_vec<VEC>(x + r * C + c0, xv);
+        if (gsrc2) {
+            float h[VEC];
+            load_vec<VEC>(gsrc2 + r * C + c0, h);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) g[k] += h[k];
+        }
         masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0 : nullptr, mask_mode, sc, sh);
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
@@ -407,11 +428,13 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
     return MGW_OK;
 }
 
-// Backward.  With dz != null the masked gradient dy * (y > 0) is written there (it is also the gradient
+// Backward.  dy2 (may be null) is a second incoming gradient of the same output -- a block output that feeds
+// both the next convolution and the next shortcut -- and is added on load, which replaces autograd's separate
+// add kernel.  With dz != null the masked gradient dy * (y > 0) is written there (it is also the gradient
 // of the residual input) and the ReLU mask comes from y; dx may alias dz.  With dz == null nothing is
 // materialised: both passes read dy and x and rebuild the mask from x (gamma / beta must be the forward
 // values), which saves one read and one write of the activation.
-int mgw_bn_relu_bwd(const float* dy, const float* y, const float* x, float* dz, float* dx, long long M, int C, const float* gamma,
+int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const float* x, float* dz, float* dx, long long M, int C, const float* gamma,
                     const float* beta, const float* save_mean, const float* save_invstd, int relu, float* dgamma, float* dbeta,
                     float* partials, void* stream) {
     if (dy == nullptr || x == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
@@ -419,6 +442,7 @@ int mgw_bn_relu_bwd(const float* dy, const float* y, const float* x, float* dz, 
     const int mask1 = !relu ? 0 : (y != nullptr ? 1 : 2);          // mask used by the reduce pass
     const int mask2 = dz != nullptr ? 0 : mask1;                   // apply pass: dz already carries the mask
     const float* gsrc = dz != nullptr ? dz : dy;
+    const float* gsrc2 = dz != nullptr ? nullptr : dy2;        // dz already holds the sum of both gradients
     const int vec = (C % 4 == 0) ? 4 : 1;
     const Tiling t = make_tiling(M, C, vec);
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
@@ -426,13 +450,13 @@ int mgw_bn_relu_bwd(const float* dy, const float* y, const float* x, float* dz, 
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     if (vec == 4) {
-        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials);
+        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(gsrc, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta);
+        bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta);
     } else {
-        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(dy, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials);
+        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(gsrc, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta);
+        bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;

@@ -47,6 +47,10 @@ class TrainStep:
         self._pinned_losses = [torch.zeros(1).pin_memory() if self.cuda else torch.zeros(1) for _ in range(loss_ring)]
         self._slot = 0
         self.losses: List[float] = []
+        # input prefetch: a copy stream moves the next host batch while the current step computes
+        self._copy_stream = torch.cuda.Stream() if self.cuda else None
+        self._prefetched = None          # (host_batch, device_batch, ready_event)
+        self._staging_free: List[object] = []
 
     # ------------------------------------------------------------------ pieces
     def _host_bookkeeping(self):
@@ -124,12 +128,38 @@ class TrainStep:
             pass
         return self._device_step(device_batch)
 
-    def run(self, host_batch) -> Optional[float]:
+    def prefetch(self, host_batch) -> None:
+        """Start copying ``host_batch`` (pinned memory) to the device on the copy stream.  The next
+        ``run(host_batch)`` with the same object uses the copy instead of issuing its own."""
+        if not self.cuda or host_batch is None:
+            return
+        with torch.cuda.stream(self._copy_stream):
+            dev = self.trainer.to_device(host_batch)
+            ev = torch.cuda.Event()
+            ev.record()
+        self._prefetched = (host_batch, dev, ev)
+
+    def _take_inputs(self, host_batch):
+        pre = self._prefetched
+        if pre is not None and pre[0] is host_batch:
+            self._prefetched = None
+            torch.cuda.current_stream().wait_event(pre[2])
+            for t in pre[1]:
+                if torch.is_tensor(t) and t.is_cuda:
+                    t.record_stream(torch.cuda.current_stream())     # allocated on the copy stream, consumed here
+            return pre[1]
+        return self.trainer.to_device(host_batch)
+
+    def run(self, host_batch, next_host_batch=None) -> Optional[float]:
         """One end-to-end step from a host batch.  Returns the most recent loss value that has
-        arrived on the host (the loss of an earlier step), or ``None`` before the first arrives."""
+        arrived on the host (the loss of an earlier step), or ``None`` before the first arrives.
+        ``next_host_batch`` (optional) is copied to the device on a second stream while this step
+        computes, so that its host-to-device transfer is off the critical path of the next call."""
         self._host_bookkeeping()
-        batch = self.trainer.to_device(host_batch)
+        batch = self._take_inputs(host_batch)
         loss = self._device_step(batch)
+        if next_host_batch is not None:
+            self.prefetch(next_host_batch)
         if self.cuda:
             if len(self._pending) >= self._ring:
                 self._collect(1)

@@ -38,22 +38,30 @@ def _to_fused(bn: nn.Module, relu: bool) -> nn.Module:
 
 
 # ---- forwards for known blocks ------------------------------------------------------------------
+def _split(x):
+    """A block receives either one tensor or the previous block's (main, shortcut) pair of handles."""
+    return x if isinstance(x, tuple) else (x, x)
+
+
 def _tv_bottleneck_forward(self, x):
-    out = self.bn1(self.conv1(x))
+    x_main, x_id = _split(x)
+    out = self.bn1(self.conv1(x_main))
     out = self.bn2(self.conv2(out))
-    identity = x if self.downsample is None else self.downsample(x)
-    return self.bn3(self.conv3(out), identity)
+    identity = x_id if self.downsample is None else self.downsample(x_id)
+    return self.bn3(self.conv3(out), identity, dual=True)        # (output, same output) for the next block
 
 
 def _tv_basicblock_forward(self, x):
-    out = self.bn1(self.conv1(x))
-    identity = x if self.downsample is None else self.downsample(x)
-    return self.bn2(self.conv2(out), identity)
+    x_main, x_id = _split(x)
+    out = self.bn1(self.conv1(x_main))
+    identity = x_id if self.downsample is None else self.downsample(x_id)
+    return self.bn2(self.conv2(out), identity, dual=True)
 
 
 def _tv_resnet_forward_impl(self, x):
     x = self.maxpool(self.bn1(self.conv1(x)))
     x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
+    x = x[0] if isinstance(x, tuple) else x
     return self.fc(torch.flatten(self.avgpool(x), 1))
 
 
@@ -78,14 +86,16 @@ def _basicconv_forward(self, x):
 
 
 def _cifar_block_forward(self, x):
-    out = self.bn_a(self.conv_a(x))
-    shortcut = x if self.downsample is None else self.downsample(x)
-    return self.bn_b(self.conv_b(out), shortcut)
+    x_main, x_id = _split(x)
+    out = self.bn_a(self.conv_a(x_main))
+    shortcut = x_id if self.downsample is None else self.downsample(x_id)
+    return self.bn_b(self.conv_b(out), shortcut, dual=True)
 
 
 def _cifar_resnet_forward(self, x):
     x = self.bn_1(self.conv_1_3x3(x))
     x = self.stage_3(self.stage_2(self.stage_1(x)))
+    x = x[0] if isinstance(x, tuple) else x
     x = self.avgpool(x)
     return self.classifier(x.reshape(x.size(0), -1))
 

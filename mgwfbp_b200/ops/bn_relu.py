@@ -44,7 +44,7 @@ def _declare(lib) -> None:
     lib.mgw_bn_relu_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p]
-    lib.mgw_bn_relu_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
+    lib.mgw_bn_relu_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_void_p]
     _declared = True
@@ -56,7 +56,7 @@ def _ptr(t: Optional[torch.Tensor]):
 
 class _BNReLU(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, running_mean, running_var, num_batches_tracked, residual, relu, momentum, eps):
+    def forward(ctx, x, weight, bias, running_mean, running_var, num_batches_tracked, residual, relu, momentum, eps, dual):
         lib = _lib.load(allow_build=False)
         _declare(lib)
         M, Cc = _as_rows(x)
@@ -74,40 +74,48 @@ class _BNReLU(torch.autograd.Function):
         ctx.save_for_backward(x, y if (relu and residual is not None) else None, weight, bias, mean, invstd)
         ctx.relu, ctx.has_residual, ctx.rows = bool(relu), residual is not None, (M, Cc)
         ctx.mark_non_differentiable(*[t for t in (running_mean, running_var, num_batches_tracked) if t is not None])
+        if dual:
+            # two handles on the same output: each consumer's gradient then reaches backward() separately
+            # and the kernel sums them while loading, instead of autograd launching an add kernel
+            return y, y.view_as(y)
         return y
 
     @staticmethod
-    def backward(ctx, dy):
+    def backward(ctx, dy, dy2=None):
         lib = _lib.load(allow_build=False)
+        if dy is None:
+            dy, dy2 = dy2, None
         x, y, weight, bias, mean, invstd = ctx.saved_tensors
         M, Cc = ctx.rows
         if _as_rows(dy) is None or dy.stride() != x.stride():
             dy = dy.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else dy.contiguous()
+        if dy2 is not None and (_as_rows(dy2) is None or dy2.stride() != x.stride()):
+            dy2 = dy2.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else dy2.contiguous()
         dz = torch.empty_like(x) if ctx.has_residual else None     # only a residual needs the masked gradient itself
         dx = torch.empty_like(x)
         dgamma = torch.empty(Cc, dtype=torch.float32, device=x.device)
         dbeta = torch.empty(Cc, dtype=torch.float32, device=x.device)
         partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
         s = torch.cuda.current_stream().cuda_stream
-        _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
+        _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
                                        _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
                                        dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), s), 'bn_relu_bwd')
         counters.bump('bn_relu_bwd', 3)
         need = ctx.needs_input_grad
         return (dx if need[0] else None, dgamma if (weight is not None and need[1]) else None,
                 dbeta if need[2] else None, None, None, None, dz if (ctx.has_residual and need[6]) else None,
-                None, None, None)
+                None, None, None, None)
 
 
 def bn_relu(x, weight, bias, running_mean, running_var, num_batches_tracked, residual=None, relu=True,
-            momentum=0.1, eps=1e-5):
+            momentum=0.1, eps=1e-5, dual=False):
     """Functional form: training-mode batch norm over all but the channel dimension, optional
     residual add, optional ReLU.  ``x`` must be CUDA float32, dense, channels innermost."""
     if not x.is_cuda or x.dtype != torch.float32 or _as_rows(x) is None:
         raise ValueError('bn_relu needs a dense channels-last (or 2-D) float32 CUDA tensor')
     if residual is not None and (residual.shape != x.shape or residual.stride() != x.stride()):
         residual = residual.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else residual.contiguous()
-    return _BNReLU.apply(x, weight, bias, running_mean, running_var, num_batches_tracked, residual, relu, momentum, eps)
+    return _BNReLU.apply(x, weight, bias, running_mean, running_var, num_batches_tracked, residual, relu, momentum, eps, dual)
 
 
 class _FusedBNMixin:
@@ -117,19 +125,22 @@ class _FusedBNMixin:
         return (self.training and x.is_cuda and x.dtype == torch.float32 and self.momentum is not None
                 and self.track_running_stats and _as_rows(x) is not None and x.numel() > 0)
 
-    def forward(self, x, residual=None):
+    def forward(self, x, residual=None, dual=False):
+        """``dual=True`` returns the output twice (two handles on one tensor) for a consumer pair such as
+        the next block's first convolution and its shortcut; see :func:`bn_relu`."""
         if self._native_ok(x):
             return bn_relu(x, self.weight, self.bias, self.running_mean, self.running_var, self.num_batches_tracked,
-                           residual, self.fused_relu, self.momentum, self.eps)
+                           residual, self.fused_relu, self.momentum, self.eps, dual)
         if x.is_cuda and x.dim() == 4 and self.training and not x.is_contiguous(memory_format=torch.channels_last) \
                 and x.dtype == torch.float32 and self.momentum is not None and self.track_running_stats:
             # keep the native path: one layout conversion is cheaper than leaving the fused kernels
             return self.forward(x.contiguous(memory_format=torch.channels_last),
-                                None if residual is None else residual.contiguous(memory_format=torch.channels_last))
+                                None if residual is None else residual.contiguous(memory_format=torch.channels_last), dual)
         out = super().forward(x)
         if residual is not None:
             out = out + residual
-        return F.relu(out) if self.fused_relu else out
+        out = F.relu(out) if self.fused_relu else out
+        return (out, out) if dual else out
 
     def extra_repr(self):
         return super().extra_repr() + ', fused_relu=%s' % self.fused_relu

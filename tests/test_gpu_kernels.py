@@ -252,3 +252,33 @@ def test_fused_lstm_matches_cudnn_lstm():
     torch.testing.assert_close(x2.grad, x1.grad, rtol=1e-3, atol=1e-4)
     for (n, p1), p2 in zip(ref.named_parameters(), mine.parameters()):
         torch.testing.assert_close(p2.grad, p1.grad, rtol=1e-3, atol=1e-4, msg=lambda m: '%s: %s' % (n, m))
+
+
+def test_bn_relu_dual_output_sums_both_gradients():
+    """A block output feeding two consumers: both gradients reach the backward kernel and are summed there."""
+    from mgwfbp_b200.ops.bn_relu import bn_relu
+    torch.manual_seed(0)
+    dev = torch.device('cuda')
+    shape, C_ = (4, 32, 6, 6), 32
+    mk = lambda: (torch.randn(shape, device=dev)).contiguous(memory_format=torch.channels_last)
+    x, res = mk().requires_grad_(True), mk().requires_grad_(True)
+    w = (torch.rand(C_, device=dev) + 0.5).requires_grad_(True)
+    b = torch.randn(C_, device=dev).requires_grad_(True)
+    x2, res2, w2, b2 = (t.detach().clone().requires_grad_(True) for t in (x, res, w, b))
+    stats = lambda: (torch.zeros(C_, device=dev), torch.ones(C_, device=dev), torch.zeros((), dtype=torch.long, device=dev))
+    y_a, y_b = bn_relu(x, w, b, *stats(), res, True, 0.1, 1e-5, dual=True)
+    assert y_a.data_ptr() == y_b.data_ptr()
+    ref = _bn_reference(x2, w2, b2, *stats()[:2], res2, True, 0.1, 1e-5)
+    ga, gb = torch.randn_like(y_a), torch.randn_like(y_a)
+    ((y_a * ga).sum() + (y_b * gb).sum()).backward()
+    (ref * (ga + gb)).sum().backward()
+    torch.testing.assert_close(x.grad, x2.grad, rtol=1e-3, atol=2e-4)
+    torch.testing.assert_close(res.grad, res2.grad, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(w.grad, w2.grad, rtol=1e-3, atol=1e-3)
+    # only one of the two handles used
+    x.grad = res.grad = None
+    y_a, y_b = bn_relu(x, w, b, *stats(), res, True, 0.1, 1e-5, dual=True)
+    (y_b * gb).sum().backward()
+    x2.grad = res2.grad = None
+    (_bn_reference(x2, w2, b2, *stats()[:2], res2, True, 0.1, 1e-5) * gb).sum().backward()
+    torch.testing.assert_close(x.grad, x2.grad, rtol=1e-3, atol=2e-4)

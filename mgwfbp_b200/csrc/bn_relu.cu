@@ -238,6 +238,45 @@ bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ residual,
     }
 }
 
+// Description of a 3x3 / stride 2 / pad 1 max-pool that follows the BatchNorm+ReLU (the ResNet / DenseNet
+// stem).  When `dp` is set, the gradient of the (never materialised) ReLU output is gathered from the
+// pooled gradient: an input position collects dp of the up-to-four windows whose arg-max it was.
+struct PoolArgs {
+    const float* dp;             // [N, OH, OW, C] gradient of the pooled output, or null
+    const unsigned char* idx;    // [N, OH, OW, C] arg-max position inside the window (kh * 3 + kw)
+    int H, W, OH, OW;
+};
+
+template <int VEC>
+__device__ __forceinline__ void pooled_grad(float (&g)[VEC], const PoolArgs& pa, long long r, int c0, int C) {
+    const int iw = (int)(r % pa.W);
+    const long long t = r / pa.W;
+    const int ih = (int)(t % pa.H);
+    const long long n = t / pa.H;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) g[k] = 0.f;
+    const int oh0 = ih >> 1, oh1 = min(pa.OH - 1, (ih + 1) >> 1);
+    const int ow0 = iw >> 1, ow1 = min(pa.OW - 1, (iw + 1) >> 1);
+    for (int oh = oh0; oh <= oh1; ++oh) {
+        const int kh = ih - (2 * oh - 1);
+        for (int ow = ow0; ow <= ow1; ++ow) {
+            const int code = kh * 3 + (iw - (2 * ow - 1));
+            const size_t o = (((size_t)n * pa.OH + oh) * pa.OW + ow) * C + c0;
+            float d[VEC];
+            load_vec<VEC>(pa.dp + o, d);
+            if (VEC == 4) {
+                const uchar4 m = *reinterpret_cast<const uchar4*>(pa.idx + o);
+                if (m.x == code) g[0] += d[0];
+                if (m.y == code) g[1 % VEC] += d[1 % VEC];
+                if (m.z == code) g[2 % VEC] += d[2 % VEC];
+                if (m.w == code) g[3 % VEC] += d[3 % VEC];
+            } else {
+                if (pa.idx[o] == code) g[0] += d[0];
+            }
+        }
+    }
+}
+
 // Gradient entering the normalisation for one vector of channels: dy, masked by the ReLU.
 // mask_mode 0: no ReLU; 1: mask from the saved output y; 2: mask recomputed from x (bitwise the same
 // fused multiply-add as the forward pass, so the sign test agrees with what the forward pass clipped).
@@ -277,7 +316,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
                      float* __restrict__ dz,
                      long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                      const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
-                     float* __restrict__ partials) {
+                     float* __restrict__ partials, const PoolArgs pool) {
     extern __shared__ float smem[];
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
@@ -291,7 +330,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
     const long long r1 = min(M, r0 + rows_per_split);
     if (active) {
         long long r = r0 + ty;
-        for (; r + TY < r1; r += 2LL * TY) {                  // two rows per trip: more loads in flight
+        for (; pool.dp == nullptr && r + TY < r1; r += 2LL * TY) {   // two rows per trip: more loads in flight
             float g0[VEC], g1[VEC], x0[VEC], x1[VEC];
             load_vec<VEC>(dy + r * C + c0, g0);
             load_vec<VEC>(dy + (r + TY) * C + c0, g1);
@@ -319,7 +358,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
         }
         for (; r < r1; r += TY) {
             float g[VEC], xv[VEC];
-            load_vec<VEC>(dy + r * C + c0, g);
+            if (pool.dp) pooled_grad<VEC>(g, pool, r, c0, C); else load_vec<VEC>(dy + r * C + c0, g);
             load_vec<VEC>(x + r * C + c0, xv);
             if (dy2) {
                 float h[VEC];
@@ -356,7 +395,7 @@ bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gs
                     float* __restrict__ dx,
                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                     const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
-                    const float* __restrict__ dgamma, const float* __restrict__ dbeta) {
+                    const float* __restrict__ dgamma, const float* __restrict__ dbeta, const PoolArgs pool) {
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int c0 = (blockIdx.x * TX + tx) * VEC;
@@ -374,7 +413,7 @@ bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gs
     const long long r1 = min(M, r0 + rows_per_split);
     for (long long r = r0 + ty; r < r1; r += TY) {
         float g[VEC], xv[VEC], o[VEC];
-        load_vec<VEC>(gsrc + r * C + c0, g);
+        if (pool.dp) pooled_grad<VEC>(g, pool, r, c0, C); else load_vec<VEC>(gsrc + r * C + c0, g);
         load_vec<VEC>(x + r * C + c0, xv);
         if (gsrc2) {
             float h[VEC];
@@ -389,6 +428,54 @@ bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gs
             o[k] = sc[k] * (g[k] - db[k] - xhat * dg[k]);
         }
         store_vec<VEC>(dx + r * C + c0, o);
+    }
+}
+
+// y_pool = maxpool3x3/s2/p1(relu(x * scale + shift)) in one pass over x; the full-resolution ReLU output is
+// never written.  One thread per (output pixel, 4 channels); idx records which of the nine taps won.
+template <int VEC>
+__global__ void __launch_bounds__(256)
+bn_relu_maxpool_kernel(const float* __restrict__ x, float* __restrict__ yp, unsigned char* __restrict__ idx, int N, int H, int W,
+                       int OH, int OW, int C, const float* __restrict__ gamma, const float* __restrict__ beta,
+                       const float* __restrict__ save_mean, const float* __restrict__ save_invstd) {
+    const int lanes = C / VEC;
+    const long long total = (long long)N * OH * OW * lanes;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int c0 = (int)(i % lanes) * VEC;
+        long long t = i / lanes;
+        const int ow = (int)(t % OW); t /= OW;
+        const int oh = (int)(t % OH);
+        const long long n = t / OH;
+        float mean[VEC], istd[VEC], sc[VEC], sh[VEC], best[VEC];
+        int code[VEC];
+        load_channel_consts<VEC>(c0, C, gamma, beta, save_mean, save_invstd, mean, istd, sc, sh);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) { best[k] = -INFINITY; code[k] = 0; }
+#pragma unroll
+        for (int kh = 0; kh < 3; ++kh) {
+            const int ih = 2 * oh - 1 + kh;
+            if (ih < 0 || ih >= H) continue;
+#pragma unroll
+            for (int kw = 0; kw < 3; ++kw) {
+                const int iw = 2 * ow - 1 + kw;
+                if (iw < 0 || iw >= W) continue;
+                float v[VEC];
+                load_vec<VEC>(x + (((size_t)n * H + ih) * W + iw) * C + c0, v);
+#pragma unroll
+                for (int k = 0; k < VEC; ++k) {
+                    const float z = fmaxf(fmaf(v[k], sc[k], sh[k]), 0.f);
+                    if (z > best[k]) { best[k] = z; code[k] = kh * 3 + kw; }
+                }
+            }
+        }
+        const size_t o = (((size_t)n * OH + oh) * OW + ow) * C + c0;
+        store_vec<VEC>(yp + o, best);
+        if (VEC == 4) {
+            *reinterpret_cast<uchar4*>(idx + o) = make_uchar4((unsigned char)code[0], (unsigned char)code[1 % VEC],
+                                                              (unsigned char)code[2 % VEC], (unsigned char)code[3 % VEC]);
+        } else {
+            idx[o] = (unsigned char)code[0];
+        }
     }
 }
 
@@ -439,6 +526,7 @@ int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const flo
                     float* partials, void* stream) {
     if (dy == nullptr || x == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
     if (dgamma == nullptr || dbeta == nullptr || save_mean == nullptr || save_invstd == nullptr) return MGW_ERR_ARG;
+    const PoolArgs pool = {nullptr, nullptr, 0, 0, 0, 0};
     const int mask1 = !relu ? 0 : (y != nullptr ? 1 : 2);          // mask used by the reduce pass
     const int mask2 = dz != nullptr ? 0 : mask1;                   // apply pass: dz already carries the mask
     const float* gsrc = dz != nullptr ? dz : dy;
@@ -450,13 +538,73 @@ int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const flo
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     if (vec == 4) {
-        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials);
+        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta);
+        bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     } else {
-        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials);
+        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta);
+        bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
+    }
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}
+
+// BatchNorm + ReLU + 3x3/stride-2/pad-1 max-pool of a channels-last [N, H, W, C] tensor (the ResNet / DenseNet stem).
+// Statistics over x as usual; the normalised full-resolution tensor is never written: the second pass pools
+// on the fly and stores [N, OH, OW, C] values plus one byte per value naming the winning tap.
+int mgw_bn_relu_maxpool_fwd(const float* x, float* y_pool, unsigned char* idx, int N, int H, int W, int C, const float* gamma,
+                            const float* beta, float* running_mean, float* running_var, long long* num_batches_tracked,
+                            float momentum, float eps, float* save_mean, float* save_invstd, float* partials, void* stream) {
+    if (x == nullptr || y_pool == nullptr || idx == nullptr || N <= 0 || H <= 0 || W <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
+    const long long M = (long long)N * H * W;
+    const int OH = (H + 2 - 3) / 2 + 1, OW = (W + 2 - 3) / 2 + 1;
+    const int vec = (C % 4 == 0) ? 4 : 1;
+    const Tiling t = make_tiling(M, C, vec);
+    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
+    const dim3 fgrid((C + 31) / 32), fblock(32, 32);
+    const long long work = (long long)N * OH * OW * (C / vec);
+    const int pgrid = (int)((work + 255) / 256 < 148LL * 16 ? (work + 255) / 256 : 148LL * 16);
+    if (vec == 4) {
+        bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
+        bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
+                                                        momentum, eps, save_mean, save_invstd);
+        bn_relu_maxpool_kernel<4><<<pgrid, 256, 0, s>>>(x, y_pool, idx, N, H, W, OH, OW, C, gamma, beta, save_mean, save_invstd);
+    } else {
+        bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
+        bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
+                                                        momentum, eps, save_mean, save_invstd);
+        bn_relu_maxpool_kernel<1><<<pgrid, 256, 0, s>>>(x, y_pool, idx, N, H, W, OH, OW, C, gamma, beta, save_mean, save_invstd);
+    }
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}
+
+// Backward of the above: dp is the gradient of the pooled output; the gradient of the un-pooled ReLU output is
+// gathered from dp / idx inside both BatchNorm passes (never materialised), the ReLU mask is rebuilt from x.
+int mgw_bn_relu_maxpool_bwd(const float* dp, const unsigned char* idx, const float* x, float* dx, int N, int H, int W, int C,
+                            const float* gamma, const float* beta, const float* save_mean, const float* save_invstd,
+                            float* dgamma, float* dbeta, float* partials, void* stream) {
+    if (dp == nullptr || idx == nullptr || x == nullptr || dx == nullptr || partials == nullptr || dgamma == nullptr || dbeta == nullptr)
+        return MGW_ERR_ARG;
+    const long long M = (long long)N * H * W;
+    const PoolArgs pool = {dp, idx, H, W, (H + 2 - 3) / 2 + 1, (W + 2 - 3) / 2 + 1};
+    const int vec = (C % 4 == 0) ? 4 : 1;
+    const Tiling t = make_tiling(M, C, vec);
+    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
+    const dim3 fgrid((C + 31) / 32), fblock(32, 32);
+    if (vec == 4) {
+        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
+        bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
+        bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
+    } else {
+        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
+        bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
+        bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;

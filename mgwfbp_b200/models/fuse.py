@@ -20,7 +20,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops.bn_relu import FusedBatchNorm1d, FusedBatchNorm2d
+from ..ops.bn_relu import FusedBatchNorm1d, FusedBatchNorm2d, bn_relu_maxpool
 
 
 def _to_fused(bn: nn.Module, relu: bool) -> nn.Module:
@@ -59,7 +59,7 @@ def _tv_basicblock_forward(self, x):
 
 
 def _tv_resnet_forward_impl(self, x):
-    x = self.maxpool(self.bn1(self.conv1(x)))
+    x = bn_relu_maxpool(self.bn1, self.maxpool, self.conv1(x))       # stem: BN + ReLU + pool in two passes over x
     x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
     x = x[0] if isinstance(x, tuple) else x
     return self.fc(torch.flatten(self.avgpool(x), 1))
@@ -76,7 +76,11 @@ def _tv_denselayer_forward(self, input):
 
 
 def _tv_densenet_forward(self, x):
-    out = self.features(x)                 # norm5 carries the final ReLU
+    f = self.features
+    out = bn_relu_maxpool(f.norm0, f.pool0, f.conv0(x))            # stem: BN + ReLU + pool fused
+    for name, module in f.named_children():
+        if name not in ('conv0', 'norm0', 'relu0', 'pool0'):
+            out = module(out)                                      # norm5 carries the final ReLU
     out = torch.flatten(F.adaptive_avg_pool2d(out, (1, 1)), 1)
     return self.classifier(out)
 

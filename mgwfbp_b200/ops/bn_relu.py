@@ -152,3 +152,82 @@ class FusedBatchNorm2d(_FusedBNMixin, nn.BatchNorm2d):
 
 class FusedBatchNorm1d(_FusedBNMixin, nn.BatchNorm1d):
     pass
+
+
+# --------------------------------------------------------------------------------------------------
+# BatchNorm + ReLU + MaxPool(3, stride 2, padding 1): the ResNet / DenseNet stem in two passes over x
+# --------------------------------------------------------------------------------------------------
+_pool_declared = False
+
+
+def _declare_pool(lib) -> None:
+    global _pool_declared
+    if not _pool_declared:
+        lib.mgw_bn_relu_maxpool_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                                C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_void_p,
+                                                C.c_void_p, C.c_void_p, C.c_void_p]
+        lib.mgw_bn_relu_maxpool_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                                C.c_void_p]
+        _pool_declared = True
+
+
+class _BNReLUMaxPool(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, running_mean, running_var, num_batches_tracked, momentum, eps):
+        lib = _lib.load(allow_build=False)
+        _declare(lib)
+        _declare_pool(lib)
+        n, c, h, w = x.shape
+        oh, ow = (h - 1) // 2 + 1, (w - 1) // 2 + 1
+        y = torch.empty((n, c, oh, ow), dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+        idx = torch.empty((n, oh, ow, c), dtype=torch.uint8, device=x.device)
+        mean = torch.empty(c, dtype=torch.float32, device=x.device)
+        invstd = torch.empty(c, dtype=torch.float32, device=x.device)
+        partials = torch.empty(lib.mgw_bn_partials_floats(n * h * w, c), dtype=torch.float32, device=x.device)
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.mgw_bn_relu_maxpool_fwd(x.data_ptr(), y.data_ptr(), idx.data_ptr(), n, h, w, c, _ptr(weight), _ptr(bias),
+                                               _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked), float(momentum),
+                                               float(eps), mean.data_ptr(), invstd.data_ptr(), partials.data_ptr(), s),
+                   'bn_relu_maxpool_fwd')
+        counters.bump('bn_relu_maxpool_fwd', 3)
+        ctx.save_for_backward(x, idx, weight, bias, mean, invstd)
+        ctx.mark_non_differentiable(*[t for t in (running_mean, running_var, num_batches_tracked) if t is not None])
+        return y
+
+    @staticmethod
+    def backward(ctx, dp):
+        lib = _lib.load(allow_build=False)
+        x, idx, weight, bias, mean, invstd = ctx.saved_tensors
+        n, c, h, w = x.shape
+        if not dp.is_contiguous(memory_format=torch.channels_last):
+            dp = dp.contiguous(memory_format=torch.channels_last)
+        dx = torch.empty_like(x)
+        dgamma = torch.empty(c, dtype=torch.float32, device=x.device)
+        dbeta = torch.empty(c, dtype=torch.float32, device=x.device)
+        partials = torch.empty(lib.mgw_bn_partials_floats(n * h * w, c), dtype=torch.float32, device=x.device)
+        s = torch.cuda.current_stream().cuda_stream
+        _lib.check(lib.mgw_bn_relu_maxpool_bwd(dp.data_ptr(), idx.data_ptr(), x.data_ptr(), dx.data_ptr(), n, h, w, c, _ptr(weight),
+                                               _ptr(bias), mean.data_ptr(), invstd.data_ptr(), dgamma.data_ptr(), dbeta.data_ptr(),
+                                               partials.data_ptr(), s), 'bn_relu_maxpool_bwd')
+        counters.bump('bn_relu_maxpool_bwd', 3)
+        need = ctx.needs_input_grad
+        return (dx if need[0] else None, dgamma if (weight is not None and need[1]) else None, dbeta if need[2] else None,
+                None, None, None, None, None)
+
+
+def bn_relu_maxpool(bn: torch.nn.BatchNorm2d, pool: torch.nn.MaxPool2d, x: torch.Tensor) -> torch.Tensor:
+    """``pool(relu(bn(x)))`` for a training-mode BatchNorm and a 3x3 / stride 2 / padding 1 max-pool, without ever
+    writing the full-resolution normalised tensor; any other configuration runs the modules one after the other."""
+    def _pair(v):
+        return tuple(v) if isinstance(v, (tuple, list)) else (v, v)
+    fusable = (isinstance(bn, _FusedBNMixin) and bn._native_ok(x) and x.dim() == 4 and x.shape[1] % 4 == 0
+               and _pair(pool.kernel_size) == (3, 3) and _pair(pool.stride) == (2, 2) and _pair(pool.padding) == (1, 1)
+               and _pair(pool.dilation) == (1, 1) and not pool.ceil_mode and not pool.return_indices)
+    if not fusable:
+        out = bn(x)
+        if not getattr(bn, 'fused_relu', False):
+            out = F.relu(out)
+        return pool(out)
+    return _BNReLUMaxPool.apply(x, bn.weight, bn.bias, bn.running_mean, bn.running_var, bn.num_batches_tracked,
+                                bn.momentum, bn.eps)

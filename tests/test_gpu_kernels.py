@@ -282,3 +282,31 @@ def test_bn_relu_dual_output_sums_both_gradients():
     x2.grad = res2.grad = None
     (_bn_reference(x2, w2, b2, *stats()[:2], res2, True, 0.1, 1e-5) * gb).sum().backward()
     torch.testing.assert_close(x.grad, x2.grad, rtol=1e-3, atol=2e-4)
+
+
+@pytest.mark.parametrize('shape', [(2, 16, 12, 12), (3, 64, 17, 15), (2, 8, 7, 9)])
+def test_bn_relu_maxpool_stem_matches_pytorch(shape):
+    from mgwfbp_b200.ops.bn_relu import FusedBatchNorm2d, bn_relu_maxpool
+    torch.manual_seed(0)
+    dev = torch.device('cuda')
+    C_ = shape[1]
+    bn = FusedBatchNorm2d(C_).to(dev)
+    bn.fused_relu = True
+    ref = torch.nn.BatchNorm2d(C_).to(dev)
+    with torch.no_grad():
+        bn.weight.uniform_(0.5, 1.5)
+        bn.bias.normal_()
+    ref.load_state_dict(bn.state_dict())
+    pool = torch.nn.MaxPool2d(3, 2, 1)
+    x = torch.randn(shape, device=dev).contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    x2 = x.detach().clone().requires_grad_(True)
+    y = bn_relu_maxpool(bn, pool, x)
+    y2 = pool(torch.relu(ref(x2)))
+    torch.testing.assert_close(y, y2, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(bn.running_var, ref.running_var, rtol=1e-4, atol=1e-5)
+    g = torch.randn_like(y2)
+    y.backward(g)
+    y2.backward(g)
+    torch.testing.assert_close(x.grad, x2.grad, rtol=1e-3, atol=2e-4)
+    torch.testing.assert_close(bn.weight.grad, ref.weight.grad, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(bn.bias.grad, ref.bias.grad, rtol=1e-3, atol=1e-3)

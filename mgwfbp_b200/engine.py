@@ -65,7 +65,10 @@ class TrainStep:
         t.optimizer.zero_grad()
         loss, outputs, labels, hidden = t.forward_loss(batch, self._hidden, on_device=True)
         if t.dnn == 'lstm':
-            self._hidden = hidden
+            # keep only the values: a live reference into this step's autograd graph would keep its
+            # gradient-accumulator nodes (and their stream) alive into the next step / a later capture
+            from .models.lstm import repackage_hidden
+            self._hidden = repackage_hidden(hidden)
         loss.backward()
         t.optimizer.step()
         return loss.detach()
@@ -81,6 +84,7 @@ class TrainStep:
             # the recurrent state lives in static buffers that the captured step reads and then overwrites
             start = self._hidden if self._hidden is not None else t.net.init_hidden()
             self._static_hidden = tuple(h.detach().clone() for h in start)
+            self._hidden = None
         with torch.cuda.graph(g):
             loss, _o, _l, hid = t.forward_loss(self._static_batch, self._static_hidden, on_device=True)
             loss.backward()

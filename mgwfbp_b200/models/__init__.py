@@ -95,7 +95,7 @@ def create_net(num_classes, dnn='resnet20', fuse=False, channels_last=False, **k
         net, ext = LSTMAN4(datapath=kwargs.get('datapath'))
     elif dnn == 'lstm':
         net = lstm(vocab_size=kwargs['vocab_size'], batch_size=kwargs['batch_size'],
-                   num_steps=kwargs.get('num_steps', 35), fused=fuse)
+                   num_steps=kwargs.get('num_steps', 35), fused=kwargs.get('fused_lstm', False))
     else:
         raise ValueError('Unsupport neural network %s' % dnn)
     if not hasattr(net, 'name'):

@@ -56,6 +56,9 @@ FUSED_UPDATE = _env_flag('FUSED_UPDATE', True)
 
 # Swap BatchNorm+ReLU pairs and LSTMs for this package's fused CUDA modules when a model is built on a GPU.
 FUSE_MODULES = _env_flag('FUSE', True)
+# The PTB model's recurrent part: torch.nn.LSTM (cuDNN's persistent kernels, faster at batch 20) unless this is set,
+# in which case mgwfbp_b200.ops.lstm.FusedLSTM (this package's cell kernels) is used.
+FUSE_LSTM = _env_flag('FUSE_LSTM', False)
 # Keep convolutional models and their inputs in channels-last (NHWC) memory format on the GPU.
 CHANNELS_LAST = _env_flag('CHANNELS_LAST', True)
 

@@ -75,7 +75,8 @@ class DLTrainer:
                 self.data_prepare()
             kwargs = {}
             if dnn == 'lstm':
-                kwargs = dict(vocab_size=self.vocab_size, batch_size=self.batch_size, num_steps=self.num_steps)
+                kwargs = dict(vocab_size=self.vocab_size, batch_size=self.batch_size, num_steps=self.num_steps,
+                              fused_lstm=self.fuse and settings.FUSE_LSTM)
             elif dnn == 'lstman4':
                 kwargs = dict(datapath=None if _is_synthetic(data_dir) else data_dir)
             is_conv = dnn not in ('lstm', 'lstman4', 'fcn5net', 'lr')

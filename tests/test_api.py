@@ -119,7 +119,7 @@ def test_registry_builds_every_name_with_reference_parameter_counts():
 
 def test_lstm_state_dict_keys_match_torch_lstm():
     a, _ = create_net(10, 'lstm', vocab_size=50, batch_size=2)
-    b, _ = create_net(10, 'lstm', vocab_size=50, batch_size=2, fuse=True)
+    b, _ = create_net(10, 'lstm', vocab_size=50, batch_size=2, fused_lstm=True)
     assert list(a.state_dict()) == list(b.state_dict())
     assert 'lstm.weight_ih_l0' in a.state_dict() and 'lstm.bias_hh_l1' in a.state_dict()
     b.load_state_dict(a.state_dict())

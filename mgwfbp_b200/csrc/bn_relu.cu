@@ -53,7 +53,7 @@ struct Tiling {
     int tx, ty, grid_x, grid_y, rows_per_split;
 };
 
-Tiling make_tiling(long long M, int C, int vec) {
+Tiling make_tiling(long long M, int C, int vec, int blocks_per_sm = 4) {
     Tiling t;
     const int lanes = (C + vec - 1) / vec;
     int tx = 1;
@@ -61,7 +61,7 @@ Tiling make_tiling(long long M, int C, int vec) {
     t.tx = tx;
     t.ty = kThreads / tx;
     t.grid_x = (lanes + tx - 1) / tx;
-    const int target_blocks = 148 * 4;
+    const int target_blocks = 148 * blocks_per_sm;            // exactly one resident wave
     long long max_splits = (M + t.ty - 1) / t.ty;
     long long gy = (target_blocks + t.grid_x - 1) / t.grid_x;
     if (gy > max_splits) gy = max_splits;
@@ -102,7 +102,7 @@ __device__ __forceinline__ void block_reduce_rows(float (&a)[VEC], float (&b)[VE
 }
 
 template <int VEC>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int rows_per_split, float* __restrict__ partials) {
     extern __shared__ float smem[];
     const int TY = kThreads / TX;
@@ -199,7 +199,7 @@ bn_bwd_finalize_kernel(const float* __restrict__ partials, int n_splits, int C, 
 }
 
 template <int VEC>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 4)
 bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ residual, float* __restrict__ y, long long M, int C,
                 int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta, int relu,
                 const float* __restrict__ save_mean, const float* __restrict__ save_invstd) {
@@ -310,8 +310,8 @@ __device__ __forceinline__ void load_channel_consts(int c0, int C, const float* 
     }
 }
 
-template <int VEC>
-__global__ void __launch_bounds__(kThreads)
+template <int VEC, bool POOL>
+__global__ void __launch_bounds__(kThreads, 2)
 bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2, const float* __restrict__ y, const float* __restrict__ x,
                      float* __restrict__ dz,
                      long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
@@ -330,35 +330,9 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
     const long long r1 = min(M, r0 + rows_per_split);
     if (active) {
         long long r = r0 + ty;
-        for (; pool.dp == nullptr && r + TY < r1; r += 2LL * TY) {   // two rows per trip: more loads in flight
-            float g0[VEC], g1[VEC], x0[VEC], x1[VEC];
-            load_vec<VEC>(dy + r * C + c0, g0);
-            load_vec<VEC>(dy + (r + TY) * C + c0, g1);
-            load_vec<VEC>(x + r * C + c0, x0);
-            load_vec<VEC>(x + (r + TY) * C + c0, x1);
-            if (dy2) {                                           // the output had two consumers: sum their gradients here
-                float h0[VEC], h1[VEC];
-                load_vec<VEC>(dy2 + r * C + c0, h0);
-                load_vec<VEC>(dy2 + (r + TY) * C + c0, h1);
-#pragma unroll
-                for (int k = 0; k < VEC; ++k) { g0[k] += h0[k]; g1[k] += h1[k]; }
-            }
-            masked_grad<VEC>(g0, x0, mask_mode == 1 ? y + r * C + c0 : nullptr, mask_mode, sc, sh);
-            masked_grad<VEC>(g1, x1, mask_mode == 1 ? y + (r + TY) * C + c0 : nullptr, mask_mode, sc, sh);
-#pragma unroll
-            for (int k = 0; k < VEC; ++k) {
-                s[k] += g0[k] + g1[k];
-                q[k] = fmaf(g0[k], (x0[k] - mean[k]) * istd[k], q[k]);
-                q[k] = fmaf(g1[k], (x1[k] - mean[k]) * istd[k], q[k]);
-            }
-            if (dz) {
-                store_vec<VEC>(dz + r * C + c0, g0);
-                store_vec<VEC>(dz + (r + TY) * C + c0, g1);
-            }
-        }
         for (; r < r1; r += TY) {
             float g[VEC], xv[VEC];
-            if (pool.dp) pooled_grad<VEC>(g, pool, r, c0, C); else load_vec<VEC>(dy + r * C + c0, g);
+            if (POOL) pooled_grad<VEC>(g, pool, r, c0, C); else load_vec<VEC>(dy + r * C + c0, g);
             load_vec<VEC>(x + r * C + c0, xv);
             if (dy2) {
                 float h[VEC];
@@ -389,8 +363,8 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
 }
 
 // gsrc is dz (mask already applied, mask_mode 0) or dy (mask applied here again, mask_mode 1 / 2).
-template <int VEC>
-__global__ void __launch_bounds__(kThreads)
+template <int VEC, bool POOL>
+__global__ void __launch_bounds__(kThreads, 2)
 bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gsrc2, const float* __restrict__ y, const float* __restrict__ x,
                     float* __restrict__ dx,
                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
@@ -413,7 +387,7 @@ bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gs
     const long long r1 = min(M, r0 + rows_per_split);
     for (long long r = r0 + ty; r < r1; r += TY) {
         float g[VEC], xv[VEC], o[VEC];
-        if (pool.dp) pooled_grad<VEC>(g, pool, r, c0, C); else load_vec<VEC>(gsrc + r * C + c0, g);
+        if (POOL) pooled_grad<VEC>(g, pool, r, c0, C); else load_vec<VEC>(gsrc + r * C + c0, g);
         load_vec<VEC>(x + r * C + c0, xv);
         if (gsrc2) {
             float h[VEC];
@@ -532,19 +506,19 @@ int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const flo
     const float* gsrc = dz != nullptr ? dz : dy;
     const float* gsrc2 = dz != nullptr ? nullptr : dy2;        // dz already holds the sum of both gradients
     const int vec = (C % 4 == 0) ? 4 : 1;
-    const Tiling t = make_tiling(M, C, vec);
+    const Tiling t = make_tiling(M, C, vec, 2);      // backward kernels hold 2 blocks per SM
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     if (vec == 4) {
-        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
+        bn_bwd_reduce_kernel<4, false><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<4, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     } else {
-        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
+        bn_bwd_reduce_kernel<1, false><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<1, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
@@ -592,19 +566,19 @@ int mgw_bn_relu_maxpool_bwd(const float* dp, const unsigned char* idx, const flo
     const long long M = (long long)N * H * W;
     const PoolArgs pool = {dp, idx, H, W, (H + 2 - 3) / 2 + 1, (W + 2 - 3) / 2 + 1};
     const int vec = (C % 4 == 0) ? 4 : 1;
-    const Tiling t = make_tiling(M, C, vec);
+    const Tiling t = make_tiling(M, C, vec, 2);      // backward kernels hold 2 blocks per SM
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     if (vec == 4) {
-        bn_bwd_reduce_kernel<4><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
+        bn_bwd_reduce_kernel<4, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<4, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     } else {
-        bn_bwd_reduce_kernel<1><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
+        bn_bwd_reduce_kernel<1, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<1, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;

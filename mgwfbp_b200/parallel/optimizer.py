@@ -347,6 +347,7 @@ class _DistributedMixin:
                         if p.grad is None or p.grad.data_ptr() != view.data_ptr():
                             p.grad = view
             self._handles.clear()
+            self._print_profiling()
         self._synchronized = True
         self.train_iter += 1
 
@@ -361,6 +362,19 @@ class _DistributedMixin:
             params = [p for g in self.param_groups for p in g['params'] if p.grad is not None]
             torch.nn.utils.clip_grad_norm_(params, self._norm_clip)
         return self._local_step(closure)
+
+    def _print_profiling(self) -> None:
+        """Log mean wait / update times per merged group once 40 samples exist (enable with
+        ``optimizer._profiling = True``; unfused data plane only).  Reference ``:407-425``."""
+        ars = self._allreduce_timers
+        if not (self._profiling and runtime.rank() == 0 and ars and len(next(iter(ars.values()))) >= 40):
+            return
+        tar = sum(float(np.mean(v)) for v in ars.values())
+        tup = sum(float(np.mean(v)) for v in self._update_times.values()) if self._update_times else 0.0
+        logger.info('[%d]: Total compress: %f, allreduce: %f, update: %f, total: %f', runtime.rank(), 0.0, tar, tup, tar + tup)
+        self._compression_timers.clear()
+        ars.clear()
+        self._update_times.clear()
 
     def sync_hyper(self) -> None:
         """Push the current ``param_groups`` hyper-parameters to the device tables of the fused

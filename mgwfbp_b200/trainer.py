@@ -185,6 +185,12 @@ class DLTrainer:
     def update_model(self):
         self.optimizer.step()
 
+    def print_weight_gradient_ratio(self):
+        """Weight histograms to the TensorBoard writer, if one was given (rank 0 only)."""
+        if self.rank == 0 and self.writer is not None:
+            for name, param in self.net.named_parameters():
+                self.writer.add_histogram(name, param.detach().cpu().numpy(), self.train_epoch)
+
     def finish(self):
         if self.writer is not None:
             self.writer.close()

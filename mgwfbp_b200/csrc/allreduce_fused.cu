@@ -31,6 +31,8 @@
 
 namespace {
 
+constexpr int kUnroll = 4;      // float4 slots a thread keeps in flight in the streaming loops
+
 struct Smem {
     int failed;
     float red[32];
@@ -100,15 +102,20 @@ __global__ void __launch_bounds__(512) mgw_allreduce_kernel(const MgwAllreduceAr
     if (ALGO == MGW_ALGO_ONESHOT) {
         const size_t row = (size_t)a.inbox_stride;
         const size_t parity_base = (size_t)(e & 1u) * world * row;
-        for (int v = c0 + tid; v < c1; v += nthr) {
-            const float4 x = mgw_load_grad(g, v, hint_l, 1.f);
+        for (int v0 = c0 + tid; v0 < c1; v0 += nthr * kUnroll) {
+            float4 x[kUnroll];
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k)
+                if (v0 + k * nthr < c1) x[k] = mgw_load_grad(g, v0 + k * nthr, hint_l, 1.f);
 #pragma unroll
             for (int i = 0; i < (W > 0 ? W : MGW_MAX_RANKS); ++i) {
                 if (i < world) {
                     int q = a.rank + 1 + i;
                     if (q >= world) q -= world;
                     float4* inbox = reinterpret_cast<float4*>(a.stage[q]) + parity_base + (size_t)a.rank * row;
-                    mgw_st_peer(inbox + v, x);
+#pragma unroll
+                    for (int k = 0; k < kUnroll; ++k)
+                        if (v0 + k * nthr < c1) mgw_st_peer(inbox + v0 + k * nthr, x[k]);
                 }
             }
         }
@@ -125,7 +132,15 @@ __global__ void __launch_bounds__(512) mgw_allreduce_kernel(const MgwAllreduceAr
         }
     } else {
         float4* local = reinterpret_cast<float4*>(a.stage[a.rank]);
-        for (int v = c0 + tid; v < c1; v += nthr) mgw_st_peer(local + v, mgw_load_grad(g, v, hint_l, 1.f));
+        for (int v0 = c0 + tid; v0 < c1; v0 += nthr * kUnroll) {          // several independent loads in flight per thread
+            float4 x[kUnroll];
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k)
+                if (v0 + k * nthr < c1) x[k] = mgw_load_grad(g, v0 + k * nthr, hint_l, 1.f);
+#pragma unroll
+            for (int k = 0; k < kUnroll; ++k)
+                if (v0 + k * nthr < c1) mgw_st_peer(local + v0 + k * nthr, x[k]);
+        }
         ok = rank_barrier(a, 0, e, &sm);
         if (ok) {
             const int sub = per / world;
@@ -158,8 +173,15 @@ __global__ void __launch_bounds__(512) mgw_allreduce_kernel(const MgwAllreduceAr
             ok = rank_barrier(a, 1, e, &sm);
         }
         if (ok) {
-            for (int v = c0 + tid; v < c1; v += nthr)
-                mgw_consume(g, v, mgw_ld_peer(local + v), a.mode, a.hyper, a.first_step, hint_c, sumsq);
+            for (int v0 = c0 + tid; v0 < c1; v0 += nthr * kUnroll) {
+                float4 x[kUnroll];
+#pragma unroll
+                for (int k = 0; k < kUnroll; ++k)
+                    if (v0 + k * nthr < c1) x[k] = mgw_ld_peer(local + v0 + k * nthr);
+#pragma unroll
+                for (int k = 0; k < kUnroll; ++k)
+                    if (v0 + k * nthr < c1) mgw_consume(g, v0 + k * nthr, x[k], a.mode, a.hyper, a.first_step, hint_c, sumsq);
+            }
         }
     }
 

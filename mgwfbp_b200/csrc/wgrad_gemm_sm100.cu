@@ -15,15 +15,16 @@
 // 25088 -> 4096 VGG layer on 8 GPUs), and every rank then runs this same GEMM over K = W*B rows in
 // the same order, so replicas stay bit-identical.
 //
-// Structure of one CTA (192 threads, one 128x128 output tile, two CTAs per SM):
+// Structure of one CTA (320 threads, one 128x128 output tile, three CTAs per SM):
 //   warp 0   : TMA producer.  Per K-block of 32 rows: four 2-D tiled bulk-tensor loads of
 //              [32 rows x 32 floats] for each operand (128-byte swizzle with 32-byte atoms), completing
 //              on an mbarrier.
 //   warp 1   : allocates 128 tensor-memory columns, then one lane issues tcgen05.mma kind::tf32
 //              (M=128, N=128, K=8 per instruction, both operands MN-major from shared memory) and
 //              commits each stage back to the producer and the finished tile to the epilogue.
-//   warps 2-5: epilogue.  tcgen05.ld (32 lanes x 32 columns per warp) -> swizzled shared-memory
-//              slab -> coalesced 128-byte row segments of W / momentum / gradient in global memory.
+//   warps 2-9: epilogue, two warps per tensor-memory lane quarter.  tcgen05.ld (32 lanes x 32 columns)
+//              -> swizzled staging in the (by then idle) operand stages -> 256-byte row segments of
+//              W / momentum / gradient in global memory, optimizer applied in registers.
 // Every mbarrier wait is bounded; on expiry the CTA records an error, lets its outstanding bulk
 // copies land (bounded as well), frees its tensor memory and returns.
 #include <cuda.h>
@@ -38,9 +39,11 @@ constexpr int kRegionBytes = BK * 128;                // one [BK x 32 floats] bo
 constexpr int kAStageBytes = (BM / kAtomFloats) * kRegionBytes;   // 16 KB
 constexpr int kBStageBytes = (BN / kAtomFloats) * kRegionBytes;   // 16 KB
 constexpr int kStageBytes = kAStageBytes + kBStageBytes;
-constexpr int kSlabCols = 32;
-constexpr int kSlabBytes = BM * kSlabCols * 4;        // 16 KB
-constexpr int kSmemBytes = 1024 + kStages * kStageBytes + kSlabBytes + 256;
+constexpr int kEpiWarps = 8;                          // two per tensor-memory lane quarter, 64 columns each
+constexpr int kThreadsPerCta = 64 + 32 * kEpiWarps;   // producer warp + MMA warp + epilogue warps
+constexpr int kEpiWarpFloats = 32 * 64;               // one warp stages 32 rows x 64 columns (8 KB)
+static_assert(kEpiWarps * kEpiWarpFloats * 4 <= kStages * kStageBytes, "epilogue staging reuses the operand stages");
+constexpr int kSmemBytes = 1024 + kStages * kStageBytes + 256;
 constexpr int kTmemCols = 128;
 constexpr uint32_t kWaitSpins = 1u << 22;
 
@@ -53,7 +56,6 @@ struct Params {
     float* grad_out;
     const MgwHyper* hyper;
     int* status;
-    float* debug;              // optional dump of stage 0 and raw accumulators of tile (0,0); null in production
     int M, N, K;
     int mode, pg, first_step;
     float scale;
@@ -139,19 +141,16 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
-__device__ __forceinline__ void epilogue_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
 __device__ __forceinline__ void report(int* status, int code) {
     if (status) atomicCAS(status, 0, code);
 }
 
-__global__ void __launch_bounds__(192)
+__global__ void __launch_bounds__(kThreadsPerCta, 3)
 wgrad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const Params p) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* stages = smem;                                           // kStages x (A | B), 1024-byte aligned
-    float4* slab = reinterpret_cast<float4*>(smem + kStages * kStageBytes);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + kSlabBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
     uint64_t* full = bars;                     // [kStages]
     uint64_t* empty = bars + kStages;          // [kStages]
     uint64_t* acc_ready = bars + 2 * kStages;  // [1]
@@ -227,58 +226,56 @@ wgrad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             umma_commit(acc_ready);              // arrives when every MMA issued above has completed
         }
     } else {
-        // ---------------- epilogue (warps 2..5) ----------------
-        const int q = warp & 3;                  // tensor-memory lane quarter this warp may read
-        const int et = threadIdx.x - 64;         // 0..127
+        // ---------------- epilogue (warps 2..9) ----------------
+        // Warp w may read tensor-memory lanes 32*(w%4)..+31, i.e. 32 rows of the tile; two warps share a lane
+        // quarter and split the 128 columns.  Once the accumulator is complete every MMA has finished reading
+        // the operand stages, so each warp reuses 8 KB of them to turn its rows (one thread = one row out of
+        // tensor memory) into 256-byte row segments (16 threads = one row segment) for global memory.
+        const int q = warp & 3;
+        const int half = (warp - 2) >> 2;
+        float4* wsm = reinterpret_cast<float4*>(stages) + (size_t)(warp - 2) * (kEpiWarpFloats / 4);
         bool ok = mbar_wait(acc_ready, 0);
         if (!ok) { report(p.status, 13); *failed = 1; }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        MgwHyper h;
-        if (p.mode & WG_MODE_SGD) h = p.hyper[p.pg];
-        if (p.debug != nullptr && blockIdx.x == 0 && blockIdx.y == 0) {
-            if (et == 0) { p.debug[0] = __uint_as_float(tmem_base); p.debug[1] = (float)num_kb; }
-            const float* st = reinterpret_cast<const float*>(stages);
-            for (int i = et; i < kStageBytes / 4; i += 128) p.debug[16 + i] = st[i];
-            float v[32];
-            tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16), v);
-            for (int j = 0; j < 8; ++j) p.debug[16 + kStageBytes / 4 + (q * 32 + lane) * 8 + j] = v[j];
-        }
-        for (int sc = 0; sc < BN / kSlabCols; ++sc) {
-            if (ok && !*failed) {
-                float v[32];
-                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(sc * kSlabCols), v);
-                const int r = q * 32 + lane;     // row of the tile held by this thread
+        if (ok && !*failed) {
+            MgwHyper h;
+            if (p.mode & WG_MODE_SGD) h = p.hyper[p.pg];
 #pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    slab[r * 8 + (c ^ (r & 7))] = make_float4(v[4 * c] * p.scale, v[4 * c + 1] * p.scale, v[4 * c + 2] * p.scale, v[4 * c + 3] * p.scale);
+            for (int cb = 0; cb < 2; ++cb) {
+                float v[32];
+                tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(half * 64 + cb * 32), v);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int chunk = cb * 8 + c;
+                    wsm[lane * 16 + (chunk ^ (lane & 7))] =
+                        make_float4(v[4 * c] * p.scale, v[4 * c + 1] * p.scale, v[4 * c + 2] * p.scale, v[4 * c + 3] * p.scale);
+                }
             }
-            epilogue_bar();
-            if (ok && !*failed) {
-                const int c = et & 7;
-                const int n = n0 + sc * kSlabCols + 4 * c;
+            __syncwarp();
+            const int ch = lane & 15;
+            const int n = n0 + half * 64 + 4 * ch;
+            const bool use_m = (p.mode & WG_MODE_SGD) && p.mom != nullptr && h.momentum != 0.f;
 #pragma unroll 4
-                for (int r = et >> 3; r < BM; r += 16) {
-                    const int m = m0 + r;
-                    if (m < p.M && n < p.N) {
-                        float4 g = slab[r * 8 + (c ^ (r & 7))];
-                        const size_t off = (size_t)m * p.N + n;
-                        if (p.mode & WG_MODE_STORE) *reinterpret_cast<float4*>(p.grad_out + off) = g;
-                        if (p.mode & WG_MODE_SGD) {
-                            float4 w = *reinterpret_cast<float4*>(p.weight + off);
-                            const bool use_m = p.mom != nullptr && h.momentum != 0.f;
-                            float4 mo = make_float4(0.f, 0.f, 0.f, 0.f);
-                            if (use_m && !p.first_step) mo = *reinterpret_cast<float4*>(p.mom + off);
-                            mgw_sgd_scalar(g.x, w.x, use_m ? &mo.x : nullptr, h, p.first_step);
-                            mgw_sgd_scalar(g.y, w.y, use_m ? &mo.y : nullptr, h, p.first_step);
-                            mgw_sgd_scalar(g.z, w.z, use_m ? &mo.z : nullptr, h, p.first_step);
-                            mgw_sgd_scalar(g.w, w.w, use_m ? &mo.w : nullptr, h, p.first_step);
-                            *reinterpret_cast<float4*>(p.weight + off) = w;
-                            if (use_m) *reinterpret_cast<float4*>(p.mom + off) = mo;
-                        }
+            for (int i = 0; i < 16; ++i) {
+                const int rr = 2 * i + (lane >> 4);
+                const int m = m0 + q * 32 + rr;
+                if (m < p.M && n < p.N) {
+                    float4 g = wsm[rr * 16 + (ch ^ (rr & 7))];
+                    const size_t off = (size_t)m * p.N + n;
+                    if (p.mode & WG_MODE_STORE) *reinterpret_cast<float4*>(p.grad_out + off) = g;
+                    if (p.mode & WG_MODE_SGD) {
+                        float4 w = *reinterpret_cast<float4*>(p.weight + off);
+                        float4 mo = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (use_m && !p.first_step) mo = *reinterpret_cast<float4*>(p.mom + off);
+                        mgw_sgd_scalar(g.x, w.x, use_m ? &mo.x : nullptr, h, p.first_step);
+                        mgw_sgd_scalar(g.y, w.y, use_m ? &mo.y : nullptr, h, p.first_step);
+                        mgw_sgd_scalar(g.z, w.z, use_m ? &mo.z : nullptr, h, p.first_step);
+                        mgw_sgd_scalar(g.w, w.w, use_m ? &mo.w : nullptr, h, p.first_step);
+                        *reinterpret_cast<float4*>(p.weight + off) = w;
+                        if (use_m) *reinterpret_cast<float4*>(p.mom + off) = mo;
                     }
                 }
             }
-            epilogue_bar();
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
@@ -376,12 +373,10 @@ int mgw_wgrad_gemm_supported(const void* dy, const void* x, int M, int N, int K)
     return 1;
 }
 
-// `debug` (may be null): >= 16 + 8192 + 1024 floats that receive tile (0,0)'s first operand stage and raw
-// accumulator columns, for bring-up.
 // dy: [K, M], x: [K, N] row-major fp32.  mode bit 1: grad_out[M, N] = scale * dy^T x;
 // mode bit 2: momentum-SGD on (weight, mom) with hyper[pg].  status: one device-visible int (0 = ok).
-int mgw_wgrad_gemm_debug(const float* dy, const float* x, int M, int N, int K, float scale, int mode, float* grad_out, float* weight,
-                         float* mom, const MgwHyper* hyper, int pg, int first_step, int* status, float* debug, void* stream) {
+int mgw_wgrad_gemm(const float* dy, const float* x, int M, int N, int K, float scale, int mode, float* grad_out, float* weight,
+                   float* mom, const MgwHyper* hyper, int pg, int first_step, int* status, void* stream) {
     if (!mgw_wgrad_gemm_supported(dy, x, M, N, K)) return MGW_ERR_ARG;
     if ((mode & WG_MODE_STORE) && grad_out == nullptr) return MGW_ERR_ARG;
     if ((mode & WG_MODE_SGD) && (weight == nullptr || hyper == nullptr)) return MGW_ERR_ARG;
@@ -397,17 +392,12 @@ int mgw_wgrad_gemm_debug(const float* dy, const float* x, int M, int N, int K, f
         configured = true;
     }
     Params p;
-    p.weight = weight; p.mom = mom; p.grad_out = grad_out; p.hyper = hyper; p.status = status; p.debug = debug;
+    p.weight = weight; p.mom = mom; p.grad_out = grad_out; p.hyper = hyper; p.status = status;
     p.M = M; p.N = N; p.K = K; p.mode = mode; p.pg = pg; p.first_step = first_step; p.scale = scale;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-    wgrad_gemm_kernel<<<grid, 192, kSmemBytes, (cudaStream_t)stream>>>(map_a, map_b, p);
+    wgrad_gemm_kernel<<<grid, kThreadsPerCta, kSmemBytes, (cudaStream_t)stream>>>(map_a, map_b, p);
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
-}
-
-int mgw_wgrad_gemm(const float* dy, const float* x, int M, int N, int K, float scale, int mode, float* grad_out, float* weight,
-                   float* mom, const MgwHyper* hyper, int pg, int first_step, int* status, void* stream) {
-    return mgw_wgrad_gemm_debug(dy, x, M, N, K, scale, mode, grad_out, weight, mom, hyper, pg, first_step, status, nullptr, stream);
 }
 
 // flags: every rank's flag block (same layout and size as mgw_flag_block_bytes()); epoch: local [MGW_MAX_CTAS] counters.

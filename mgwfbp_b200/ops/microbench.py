@@ -89,8 +89,8 @@ def bench_bn(args, timer):
     report('bn_relu_fwd[%dx%d]' % (M, Cc), timer(fwd), nbytes=(3 + (1 if args.residual else 0)) * nb)
     dy = torch.randn(M, Cc, device='cuda')
 
-    def bwd():
-        y[0].backward(dy, retain_graph=True)
+    def bwd():          # autograd.grad: no accumulation into leaf .grad tensors, only the kernels under test
+        torch.autograd.grad(y[0], [x, w, b], dy, retain_graph=True)
     report('bn_relu_bwd[%dx%d]' % (M, Cc), timer(bwd), nbytes=5 * nb)
 
 

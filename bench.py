@@ -203,6 +203,16 @@ def run_ours(args):
     ms_e2e = hvd.parallel.runtime.max_over_ranks(ms_e2e) if world > 1 else ms_e2e
     final_loss = step.last_loss()
 
+    if args.timeline:
+        # after the timed region: three more steps under the CUPTI activity tracer, one chrome-trace file per rank
+        # (kernel name, stream, start, duration), the evidence for what overlaps what inside a replayed step
+        from torch.profiler import profile, ProfilerActivity
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for i in range(3):
+                step_device(i)
+            torch.cuda.synchronize()
+        prof.export_chrome_trace('%s.rank%d.json' % (args.timeline, rank))
+
     exposed = comm_ms = None
     if world > 1 and getattr(optimizer, '_fused_comm', False):
         # exposed communication = end of the last communication kernel minus end of backward (>= 0), eager steps
@@ -399,6 +409,8 @@ def main():
     ap.add_argument('--batch-size', type=int, default=None, help='per-GPU batch (default: the workload\'s)')
     ap.add_argument('--policy', choices=['mgwfbp', 'wfbp', 'single'], default='mgwfbp')
     ap.add_argument('--no-graph', action='store_true', help='do not capture the training step in a CUDA graph')
+    ap.add_argument('--timeline', default=None, metavar='PREFIX',
+                    help='after timing, trace three steps and write PREFIX.rank<r>.json (chrome trace of every kernel)')
     ap.add_argument('--skip-e2e', action='store_true', help='profiling aid: time only the device-resident loop')
     ap.add_argument('--profiler-range', action='store_true',
                     help='profiling aid: bracket the timed device loop with cudaProfilerStart/Stop (ncu --profile-from-start off)')

@@ -80,11 +80,20 @@ __device__ __forceinline__ void multimem_st(float4* mc, float4 v) {
 }
 
 // W > 0: world size known at compile time (loops unroll); W == 0: read it from the arguments.
+//
+// Slot mapping of the streaming loops: per iteration a CTA covers blockDim.x * U consecutive slots,
+// warp w of it the 32 * U slots starting at w * 32 * U, and a lane the U slots `lane + 32 k` of
+// those, so every warp request is one contiguous 512-byte line group and the U slots of a thread
+// lie within 1.5 KB of one another (the span that must fall inside one tensor for the table-free path).
 template <int W, int ALGO>
-__global__ void __launch_bounds__(512) mgw_allreduce_kernel(const MgwAllreduceArgs a) {
+__global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduceArgs a) {
+    constexpr int WW = W > 0 ? W : MGW_MAX_RANKS;
+    constexpr int U = kUnroll;                                  // pack / consume: one operand stream per slot
+    constexpr int UR = W == 2 ? 4 : (W == 4 ? 2 : 1);           // reduce: W peer loads per slot, keep ~8 in flight
     __shared__ Smem sm;
     const int world = W > 0 ? W : a.world;
     const int tid = threadIdx.x, nthr = blockDim.x, b = blockIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
     if (tid == 0) sm.failed = 0;
     const uint32_t e = a.epoch[b] + 1u;
     const MgwGroup& g = a.group;
@@ -95,51 +104,64 @@ __global__ void __launch_bounds__(512) mgw_allreduce_kernel(const MgwAllreduceAr
     per = (per + world - 1) / world * world;
     const int c0 = min(g.n_vec, b * per);
     const int c1 = min(g.n_vec, c0 + per);
-    int hint_l = -1, hint_c = -1;
     float sumsq = 0.f;
-    bool ok = true;
+    // checked build: the chunk must lie inside the region the host sized; otherwise this CTA does nothing
+    bool ok = MGW_CHECK(c1 <= (ALGO == MGW_ALGO_ONESHOT ? a.inbox_stride : a.stage_slots), MGW_BOUNDS_STAGE, c1,
+                        ALGO == MGW_ALGO_ONESHOT ? a.inbox_stride : a.stage_slots, 0);
 
-    if (ALGO == MGW_ALGO_ONESHOT) {
+    if (!ok) {
+        // fall through to the epoch update
+    } else if (ALGO == MGW_ALGO_ONESHOT) {
         const size_t row = (size_t)a.inbox_stride;
         const size_t parity_base = (size_t)(e & 1u) * world * row;
-        for (int v0 = c0 + tid; v0 < c1; v0 += nthr * kUnroll) {
-            float4 x[kUnroll];
+        MgwCursor cl = mgw_cursor();
+        for (int v0 = c0 + warp * 32 * U + lane; v0 < c1; v0 += nthr * U) {
+            float4 x[U];
+            mgw_load_grad_batch<U>(g, v0, 32, c1, cl, 1.f, x);
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k)
-                if (v0 + k * nthr < c1) x[k] = mgw_load_grad(g, v0 + k * nthr, hint_l, 1.f);
-#pragma unroll
-            for (int i = 0; i < (W > 0 ? W : MGW_MAX_RANKS); ++i) {
+            for (int i = 0; i < WW; ++i) {
                 if (i < world) {
                     int q = a.rank + 1 + i;
                     if (q >= world) q -= world;
                     float4* inbox = reinterpret_cast<float4*>(a.stage[q]) + parity_base + (size_t)a.rank * row;
 #pragma unroll
-                    for (int k = 0; k < kUnroll; ++k)
-                        if (v0 + k * nthr < c1) mgw_st_peer(inbox + v0 + k * nthr, x[k]);
+                    for (int k = 0; k < U; ++k)
+                        if (v0 + k * 32 < c1) mgw_st_peer(inbox + v0 + k * 32, x[k]);
                 }
             }
         }
         ok = rank_barrier(a, 0, e, &sm);
         if (ok) {
             const float4* mine = reinterpret_cast<const float4*>(a.stage[a.rank]) + parity_base;
-            for (int v = c0 + tid; v < c1; v += nthr) {
-                float4 acc = mgw_ld_peer(mine + v);
+            MgwCursor cc = mgw_cursor();
+            for (int v0 = c0 + warp * 32 * UR + lane; v0 < c1; v0 += nthr * UR) {
+                float4 x[UR][WW];
 #pragma unroll
-                for (int s = 1; s < (W > 0 ? W : MGW_MAX_RANKS); ++s)
-                    if (s < world) acc = add4(acc, mgw_ld_peer(mine + (size_t)s * row + v));
-                mgw_consume(g, v, scale4(acc, inv), a.mode, a.hyper, a.first_step, hint_c, sumsq);
+                for (int k = 0; k < UR; ++k)
+#pragma unroll
+                    for (int s = 0; s < WW; ++s)
+                        if (s < world && v0 + k * 32 < c1) x[k][s] = mgw_ld_peer(mine + (size_t)s * row + v0 + k * 32);
+                float4 acc[UR];
+#pragma unroll
+                for (int k = 0; k < UR; ++k) {
+                    acc[k] = x[k][0];
+#pragma unroll
+                    for (int s = 1; s < WW; ++s)
+                        if (s < world) acc[k] = add4(acc[k], x[k][s]);
+                    acc[k] = scale4(acc[k], inv);
+                }
+                mgw_consume_batch<UR>(g, v0, 32, c1, cc, acc, a.mode, a.hyper, a.first_step, sumsq);
             }
         }
     } else {
         float4* local = reinterpret_cast<float4*>(a.stage[a.rank]);
-        for (int v0 = c0 + tid; v0 < c1; v0 += nthr * kUnroll) {          // several independent loads in flight per thread
-            float4 x[kUnroll];
+        MgwCursor cl = mgw_cursor();
+        for (int v0 = c0 + warp * 32 * U + lane; v0 < c1; v0 += nthr * U) {
+            float4 x[U];
+            mgw_load_grad_batch<U>(g, v0, 32, c1, cl, 1.f, x);
 #pragma unroll
-            for (int k = 0; k < kUnroll; ++k)
-                if (v0 + k * nthr < c1) x[k] = mgw_load_grad(g, v0 + k * nthr, hint_l, 1.f);
-#pragma unroll
-            for (int k = 0; k < kUnroll; ++k)
-                if (v0 + k * nthr < c1) mgw_st_peer(local + v0 + k * nthr, x[k]);
+            for (int k = 0; k < U; ++k)
+                if (v0 + k * 32 < c1) mgw_st_peer(local + v0 + k * 32, x[k]);
         }
         ok = rank_barrier(a, 0, e, &sm);
         if (ok) {
@@ -148,24 +170,40 @@ __global__ void __launch_bounds__(512) mgw_allreduce_kernel(const MgwAllreduceAr
             const int s1 = min(c1, s0 + sub);
             if (ALGO == MGW_ALGO_NVLS) {
                 float4* mc = reinterpret_cast<float4*>(a.mc_stage);
-                for (int v = s0 + tid; v < s1; v += nthr) multimem_st(mc + v, scale4(multimem_ld_reduce(mc + v), inv));
+                for (int v0 = s0 + warp * 32 * U + lane; v0 < s1; v0 += nthr * U) {
+                    float4 x[U];
+#pragma unroll
+                    for (int k = 0; k < U; ++k)
+                        if (v0 + k * 32 < s1) x[k] = multimem_ld_reduce(mc + v0 + k * 32);
+#pragma unroll
+                    for (int k = 0; k < U; ++k)
+                        if (v0 + k * 32 < s1) multimem_st(mc + v0 + k * 32, scale4(x[k], inv));
+                }
             } else {
-                for (int v = s0 + tid; v < s1; v += nthr) {
-                    float4 x[W > 0 ? W : MGW_MAX_RANKS];
+                for (int v0 = s0 + warp * 32 * UR + lane; v0 < s1; v0 += nthr * UR) {
+                    float4 x[UR][WW];
 #pragma unroll
-                    for (int q = 0; q < (W > 0 ? W : MGW_MAX_RANKS); ++q)
-                        if (q < world) x[q] = mgw_ld_peer(reinterpret_cast<const float4*>(a.stage[q]) + v);
-                    float4 acc = x[0];
+                    for (int k = 0; k < UR; ++k)
 #pragma unroll
-                    for (int q = 1; q < (W > 0 ? W : MGW_MAX_RANKS); ++q)
-                        if (q < world) acc = add4(acc, x[q]);
-                    acc = scale4(acc, inv);
+                        for (int q = 0; q < WW; ++q)
+                            if (q < world && v0 + k * 32 < s1)
+                                x[k][q] = mgw_ld_peer(reinterpret_cast<const float4*>(a.stage[q]) + v0 + k * 32);
 #pragma unroll
-                    for (int i = 0; i < (W > 0 ? W : MGW_MAX_RANKS); ++i) {
+                    for (int k = 0; k < UR; ++k) {
+                        float4 acc = x[k][0];
+#pragma unroll
+                        for (int q = 1; q < WW; ++q)
+                            if (q < world) acc = add4(acc, x[k][q]);
+                        x[k][0] = scale4(acc, inv);
+                    }
+#pragma unroll
+                    for (int i = 0; i < WW; ++i) {
                         if (i < world) {
                             int q = a.rank + 1 + i;
                             if (q >= world) q -= world;
-                            mgw_st_peer(reinterpret_cast<float4*>(a.stage[q]) + v, acc);
+#pragma unroll
+                            for (int k = 0; k < UR; ++k)
+                                if (v0 + k * 32 < s1) mgw_st_peer(reinterpret_cast<float4*>(a.stage[q]) + v0 + k * 32, x[k][0]);
                         }
                     }
                 }
@@ -173,14 +211,13 @@ __global__ void __launch_bounds__(512) mgw_allreduce_kernel(const MgwAllreduceAr
             ok = rank_barrier(a, 1, e, &sm);
         }
         if (ok) {
-            for (int v0 = c0 + tid; v0 < c1; v0 += nthr * kUnroll) {
-                float4 x[kUnroll];
+            MgwCursor cc = mgw_cursor();
+            for (int v0 = c0 + warp * 32 * U + lane; v0 < c1; v0 += nthr * U) {
+                float4 x[U];
 #pragma unroll
-                for (int k = 0; k < kUnroll; ++k)
-                    if (v0 + k * nthr < c1) x[k] = mgw_ld_peer(local + v0 + k * nthr);
-#pragma unroll
-                for (int k = 0; k < kUnroll; ++k)
-                    if (v0 + k * nthr < c1) mgw_consume(g, v0 + k * nthr, x[k], a.mode, a.hyper, a.first_step, hint_c, sumsq);
+                for (int k = 0; k < U; ++k)
+                    if (v0 + k * 32 < c1) x[k] = mgw_ld_peer(local + v0 + k * 32);
+                mgw_consume_batch<U>(g, v0, 32, c1, cc, x, a.mode, a.hyper, a.first_step, sumsq);
             }
         }
     }
@@ -207,6 +244,8 @@ cudaError_t launch_world(const MgwAllreduceArgs& a, cudaStream_t s) {
 
 }  // namespace
 
+MGW_DEFINE_BOUNDS_READER(mgw_bounds_allreduce)
+
 extern "C" size_t mgw_flag_block_bytes(void) {
     return sizeof(uint32_t) * 2 * MGW_MAX_CTAS * MGW_MAX_RANKS;
 }
@@ -226,7 +265,8 @@ extern "C" int mgw_allreduce_group(const MgwAllreduceArgs* args, void* stream) {
     if ((a.mode & MGW_MODE_SUMSQ) && a.sumsq_partials == nullptr) return MGW_ERR_ARG;
     if ((a.mode & MGW_MODE_UPDATE) && a.hyper == nullptr) return MGW_ERR_ARG;
     if (a.algo == MGW_ALGO_NVLS && a.mc_stage == nullptr) return MGW_ERR_ARG;
-    if (a.algo == MGW_ALGO_ONESHOT && a.inbox_stride < a.group.n_vec) return MGW_ERR_ARG;
+    if (a.algo == MGW_ALGO_ONESHOT && a.inbox_stride < a.group.n_vec) return MGW_ERR_TOO_LARGE;
+    if (a.algo != MGW_ALGO_ONESHOT && a.stage_slots < a.group.n_vec) return MGW_ERR_TOO_LARGE;
     for (int r = 0; r < a.world; ++r)
         if (a.stage[r] == nullptr || a.flags[r] == nullptr) return MGW_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;

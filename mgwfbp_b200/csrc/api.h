@@ -39,11 +39,15 @@ typedef struct {
     int algo, n_ctas, n_threads;
     int mode, first_step;
     int inbox_stride;                   // one-shot: float4 slots between consecutive inbox rows (>= n_vec)
-    int reserved;
+    int stage_slots;                    // two-shot / NVLS: float4 slots the staging area holds (>= n_vec)
     unsigned long long timeout_ns;
 } MgwAllreduceArgs;
 
 int mgw_allreduce_group(const MgwAllreduceArgs* args, void* stream);
+// Checked build only (-DMGW_CHECKED): first index violation recorded by the kernels of allreduce_fused.cu /
+// multi_tensor_sgd.cu as {code, a, b, c, block, thread, 0, 0} (MGW_BOUNDS_*), cleared by the call.  All zeros otherwise.
+int mgw_bounds_allreduce(int* out8);
+int mgw_bounds_sgd(int* out8);
 size_t mgw_flag_block_bytes(void);
 // staging bytes one rank needs for a group of n_vec float4 slots under `algo`
 size_t mgw_stage_bytes(int algo, int n_vec, int world);

@@ -4,7 +4,7 @@
 #include <stdint.h>
 
 #define MGW_MAX_RANKS 16
-#define MGW_MAX_CTAS 64
+#define MGW_MAX_CTAS 128
 #define MGW_MAX_PARAM_GROUPS 16
 
 // return codes of the host entry points
@@ -61,7 +61,50 @@ struct MgwGroup {
 #define MGW_MODE_WRITEBACK 2   // store the averaged gradient back into the gradient tensors
 #define MGW_MODE_SUMSQ 4       // emit one partial sum of squares of the averaged gradient per CTA
 
+// codes of the checked build's bounds word (MGW_CHECKED, see below)
+#define MGW_BOUNDS_SLOT 1       // a float4 slot index outside [0, n_vec)                     {slot, n_vec}
+#define MGW_BOUNDS_TENSOR 2     // the tensor found for a slot does not contain it              {slot, tensor}
+#define MGW_BOUNDS_TABLE 3      // voff[] and numel of a tensor disagree                        {tensor, numel, slots}
+#define MGW_BOUNDS_ELEMENT 4    // a slot starts at or beyond its tensor's last element         {slot, tensor, numel}
+#define MGW_BOUNDS_STAGE 5      // a staging / inbox index beyond the region the host sized     {slot, capacity}
+
 #ifdef __CUDACC__
+
+// ---- checked build ----------------------------------------------------------------------------------------
+// Compiled with -DMGW_CHECKED (libmgwfbp_b200_checked.so) the table-driven kernels verify every index they
+// derive from a group table before using it.  A violation is recorded once per translation unit in
+// g_mgw_bounds {code, a, b, c, block, thread} and the access is SKIPPED, so a wrong table costs a wrong
+// result and a report, never a fault.  Without the macro the checks compile to nothing.
+#ifdef MGW_CHECKED
+static __device__ int g_mgw_bounds[8];
+__device__ __forceinline__ bool mgw_checked(bool ok, int code, int a, int b, int c) {
+    if (ok) return true;
+    if (atomicCAS(&g_mgw_bounds[0], 0, code) == 0) {
+        g_mgw_bounds[1] = a; g_mgw_bounds[2] = b; g_mgw_bounds[3] = c;
+        g_mgw_bounds[4] = blockIdx.x; g_mgw_bounds[5] = threadIdx.x;
+    }
+    return false;
+}
+#define MGW_CHECK(cond, code, a, b, c) mgw_checked((cond), (code), (a), (b), (c))
+// Host reader of this translation unit's word: out8 receives the record, which is then cleared.
+#define MGW_DEFINE_BOUNDS_READER(fn)                                                        \
+    extern "C" int fn(int* out8) {                                                          \
+        if (out8 == nullptr) return MGW_ERR_ARG;                                            \
+        MGW_CUDA_CHECK(cudaDeviceSynchronize());                                            \
+        MGW_CUDA_CHECK(cudaMemcpyFromSymbol(out8, g_mgw_bounds, 8 * sizeof(int)));          \
+        const int zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};                                       \
+        MGW_CUDA_CHECK(cudaMemcpyToSymbol(g_mgw_bounds, zero, sizeof(zero)));               \
+        return MGW_OK;                                                                      \
+    }
+#else
+#define MGW_CHECK(cond, code, a, b, c) (true)
+#define MGW_DEFINE_BOUNDS_READER(fn)                                  \
+    extern "C" int fn(int* out8) {                                    \
+        if (out8 == nullptr) return MGW_ERR_ARG;                      \
+        for (int i = 0; i < 8; ++i) out8[i] = 0;                      \
+        return MGW_OK;                                                \
+    }
+#endif
 
 __device__ __forceinline__ uint64_t mgw_globaltimer_ns() {
     uint64_t t;
@@ -135,10 +178,13 @@ __device__ __forceinline__ int mgw_find_tensor(const int* __restrict__ voff, int
 
 // Load the four gradient values of slot v (zero beyond the tensor's end).
 __device__ __forceinline__ float4 mgw_load_grad(const MgwGroup& g, int v, int& t_hint, float scale) {
+    if (!MGW_CHECK(v >= 0 && v < g.n_vec, MGW_BOUNDS_SLOT, v, g.n_vec, 0)) return make_float4(0.f, 0.f, 0.f, 0.f);
     const int t = mgw_find_tensor(g.voff, g.n_tensors, v, t_hint);
     t_hint = t;
+    if (!MGW_CHECK(g.voff[t] <= v && v < g.voff[t + 1], MGW_BOUNDS_TENSOR, v, t, 0)) return make_float4(0.f, 0.f, 0.f, 0.f);
     const int e0 = (v - g.voff[t]) << 2;
     const int n = g.tensors[t].numel;
+    if (!MGW_CHECK(e0 < n, MGW_BOUNDS_ELEMENT, v, t, n)) return make_float4(0.f, 0.f, 0.f, 0.f);
     const float* src = g.grads[t];
     float4 r;
     if (e0 + 4 <= n) {
@@ -168,11 +214,14 @@ __device__ __forceinline__ float mgw_sgd_scalar(float g, float& w, float* mom_sl
 // update, optional sum of squares.
 __device__ __forceinline__ void mgw_consume(const MgwGroup& g, int v, float4 avg, int mode, const MgwHyper* hyper,
                                             int first_step, int& t_hint, float& sumsq) {
+    if (!MGW_CHECK(v >= 0 && v < g.n_vec, MGW_BOUNDS_SLOT, v, g.n_vec, 0)) return;
     const int t = mgw_find_tensor(g.voff, g.n_tensors, v, t_hint);
     t_hint = t;
+    if (!MGW_CHECK(g.voff[t] <= v && v < g.voff[t + 1], MGW_BOUNDS_TENSOR, v, t, 0)) return;
     const MgwTensor te = g.tensors[t];
     const int e0 = (v - g.voff[t]) << 2;
     const int n = te.numel;
+    if (!MGW_CHECK(e0 < n, MGW_BOUNDS_ELEMENT, v, t, n)) return;
     const bool full = e0 + 4 <= n;
     if (mode & MGW_MODE_SUMSQ) {
         // padded lanes hold exact zeros, so they do not disturb the sum
@@ -213,6 +262,123 @@ __device__ __forceinline__ void mgw_consume(const MgwGroup& g, int v, float4 avg
                     wp[k] = w;
                 }
             }
+        }
+    }
+}
+
+// ---- batched streaming access -------------------------------------------------------------------------
+// A thread walks slots v0, v0 + stride, ..., v0 + (U-1) * stride per iteration.  MgwCursor caches the
+// tensor that owns them; while all U slots are whole float4s of that one tensor (the common case
+// for convolution and linear weights) the loads of a batch are issued back to back with no table
+// lookups in between, so U independent 16-byte requests per operand are in flight per thread.
+
+struct MgwCursor {
+    int t;         // cached tensor index (-1: nothing cached yet)
+    int vbeg;      // its first slot
+    int vfull;     // first slot not entirely inside the tensor: vbeg + numel / 4
+    int vend;      // first slot of the next tensor
+    int numel, pg;
+    float* grad;
+    float* param;
+    float* mom;
+};
+
+__device__ __forceinline__ MgwCursor mgw_cursor() {
+    MgwCursor c;
+    c.t = -1; c.vbeg = 0; c.vfull = 0; c.vend = 0; c.numel = 0; c.pg = 0;
+    c.grad = nullptr; c.param = nullptr; c.mom = nullptr;
+    return c;
+}
+
+__device__ __forceinline__ void mgw_seek(const MgwGroup& g, int v, MgwCursor& c) {
+    const int t = mgw_find_tensor(g.voff, g.n_tensors, v, c.t + 1);      // walking forward: the next tensor is the likely one
+    const MgwTensor te = g.tensors[t];
+    c.t = t;
+    c.vbeg = g.voff[t];
+    c.vend = g.voff[t + 1];
+    c.numel = te.numel;
+    c.vfull = c.vbeg + (te.numel >> 2);
+    c.pg = te.pg;
+    c.grad = g.grads[t];
+    c.param = te.param;
+    c.mom = te.mom;
+    if (!MGW_CHECK(c.vbeg <= v && v < c.vend && c.vbeg + ((te.numel + 3) >> 2) == c.vend, MGW_BOUNDS_TABLE, t, te.numel,
+                   c.vend - c.vbeg))
+        c.vfull = c.vbeg;            // no slot qualifies for the table-free path; the per-slot path re-checks each one
+}
+
+// True when slots v0 .. v0 + (U-1) * stride are all below `vlimit` and whole float4s of one tensor; positions the cursor.
+template <int U>
+__device__ __forceinline__ bool mgw_batch_is_plain(const MgwGroup& g, int v0, int stride, int vlimit, MgwCursor& c) {
+    const int vl = v0 + (U - 1) * stride;
+    if (vl >= vlimit) return false;
+    if (v0 < c.vbeg || v0 >= c.vend) mgw_seek(g, v0, c);
+    return vl < c.vfull;
+}
+
+template <int U>
+__device__ __forceinline__ void mgw_load_grad_batch(const MgwGroup& g, int v0, int stride, int vlimit, MgwCursor& c,
+                                                    float scale, float4 (&x)[U]) {
+    if (mgw_batch_is_plain<U>(g, v0, stride, vlimit, c)) {
+        const float4* src = reinterpret_cast<const float4*>(c.grad) + (v0 - c.vbeg);
+#pragma unroll
+        for (int k = 0; k < U; ++k) x[k] = src[k * stride];
+#pragma unroll
+        for (int k = 0; k < U; ++k) { x[k].x *= scale; x[k].y *= scale; x[k].z *= scale; x[k].w *= scale; }
+    } else {
+        int hint = c.t;
+#pragma unroll
+        for (int k = 0; k < U; ++k)
+            if (v0 + k * stride < vlimit) x[k] = mgw_load_grad(g, v0 + k * stride, hint, scale);
+    }
+}
+
+template <int U>
+__device__ __forceinline__ void mgw_consume_batch(const MgwGroup& g, int v0, int stride, int vlimit, MgwCursor& c,
+                                                  const float4 (&x)[U], int mode, const MgwHyper* hyper, int first_step,
+                                                  float& sumsq) {
+    if (!mgw_batch_is_plain<U>(g, v0, stride, vlimit, c)) {
+        int hint = c.t;
+#pragma unroll
+        for (int k = 0; k < U; ++k)
+            if (v0 + k * stride < vlimit) mgw_consume(g, v0 + k * stride, x[k], mode, hyper, first_step, hint, sumsq);
+        return;
+    }
+    const int off = v0 - c.vbeg;
+    if (mode & MGW_MODE_SUMSQ) {
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            sumsq = fmaf(x[k].x, x[k].x, sumsq); sumsq = fmaf(x[k].y, x[k].y, sumsq);
+            sumsq = fmaf(x[k].z, x[k].z, sumsq); sumsq = fmaf(x[k].w, x[k].w, sumsq);
+        }
+    }
+    if (mode & MGW_MODE_WRITEBACK) {
+        float4* dst = reinterpret_cast<float4*>(c.grad) + off;
+#pragma unroll
+        for (int k = 0; k < U; ++k) dst[k * stride] = x[k];
+    }
+    if (mode & MGW_MODE_UPDATE) {
+        const MgwHyper h = hyper[c.pg];
+        float4* wp = reinterpret_cast<float4*>(c.param) + off;
+        float4* mp = reinterpret_cast<float4*>(c.mom) + off;
+        const bool use_m = (c.mom != nullptr) && h.momentum != 0.f;
+        float4 w[U], m[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) w[k] = wp[k * stride];
+#pragma unroll
+        for (int k = 0; k < U; ++k) m[k] = (use_m && !first_step) ? mp[k * stride] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+            mgw_sgd_scalar(x[k].x, w[k].x, use_m ? &m[k].x : nullptr, h, first_step);
+            mgw_sgd_scalar(x[k].y, w[k].y, use_m ? &m[k].y : nullptr, h, first_step);
+            mgw_sgd_scalar(x[k].z, w[k].z, use_m ? &m[k].z : nullptr, h, first_step);
+            mgw_sgd_scalar(x[k].w, w[k].w, use_m ? &m[k].w : nullptr, h, first_step);
+        }
+#pragma unroll
+        for (int k = 0; k < U; ++k) wp[k * stride] = w[k];
+        if (use_m) {
+#pragma unroll
+            for (int k = 0; k < U; ++k) mp[k * stride] = m[k];
         }
     }
 }

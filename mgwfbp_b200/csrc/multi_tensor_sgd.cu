@@ -4,7 +4,8 @@
 // from device memory, so no host round trip separates the norm from the update).
 #include "api.h"
 
-__global__ void __launch_bounds__(512)
+template <int U, int MIN_BLOCKS>                          // U: float4 slots per operand a thread keeps in flight
+__global__ void __launch_bounds__(512, MIN_BLOCKS)
 mgw_multi_tensor_sgd_kernel(MgwGroup g, const MgwHyper* __restrict__ hyper, const float* __restrict__ clip_coef,
                             float grad_scale, int first_step, int mode, float* __restrict__ sumsq_partials) {
     __shared__ float red[32];
@@ -13,11 +14,13 @@ mgw_multi_tensor_sgd_kernel(MgwGroup g, const MgwHyper* __restrict__ hyper, cons
     const int per = (g.n_vec + gridDim.x - 1) / gridDim.x;
     const int c0 = blockIdx.x * per;
     const int c1 = min(g.n_vec, c0 + per);
-    int hint_l = -1, hint_c = -1;
     float sumsq = 0.f;
-    for (int v = c0 + threadIdx.x; v < c1; v += blockDim.x) {
-        float4 x = mgw_load_grad(g, v, hint_l, scale);
-        mgw_consume(g, v, x, mode, hyper, first_step, hint_c, sumsq);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    MgwCursor cur = mgw_cursor();
+    for (int v0 = c0 + warp * 32 * U + lane; v0 < c1; v0 += blockDim.x * U) {
+        float4 x[U];
+        mgw_load_grad_batch<U>(g, v0, 32, c1, cur, scale, x);
+        mgw_consume_batch<U>(g, v0, 32, c1, cur, x, mode, hyper, first_step, sumsq);
     }
     if (mode & MGW_MODE_SUMSQ) {
         float r = mgw_block_sum(sumsq, red);
@@ -43,11 +46,13 @@ extern "C" int mgw_multi_tensor_sgd(const MgwGroup* group, const MgwHyper* hyper
     if (group == nullptr || group->n_vec < 0 || n_ctas <= 0) return MGW_ERR_ARG;
     if ((mode & MGW_MODE_SUMSQ) && sumsq_partials == nullptr) return MGW_ERR_ARG;
     if (group->n_vec == 0) return MGW_OK;
-    mgw_multi_tensor_sgd_kernel<<<n_ctas, 512, 0, (cudaStream_t)stream>>>(*group, hyper, clip_coef, grad_scale, first_step,
-                                                                           mode, sumsq_partials);
+    mgw_multi_tensor_sgd_kernel<2, 2><<<n_ctas, 512, 0, (cudaStream_t)stream>>>(*group, hyper, clip_coef, grad_scale, first_step,
+                                                                                 mode, sumsq_partials);
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
 }
+
+MGW_DEFINE_BOUNDS_READER(mgw_bounds_sgd)
 
 extern "C" int mgw_group_sumsq(const MgwGroup* group, float* partials, int n_ctas, void* stream) {
     return mgw_multi_tensor_sgd(group, nullptr, nullptr, 1.f, 0, MGW_MODE_SUMSQ, partials, n_ctas, stream);
@@ -93,7 +98,7 @@ extern "C" int mgw_grad_clip_coef_static(const MgwGroup* group, float max_norm, 
     float* partials = g_static_partials_addr[dev];
     cudaStream_t s = (cudaStream_t)stream;
     if (group->n_vec == 0) n_ctas = 1;
-    mgw_multi_tensor_sgd_kernel<<<n_ctas, 512, 0, s>>>(*group, nullptr, nullptr, 1.f, 0, MGW_MODE_SUMSQ, partials);
+    mgw_multi_tensor_sgd_kernel<2, 2><<<n_ctas, 512, 0, s>>>(*group, nullptr, nullptr, 1.f, 0, MGW_MODE_SUMSQ, partials);
     MGW_CUDA_CHECK(cudaGetLastError());
     mgw_clip_coef_kernel<<<1, 32, 0, s>>>(partials, n_ctas, max_norm, out2);
     MGW_CUDA_CHECK(cudaGetLastError());

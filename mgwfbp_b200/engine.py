@@ -23,6 +23,7 @@ import torch
 from .ops import counters
 from .parallel.costmodel import PiecewiseAlphaBeta, fit_piecewise
 from .parallel import runtime
+from . import settings
 from .settings import logger
 
 
@@ -33,7 +34,7 @@ class TrainStep:
         self.trainer = trainer
         self.optimizer = trainer.optimizer
         self.cuda = trainer.is_cuda
-        self.want_graph = bool(use_graph and self.cuda and trainer.dnn != 'lstman4')
+        self.want_graph = bool(use_graph and self.cuda and trainer.dnn != 'lstman4' and settings.SHADOW_EVERY <= 0)
         self._static_hidden = None
         self.graphed = False
         self._graph: Optional[torch.cuda.CUDAGraph] = None

@@ -11,10 +11,10 @@ import ctypes as C
 import os
 from typing import Optional
 
-from .build import LIB_PATH, build
+from .build import CHECKED_LIB_PATH, LIB_PATH, build
 
 MAX_RANKS = 16
-MAX_CTAS = 64
+MAX_CTAS = 128
 MAX_PARAM_GROUPS = 16
 
 MODE_UPDATE, MODE_WRITEBACK, MODE_SUMSQ = 1, 2, 4
@@ -39,7 +39,7 @@ class MgwAllreduceArgs(C.Structure):
                 ('rank', C.c_int), ('world', C.c_int),
                 ('algo', C.c_int), ('n_ctas', C.c_int), ('n_threads', C.c_int),
                 ('mode', C.c_int), ('first_step', C.c_int),
-                ('inbox_stride', C.c_int), ('reserved', C.c_int),
+                ('inbox_stride', C.c_int), ('stage_slots', C.c_int),
                 ('timeout_ns', C.c_ulonglong)]
 
 
@@ -68,6 +68,8 @@ def _declare(lib: C.CDLL) -> None:
                                          C.c_void_p, C.c_int, C.c_void_p]
     lib.mgw_clip_coef.argtypes = [C.c_void_p, C.c_int, C.c_float, C.c_void_p, C.c_void_p]
     lib.mgw_group_sumsq.argtypes = [C.POINTER(MgwGroup), C.c_void_p, C.c_int, C.c_void_p]
+    lib.mgw_bounds_allreduce.argtypes = [C.POINTER(C.c_int)]
+    lib.mgw_bounds_sgd.argtypes = [C.POINTER(C.c_int)]
     for name in ('mgw_bn_relu_fwd', 'mgw_bn_relu_bwd', 'mgw_lstm_cell_fwd', 'mgw_lstm_cell_bwd',
                  'mgw_wgrad_gemm', 'mgw_wgrad_gemm_supported', 'mgw_allgather_rows'):
         if hasattr(lib, name):
@@ -79,22 +81,49 @@ def load(allow_build: Optional[bool] = None) -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.isfile(LIB_PATH):
+    checked = is_checked()
+    path = CHECKED_LIB_PATH if checked else LIB_PATH
+    if not os.path.isfile(path):
         if allow_build is None:
             allow_build = os.environ.get('MGWFBP_BUILD_ON_IMPORT', '1') != '0'
         if not allow_build:
-            raise NativeLibraryError('%s is missing; run `python -m mgwfbp_b200.ops.build`' % LIB_PATH)
+            raise NativeLibraryError('%s is missing; run `python -m mgwfbp_b200.ops.build%s`' % (path, ' --checked' if checked else ''))
         try:
-            build()
+            build(checked=checked)
         except Exception as e:
-            raise NativeLibraryError('could not build %s: %s' % (LIB_PATH, e)) from e
+            raise NativeLibraryError('could not build %s: %s' % (path, e)) from e
     try:
-        lib = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+        lib = C.CDLL(path, mode=C.RTLD_GLOBAL)
     except OSError as e:
-        raise NativeLibraryError('could not load %s: %s' % (LIB_PATH, e)) from e
+        raise NativeLibraryError('could not load %s: %s' % (path, e)) from e
     _declare(lib)
     _lib = lib
     return lib
+
+
+def is_checked() -> bool:
+    """True when this process runs the checked build (``MGWFBP_CHECKED=1``): the table-driven kernels verify
+    every index they derive from a group table, record the first violation and skip the access."""
+    return os.environ.get('MGWFBP_CHECKED', '0').strip().lower() not in ('0', '', 'false', 'no', 'off')
+
+
+BOUNDS_CODES = {1: 'slot index outside the group', 2: 'slot not inside the tensor found for it',
+                3: 'offset table and element count of a tensor disagree', 4: 'slot starts beyond the tensor\'s last element',
+                5: 'staging index beyond the sized region'}
+
+
+def bounds_report() -> list:
+    """Violations recorded by the checked build since the last call, one dict per translation unit that saw one
+    (always empty in the normal build).  Synchronizes the device."""
+    lib = load()
+    out = []
+    for unit, fn in (('allreduce_fused', lib.mgw_bounds_allreduce), ('multi_tensor_sgd', lib.mgw_bounds_sgd)):
+        rec = (C.c_int * 8)()
+        check(fn(rec), 'bounds report')
+        if rec[0]:
+            out.append({'unit': unit, 'code': rec[0], 'what': BOUNDS_CODES.get(rec[0], '?'), 'values': [rec[1], rec[2], rec[3]],
+                        'block': rec[4], 'thread': rec[5]})
+    return out
 
 
 def check(code: int, what: str = 'native call') -> None:

@@ -22,7 +22,7 @@ def _stream_ptr() -> int:
 
 
 class FastSGD:
-    MAX_CTAS = 592           # 148 SMs x 4 resident 512-thread CTAs
+    MAX_CTAS = 296           # 148 SMs x 2 resident 512-thread CTAs
 
     def __init__(self, optimizer, params: List[torch.Tensor], norm_clip: Optional[float] = None):
         self.lib = _lib.load()

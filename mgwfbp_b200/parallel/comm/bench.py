@@ -7,7 +7,9 @@
 For every message size: device time (CUDA events on the launching stream, max over ranks) of this
 package's one-shot / two-shot / NVLS kernels (reduce + 1/N + write-back, launched on the side stream)
 and of ``torch.distributed.all_reduce`` (NCCL), the algorithm bandwidth ``S / t`` and the bus
-bandwidth ``2 (N-1)/N * S / t``.  Ends with the fitted ``alpha + beta * bytes`` per algorithm, the
+bandwidth ``2 (N-1)/N * S / t``.  The ``iters`` calls of one measurement are captured into a CUDA
+graph and replayed, as the training step does with its own launches, so the figures are device
+times free of the host's launch path (``--eager`` times back-to-back host launches instead).  Ends with the fitted ``alpha + beta * bytes`` per algorithm, the
 quantities the MG-WFBP scheduler consumes (the reference hard-codes them for its authors' Ethernet /
 InfiniBand clusters, ``distributed_optimizer.py:166-177``).  Rank 0 prints a JSON document.
 """
@@ -39,11 +41,44 @@ def _time(fn, iters: int, barrier) -> float:
     return runtime.max_over_ranks(e0.elapsed_time(e1) / iters)
 
 
+def _time_graph(fn, iters: int, barrier) -> float:
+    """Device time per call of ``fn`` replayed from a CUDA graph; falls back to :func:`_time` when
+    any rank could not capture (the decision is taken collectively, so ranks never diverge)."""
+    side = torch.cuda.Stream()
+    graph = None
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    try:
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=side):
+            for _ in range(iters):
+                fn()
+        graph = g
+    except Exception:                                      # capture refused: time the eager launches
+        graph = None
+    torch.cuda.synchronize()
+    if not all(runtime.allgather_object(graph is not None)):
+        return _time(fn, iters, barrier)
+    graph.replay()
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    graph.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return runtime.max_over_ranks(e0.elapsed_time(e1) / iters)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument('--max-mb', type=float, default=256.0)
     ap.add_argument('--iters', type=int, default=20)
+    ap.add_argument('--eager', action='store_true', help='time host-launched calls instead of a graph replay')
+    ap.add_argument('--out', default=None, help='also write the JSON document to this file')
     args = ap.parse_args(argv)
+    timeit = _time if args.eager else _time_graph
     runtime.init()
     settings.logger.setLevel('WARNING')
     from .nvl import NvlComm
@@ -58,12 +93,12 @@ def main(argv=None):
         for algo in algos:
             if algo == 'oneshot' and 4 * n > comm.oneshot_max_bytes:
                 continue
-            ms = _time(lambda: comm.synchronize(comm.allreduce_async_(x, algo=algo)), args.iters, runtime.barrier)
+            ms = timeit(lambda: comm.synchronize(comm.allreduce_async_(x, algo=algo)), args.iters, runtime.barrier)
             row[algo + '_us'] = ms * 1e3
             samples.setdefault(algo, ([], []))
             samples[algo][0].append(n)
             samples[algo][1].append(ms * 1e-3)
-        ms = _time(lambda: dist.all_reduce(x, op=dist.ReduceOp.AVG), args.iters, runtime.barrier)
+        ms = timeit(lambda: dist.all_reduce(x, op=dist.ReduceOp.AVG), args.iters, runtime.barrier)
         row['nccl_us'] = ms * 1e3
         samples.setdefault('nccl', ([], []))
         samples['nccl'][0].append(n)
@@ -80,7 +115,12 @@ def main(argv=None):
             fits[algo] = {'alpha_us': ab.alpha * 1e6, 'beta_s_per_byte': ab.beta,
                           'asymptotic_algbw_GBps': (1e-9 / ab.beta) if ab.beta > 0 else None}
     if rank == 0:
-        print(json.dumps({'world': world, 'heap': os.environ.get('MGWFBP_HEAP', 'ipc'), 'rows': rows, 'fits': fits}))
+        doc = json.dumps({'world': world, 'heap': os.environ.get('MGWFBP_HEAP', 'ipc'), 'timing': 'eager' if args.eager else 'graph',
+                          'twoshot_ctas': comm.max_ctas_twoshot, 'threads': comm.n_threads, 'rows': rows, 'fits': fits})
+        print(doc)
+        if args.out:
+            with open(args.out, 'w') as f:
+                f.write(doc)
     runtime.shutdown()
 
 

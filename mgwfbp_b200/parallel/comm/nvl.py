@@ -231,7 +231,7 @@ class NvlComm(Communicator):
         return algo, n_ctas
 
     def _fill_args(self, plan: _GroupPlan, heap, hyper_ptr: int, partials_ptr: int,
-                   inbox_stride: Optional[int] = None) -> None:
+                   inbox_stride: Optional[int] = None, stage_slots: Optional[int] = None) -> None:
         a = _lib.MgwAllreduceArgs()
         a.group = plan.table.struct
         for r in range(self._world):
@@ -246,6 +246,7 @@ class NvlComm(Communicator):
         a.algo, a.n_ctas, a.n_threads = plan.algo, plan.n_ctas, self.n_threads
         a.mode, a.first_step = 0, 0
         a.inbox_stride = plan.table.n_vec if inbox_stride is None else inbox_stride
+        a.stage_slots = plan.table.n_vec if stage_slots is None else stage_slots
         a.timeout_ns = self.timeout_ns
         plan.args = a
 
@@ -370,7 +371,7 @@ class NvlComm(Communicator):
                                                       opt._nvl_clip_out.data_ptr(), s), 'clip_coef')
                     clip_ptr = opt._nvl_clip_out.data_ptr() + 4
                     counters.bump('clip_coef')
-                n_ctas = max(1, min(592, (table.n_vec + 2047) // 2048))
+                n_ctas = max(1, min(296, (table.n_vec + 2047) // 2048))
                 _lib.check(self.lib.mgw_multi_tensor_sgd(C.byref(table.struct), self._hyper[id(opt)].data_ptr(), clip_ptr,
                                                          1.0, int(opt._nvl_first_step), _lib.MODE_UPDATE, None, n_ctas, s),
                            'multi_tensor_sgd')
@@ -505,7 +506,7 @@ class NvlComm(Communicator):
         if n_ctas is not None:
             plan.n_ctas = n_ctas
         plan.stage_off = sc['os_off'] if plan.algo == _lib.ALGO_ONESHOT else sc['ts_off']
-        self._fill_args(plan, sc['heap'], 0, 0, inbox_stride=sc['os_cap'])
+        self._fill_args(plan, sc['heap'], 0, 0, inbox_stride=sc['os_cap'], stage_slots=sc['ts_cap'])
         compute = torch.cuda.current_stream()
         ready = torch.cuda.Event()
         ready.record(compute)

@@ -106,6 +106,10 @@ class _DistributedMixin:
         want_fused = settings.FUSED_UPDATE if fused_update is None else bool(fused_update)
         self._fused_comm = bool(getattr(self._comm, 'fused', False))
         self._fused_update = bool(want_fused and self._fused_comm and self._base_is_sgd and norm_clip is None)
+        self._shadow = None
+        if settings.SHADOW_EVERY > 0 and self._fused_comm and self._base_is_sgd:
+            from ..utils.consistency import ShadowChecker
+            self._shadow = ShadowChecker(settings.SHADOW_EVERY)
 
         # Large linear layers fed by small batches exchange activations instead of weight gradients
         # (mgwfbp_b200.ops.wgrad.GatheredWgradLinear); their weights leave the merge schedule.
@@ -282,6 +286,8 @@ class _DistributedMixin:
                 self._group_missing[gi] -= 1
                 if self._group_missing[gi] == 0:
                     self._group_missing[gi] = len(self._groups[gi])
+                    if self._shadow is not None and self._shadow.active(self.train_iter):
+                        self._shadow.snapshot(self, self._groups[gi], getattr(self, '_nvl_first_step', False))
                     self._comm.launch_group(self, gi)
                     self._groups_pending.append(gi)
                 return
@@ -355,7 +361,10 @@ class _DistributedMixin:
         if self._active and not self.local:
             self.synchronize()
             if self._fused_comm:
-                return self._comm.finish_step(self, closure)
+                loss = self._comm.finish_step(self, closure)
+                if self._shadow is not None:
+                    self._shadow.verify(self)
+                return loss
         if self._norm_clip is not None and not self.local and getattr(self, '_fast_sgd', None) is None:
             # global L2-norm clip of the averaged gradient (the reference's loop calls
             # clip_grad_norm_ between synchronize() and step(), dist_trainer.py:89-94)

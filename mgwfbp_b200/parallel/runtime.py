@@ -151,6 +151,15 @@ def barrier() -> None:
         dist.barrier(group=_state['control_group'])
 
 
+def allgather_tensor(t: torch.Tensor) -> List[torch.Tensor]:
+    """All ranks' copies of a CPU tensor of equal shape, in rank order, over the control plane."""
+    if size() == 1:
+        return [t]
+    out = [torch.empty_like(t) for _ in range(size())]
+    dist.all_gather(out, t.contiguous(), group=_state['control_group'])
+    return out
+
+
 def max_over_ranks(value: float) -> float:
     """Max of a host scalar over all ranks (multi-GPU timings are reported as the slowest rank)."""
     if size() == 1:

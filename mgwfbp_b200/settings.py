@@ -69,6 +69,12 @@ GATHERED_WGRAD = _env_flag('GATHERED_WGRAD', True)
 # After the fused kernels ran, leave the averaged gradient readable in ``p.grad``.
 WRITE_BACK_GRADS = _env_flag('WRITE_BACK_GRADS', True)
 
+# Every SHADOW_EVERY-th iteration the fused data plane is checked against a slow path: local gradients, parameters
+# and momenta are snapshotted before each group is launched, averaged over the CPU control plane and the update is
+# redone in plain PyTorch (utils/consistency.py, ShadowChecker).  0 = off.  Training steps are not graph-captured
+# while this is on.
+SHADOW_EVERY = int(_env_str('SHADOW', '0') or 0)
+
 # 'auto' | 'oneshot' | 'twoshot' | 'nvls'
 COMM_ALGO = _env_str('COMM_ALGO', 'auto')
 

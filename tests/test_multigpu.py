@@ -87,6 +87,50 @@ def test_fused_data_parallel_equals_large_batch(policy, fused):
             assert torch.equal(a, b), 'replicas diverged'
 
 
+def _shadowed_training(rank, world, clip):
+    """The fused path re-checked every second iteration by the slow path (gradients over gloo, update in PyTorch);
+    then one snapshot is altered on the host and the check must name the tensor."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
+    from mgwfbp_b200.utils.consistency import ShadowMismatchError
+    settings.ADAPTIVE_MERGE = False
+    settings.SHADOW_EVERY = 2
+    torch.manual_seed(0)
+    net = torch.nn.Sequential(torch.nn.Linear(64, 301), torch.nn.ReLU(), torch.nn.Linear(301, 10)).cuda()
+    hvd.broadcast_parameters(net.state_dict(), 0)
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(net.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4, nesterov=True),
+                                   named_parameters=net.named_parameters(), threshold=20000, norm_clip=clip)
+    assert opt._shadow is not None
+    g = torch.Generator().manual_seed(5 + rank)
+    for _ in range(5):
+        opt.zero_grad()
+        net(torch.randn(16, 64, generator=g).cuda()).pow(2).mean().backward()
+        opt.step()
+    checked = opt._shadow.checked
+    # iteration 6 (index 5) is unchecked; on iteration 7 spoil the first snapshot before verify runs
+    opt.zero_grad(); net(torch.randn(16, 64, generator=g).cuda()).pow(2).mean().backward(); opt.step()
+    opt.zero_grad(); net(torch.randn(16, 64, generator=g).cuda()).pow(2).mean().backward()
+    opt.synchronize()
+    name, grad, w, buf, first = opt._shadow._snap[0]
+    opt._shadow._snap[0] = (name, grad + 1.0, w, buf, first)
+    try:
+        opt.step()
+        caught = None
+    except ShadowMismatchError as e:
+        caught = str(e)
+    torch.cuda.synchronize()
+    opt.communicator.check_status()
+    return checked, caught, name
+
+
+@pytest.mark.parametrize('clip', [None, 0.25])
+def test_shadow_path_agrees_and_detects_a_spoiled_snapshot(clip):
+    res = run_ranks(_shadowed_training, (clip,), world=_world())
+    for checked, caught, name in res:
+        assert checked == 3 * 4                 # iterations 0, 2, 4; four tensors each
+        assert caught is not None and name in caught
+
+
 def _gathered_wgrad(rank, world):
     """A large linear layer fed by a small batch: its weight is updated from gathered activations by
     the tensor-core GEMM with the SGD epilogue and never enters the gradient all-reduce."""

@@ -139,7 +139,7 @@ def run_ours(args):
     if world > 1 and args.policy == 'mgwfbp':
         seq, times, _sizes = profile_backward(trainer, warmup=3, iteration=10)
         times = hvd.broadcast_object(list(times), 0)
-    threshold = {'mgwfbp': 0, 'wfbp': 0, 'single': 524288000}[args.policy]
+    threshold = {'mgwfbp': 0, 'wfbp': 0, 'single': 524288000, 'bucket': args.threshold}[args.policy]
     norm_clip = 0.25 if args.dnn == 'lstm' else None
     cost_model = None
     if world > 1 and args.policy == 'mgwfbp' and not args.no_comm_fit:
@@ -248,7 +248,7 @@ def run_ours(args):
             'data': 'synthetic', 'impl': 'ours',
             'config': {'model': args.dnn, 'global_batch': world * bs, 'per_gpu_batch': bs,
                        'seq_len': 35 if args.dnn == 'lstm' else None, 'parallelism': 'dp%d' % world,
-                       'policy': args.policy, 'cuda_graph': step.graphed,
+                       'policy': args.policy + ('(%d)' % args.threshold if args.policy == 'bucket' else ''), 'cuda_graph': step.graphed,
                        'optimizer': 'sgd momentum 0.9 wd 1e-4' if dataset != 'ptb' else 'sgd lr 22 clip 0.25',
                        'groups': len(optimizer.merge_schedule.groups),
                        'l2': 'per-step working set (activations + weights, > 1 GB) exceeds the 126 MB L2; no explicit flush'},
@@ -339,7 +339,7 @@ def run_reference(args):
         box = [list(times)]
         torch.distributed.broadcast_object_list(box, src=0)
         times = box[0]
-    threshold = {'mgwfbp': 0, 'wfbp': 0, 'single': 524288000}[args.policy]
+    threshold = {'mgwfbp': 0, 'wfbp': 0, 'single': 524288000, 'bucket': args.threshold}[args.policy]
     from compression import compressors
     optimizer = hvd.DistributedOptimizer(trainer.optimizer, named_parameters=trainer.net.named_parameters(),
                                          compression=compressors[None], seq_layernames=seq, layerwise_times=times,
@@ -407,7 +407,9 @@ def main():
     ap.add_argument('--impl', choices=['ours', 'reference'], default='ours')
     ap.add_argument('--dnn', choices=sorted(WORKLOADS), default='resnet50')
     ap.add_argument('--batch-size', type=int, default=None, help='per-GPU batch (default: the workload\'s)')
-    ap.add_argument('--policy', choices=['mgwfbp', 'wfbp', 'single'], default='mgwfbp')
+    ap.add_argument('--policy', choices=['mgwfbp', 'wfbp', 'single', 'bucket'], default='mgwfbp',
+                    help="merge policy: MG-WFBP schedule, one message per tensor, one message in all, or fixed-size buckets")
+    ap.add_argument('--threshold', type=int, default=8 * 1024 * 1024, help="bucket size in elements for --policy bucket")
     ap.add_argument('--no-graph', action='store_true', help='do not capture the training step in a CUDA graph')
     ap.add_argument('--timeline', default=None, metavar='PREFIX',
                     help='after timing, trace three steps and write PREFIX.rank<r>.json (chrome trace of every kernel)')

@@ -21,7 +21,6 @@
 // All of it is bandwidth-bound; the second pass of each direction re-reads tensors that the first
 // pass just streamed, which the 126 MB L2 serves for the smaller layers.
 #include "api.h"
-#include <cstdlib>
 
 namespace {
 
@@ -74,18 +73,6 @@ Tiling make_tiling(long long M, int C, int vec, int blocks_per_sm = 4) {
     t.rows_per_split = (int)rps;
     t.grid_y = (int)((M + rps - 1) / rps);
     return t;
-}
-
-// The elementwise (apply) passes need no partial sums, so they may be cut finer than one resident wave: when a
-// communication kernel holds some SMs, a one-wave grid leaves the displaced blocks for a second, mostly empty
-// wave, while a grid of `waves` x as many smaller blocks only slows down in proportion to the SMs it lost.
-int apply_waves() {
-    static const int w = [] {
-        const char* e = getenv("MGW_BN_APPLY_WAVES");
-        const int v = e ? atoi(e) : 1;
-        return v < 1 ? 1 : (v > 16 ? 16 : v);
-    }();
-    return w;
 }
 
 // Sum `a` and `b` over the TY rows of the block in a fixed order; valid in threads with ty == 0.
@@ -484,8 +471,6 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
     const int vec = (C % 4 == 0) ? 4 : 1;
     const Tiling t = make_tiling(M, C, vec);
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
-    const Tiling ta = make_tiling(M, C, vec, 4 * apply_waves());      // finer cut for the elementwise pass
-    const dim3 agrid(ta.grid_x, ta.grid_y);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
@@ -493,12 +478,12 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
         bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
         bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
                                                         momentum, eps, save_mean, save_invstd);
-        bn_apply_kernel<4><<<agrid, block, 0, s>>>(x, residual, y, M, C, ta.tx, ta.rows_per_split, gamma, beta, relu, save_mean, save_invstd);
+        bn_apply_kernel<4><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd);
     } else {
         bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
         bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
                                                         momentum, eps, save_mean, save_invstd);
-        bn_apply_kernel<1><<<agrid, block, 0, s>>>(x, residual, y, M, C, ta.tx, ta.rows_per_split, gamma, beta, relu, save_mean, save_invstd);
+        bn_apply_kernel<1><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
@@ -523,19 +508,17 @@ int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const flo
     const int vec = (C % 4 == 0) ? 4 : 1;
     const Tiling t = make_tiling(M, C, vec, 2);      // backward kernels hold 2 blocks per SM
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
-    const Tiling ta = make_tiling(M, C, vec, 2 * apply_waves());      // finer cut for the elementwise pass
-    const dim3 agrid(ta.grid_x, ta.grid_y);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     if (vec == 4) {
         bn_bwd_reduce_kernel<4, false><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4, false><<<agrid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, ta.tx, ta.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<4, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     } else {
         bn_bwd_reduce_kernel<1, false><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1, false><<<agrid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, ta.tx, ta.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<1, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
@@ -553,8 +536,6 @@ int mgw_bn_relu_maxpool_fwd(const float* x, float* y_pool, unsigned char* idx, i
     const int vec = (C % 4 == 0) ? 4 : 1;
     const Tiling t = make_tiling(M, C, vec);
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
-    const Tiling ta = make_tiling(M, C, vec, 4 * apply_waves());      // finer cut for the elementwise pass
-    const dim3 agrid(ta.grid_x, ta.grid_y);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
@@ -587,19 +568,17 @@ int mgw_bn_relu_maxpool_bwd(const float* dp, const unsigned char* idx, const flo
     const int vec = (C % 4 == 0) ? 4 : 1;
     const Tiling t = make_tiling(M, C, vec, 2);      // backward kernels hold 2 blocks per SM
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
-    const Tiling ta = make_tiling(M, C, vec, 2 * apply_waves());      // finer cut for the elementwise pass
-    const dim3 agrid(ta.grid_x, ta.grid_y);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     if (vec == 4) {
         bn_bwd_reduce_kernel<4, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4, true><<<agrid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, ta.tx, ta.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<4, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     } else {
         bn_bwd_reduce_kernel<1, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1, true><<<agrid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, ta.tx, ta.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<1, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;

@@ -6,6 +6,7 @@ measured roofline (``MEASURED_PEAKS.json`` at the repository root when present).
     python -m mgwfbp_b200.ops.microbench sgd   --numel 25557032
     python -m mgwfbp_b200.ops.microbench wgrad --k 64 --m 4096 --n 25088 [--sgd]
     python -m mgwfbp_b200.ops.microbench pack  --numel 25557032          # fused all-reduce kernel, world size 1
+    python -m mgwfbp_b200.ops.microbench fused                            # all of ResNet-50 as one group: all-reduce + SGD
 
 Timing: CUDA events on the launching stream, ``--warmup`` untimed launches, a write larger than L2
 between timed launches, median of ``--iters``.  The same commands (with ``--iters 1 --warmup 1``)
@@ -147,9 +148,37 @@ def bench_pack(args, timer):
     comm.check_status(synchronize=True)
 
 
+def bench_fused(args, timer):
+    """The whole gradient set of ResNet-50 as ONE merged group through the fused all-reduce + SGD kernel at world
+    size 1 (pack, staging, self-barriers, 1/N, update): the kernel's streaming rate without any NVLink traffic.
+    Algorithmic bytes: gradient read, parameter and momentum read + write (+ gradient write-back when enabled)."""
+    import torchvision
+    from .. import settings
+    import mgwfbp_b200 as hvd
+    from ..parallel.comm.nvl import NvlComm
+    comm = NvlComm.shared()
+    net = torchvision.models.resnet50().cuda()
+    opt = hvd.DistributedOptimizer(torch.optim.SGD(net.parameters(), lr=0.01, momentum=0.9, weight_decay=1e-4),
+                                   named_parameters=net.named_parameters(), threshold=1 << 40, comm=comm)
+    assert opt._fused_comm and opt._fused_update and len(opt._groups) == 1
+    n = 0
+    for p in net.parameters():
+        p.grad = torch.randn_like(p) * 1e-3
+        n += p.numel()
+    plan = comm._plans[id(opt)][0]
+
+    def fn():
+        comm.launch_group(opt, 0)
+        comm.wait_groups(opt, [0])
+    passes = 6.0 if settings.WRITE_BACK_GRADS else 5.0
+    report('allreduce_fused+sgd[%s, world 1, resnet50 %d elements, %d CTAs x %d threads]'
+           % ({0: 'oneshot', 1: 'twoshot', 2: 'nvls'}[plan.algo], n, plan.n_ctas, comm.n_threads), timer(fn), nbytes=passes * 4 * n)
+    comm.check_status(synchronize=True)
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument('what', choices=['bn', 'sgd', 'wgrad', 'pack'])
+    ap.add_argument('what', choices=['bn', 'sgd', 'wgrad', 'pack', 'fused'])
     ap.add_argument('--rows', type=int, default=200704)
     ap.add_argument('--channels', type=int, default=256)
     ap.add_argument('--residual', action='store_true')
@@ -163,7 +192,7 @@ def main(argv=None):
     args = ap.parse_args(argv)
     _lib.load(allow_build=False)
     timer = Timer(args.warmup, args.iters)
-    {'bn': bench_bn, 'sgd': bench_sgd, 'wgrad': bench_wgrad, 'pack': bench_pack}[args.what](args, timer)
+    {'bn': bench_bn, 'sgd': bench_sgd, 'wgrad': bench_wgrad, 'pack': bench_pack, 'fused': bench_fused}[args.what](args, timer)
 
 
 if __name__ == '__main__':

@@ -149,7 +149,7 @@ class NvlComm(Communicator):
         self.timeout_ns = int(float(os.environ.get('MGWFBP_COMM_TIMEOUT_S', '10')) * 1e9)
         self.oneshot_max_bytes = _env_int('MGWFBP_ONESHOT_MAX_BYTES', 512 * 1024)
         self.max_ctas_oneshot = min(_env_int('MGWFBP_ONESHOT_CTAS', 8), _lib.MAX_CTAS)
-        self.max_ctas_twoshot = min(_env_int('MGWFBP_TWOSHOT_CTAS', 32), _lib.MAX_CTAS)
+        self.max_ctas_twoshot = min(_env_int('MGWFBP_TWOSHOT_CTAS', 128), _lib.MAX_CTAS)
         self.n_threads = _env_int('MGWFBP_COMM_THREADS', 512)
         # control block: flag rows + per-CTA launch counters, in a heap of its own
         self._flag_bytes = int(self.lib.mgw_flag_block_bytes())
@@ -224,10 +224,13 @@ class NvlComm(Communicator):
             algo = _lib.ALGO_ONESHOT
         else:
             algo = _lib.ALGO_NVLS if self.nvls_available else _lib.ALGO_TWOSHOT
+        # a CTA is worth launching for two (one-shot) / eight (two-shot) float4 slots per thread
         if algo == _lib.ALGO_ONESHOT:
-            n_ctas = max(1, min(self.max_ctas_oneshot, (n_vec + 1023) // 1024))
+            per_cta = 2 * self.n_threads
+            n_ctas = max(1, min(self.max_ctas_oneshot, (n_vec + per_cta - 1) // per_cta))
         else:
-            n_ctas = max(1, min(self.max_ctas_twoshot, (n_vec + 4095) // 4096))
+            per_cta = 8 * self.n_threads
+            n_ctas = max(1, min(self.max_ctas_twoshot, (n_vec + per_cta - 1) // per_cta))
         return algo, n_ctas
 
     def _fill_args(self, plan: _GroupPlan, heap, hyper_ptr: int, partials_ptr: int,

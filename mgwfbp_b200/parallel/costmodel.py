@@ -30,15 +30,16 @@ TABLE_10GBE: Dict[int, Tuple[float, float]] = {
     4: (4.204298980348825e-05, 2.0589360830118177e-10),
     2: (2.554691138304671e-06, 9.837548167872609e-11),
 }
-# Placeholder constants for the peer-to-peer kernels on one NVSwitch box, used only until a
-# measured fit is supplied (``DistributedOptimizer.benchmark_communication`` or
-# ``MGWFBP_ALPHA_BETA``).  alpha ~ one launch plus one cross-GPU flag round trip; beta from the
-# measured all-reduce bus bandwidth (~700 GB/s at 8 ranks => 2*(N-1)/N / 700e9 s/B).
+# The fused peer-to-peer kernels of this package on one NVSwitch box of B200s, used until a fit measured on the
+# running box is supplied (``engine.fit_comm_model``, ``DistributedOptimizer.benchmark_communication`` or
+# ``MGWFBP_ALPHA_BETA``).  Least-squares fits of the two-shot kernel (write-back mode, 128 CTAs at most) over 1 KB ..
+# 128 MB, device-timed from CUDA-graph replays (``python -m mgwfbp_b200.parallel.comm.bench``) at 2, 4 and 8 GPUs; the
+# 16-rank row is extrapolated.  The one-shot kernel that serves messages up to 512 KB starts in 9-12 us.
 TABLE_NVLINK5: Dict[int, Tuple[float, float]] = {
-    2: (7.0e-06, 1.0 / 700e9),
-    4: (8.0e-06, 1.5 / 700e9),
-    8: (9.0e-06, 1.75 / 700e9),
-    16: (1.2e-05, 1.875 / 700e9),
+    2: (1.87e-05, 2.07e-12),
+    4: (1.99e-05, 3.12e-12),
+    8: (2.03e-05, 3.65e-12),
+    16: (2.2e-05, 3.9e-12),
 }
 
 _TABLES = {'10GbE': TABLE_10GBE, '56GbIB': TABLE_56GBIB, 'NVLink5': TABLE_NVLINK5}

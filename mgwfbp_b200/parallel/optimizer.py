@@ -33,7 +33,7 @@ from ..settings import logger
 from . import runtime
 from .comm import Communicator, LocalComm, make_communicator
 from .costmodel import AlphaBeta, fit_alpha_beta, table_lookup
-from .scheduler import MergeSchedule, groups_by_threshold, groups_mgwfbp
+from .scheduler import MergeSchedule, groups_by_threshold, groups_mgwfbp, groups_mgwfbp_contended
 
 
 class HookOrderError(RuntimeError):
@@ -181,7 +181,13 @@ class _DistributedMixin:
                 raise ValueError('layerwise_times and seq_layernames differ in length')
             nbytes = 2 if settings.FP16 else 4
             cost = self._resolve_cost_model()
-            sched = groups_mgwfbp(names, sizes, self._layerwise_times, cost, nbytes)
+            # kernels of the fused data plane compete with backward for SMs and bandwidth; other backends
+            # (NCCL / gloo behind torch.distributed) are scheduled by the reference's recurrences unchanged
+            rho = settings.INTERFERENCE if self._fused_comm else 0.0
+            if rho > 0.0:
+                sched = groups_mgwfbp_contended(names, sizes, self._layerwise_times, cost, rho, nbytes)
+            else:
+                sched = groups_mgwfbp(names, sizes, self._layerwise_times, cost, nbytes)
             if runtime.rank() == 0:
                 pr = sched.predicted
                 logger.info('tc sum: %f', pr['tc_sum'])

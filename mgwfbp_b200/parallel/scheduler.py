@@ -194,3 +194,124 @@ def simulate_schedule(schedule: MergeSchedule, names: Sequence[str], sizes: Sequ
     tb_total = ready[0] if L else 0.0
     return {'tb_sum': tb_total, 'finish': t_comm_free, 'non_overlapped': max(t_comm_free - tb_total, 0.0),
             'merged_tc_sum': total_tc}
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# Interference-aware selection
+#
+# The MG-WFBP recurrences treat communication that overlaps backward as free.  That holds when the wire is the
+# bottleneck (the reference's Ethernet / InfiniBand clusters: a message costs hundreds of microseconds of NIC
+# time and no GPU time).  With peer-memory kernels over NVLink the message itself takes tens of microseconds, but
+# the kernel that moves it occupies SMs and memory bandwidth that the backward kernels running beside it want
+# too, so every second of overlapped communication delays backward by a fraction `interference` of a second.
+# Under that model many small hidden messages can cost more than a few large exposed ones, and the best
+# schedule lies somewhere between the MG-WFBP one and a single buffer.  The selection below keeps the MG-WFBP
+# machinery and searches that range: candidates are MG-WFBP schedules computed with the start-up term
+# inflated by 1x, 1.5x, 2x, ... (each step merges more), fixed-size buckets, and one single group; every candidate is played
+# through the interference-aware timeline with the TRUE cost model, and the earliest finish wins.
+
+def simulate_contended(schedule: MergeSchedule, names: Sequence[str], sizes: Sequence[int], tb: Sequence[float],
+                       cost: Callable[[float], float], interference: float, bytes_per_elem: int = 4) -> Dict[str, float]:
+    """Timeline of ``schedule`` when backward runs at rate ``1 - interference`` while a message is in flight.
+
+    Messages are sent in group order, one at a time, each as soon as its last gradient exists and the
+    previous message is done.  Returns the finish time of the iteration's backward + communication
+    (``finish``), when backward itself ended (``backward_end``), the summed message time and the number of groups.
+    """
+    rho = min(max(float(interference), 0.0), 1.0)
+    names = list(names)
+    idx = {n: i for i, n in enumerate(names)}
+    L = len(names)
+    # backward work done when layer l's gradient exists (backward runs from layer L-1 down to 0)
+    done_at = [0.0] * L
+    run = 0.0
+    for l in range(L - 1, -1, -1):
+        run += float(tb[l])
+        done_at[l] = run
+    total_work = run
+    need = [max(done_at[idx[n]] for n in g) for g in schedule.groups]
+    tcs = [float(cost(n_el * bytes_per_elem)) for n_el in schedule.group_sizes]
+    t = w = 0.0
+    qi, G = 0, len(need)
+    backward_end = 0.0 if total_work <= 0.0 else None
+    eps = 1e-15
+    rate = 1.0 - rho
+    while True:
+        if qi < G and w >= need[qi] - eps:
+            # the link is idle and the next group is complete: its message runs to the end, backward crawls beside it
+            gain = tcs[qi] * rate
+            if backward_end is None and w + gain >= total_work - eps:
+                backward_end = t + ((total_work - w) / rate if rate > 0.0 else 0.0)
+            w = min(w + gain, total_work)
+            t += tcs[qi]
+            qi += 1
+            continue
+        if qi >= G and w >= total_work - eps:
+            break
+        target = need[qi] if qi < G else total_work           # nothing to send yet: backward runs alone
+        t += max(target - w, 0.0)
+        w = target
+        if backward_end is None and w >= total_work - eps:
+            backward_end = t
+    return {'finish': t, 'backward_end': backward_end if backward_end is not None else t, 'tb_sum': total_work,
+            'merged_tc_sum': float(sum(tcs)), 'groups': float(G)}
+
+
+def groups_mgwfbp_contended(names: Sequence[str], sizes: Sequence[int], tb: Sequence[float],
+                            cost: Callable[[float], float], interference: float, bytes_per_elem: int = 4,
+                            startup: Optional[Callable[[float], float]] = None,
+                            inflations: Sequence[float] = (1, 1.5, 2, 2.5, 3, 3.5, 4, 6, 8, 16, 32, 64, 256, 1024),
+                            buckets: Sequence[int] = (1 << 18, 1 << 19, 1 << 20, 1 << 21, 1 << 22, 1 << 23, 1 << 24, 1 << 25)
+                            ) -> MergeSchedule:
+    """The MG-WFBP schedule that finishes first when overlapped communication slows backward down.
+
+    ``interference`` = 0 returns exactly :func:`groups_mgwfbp`.  Otherwise the candidates described above are
+    compared under :func:`simulate_contended`; ties go to the schedule with fewer groups.  The winner's
+    ``predicted`` dict carries the comparison (``candidates``: inflation factor or minus the bucket size in elements,
+    number of groups, predicted finish).
+    """
+    base = groups_mgwfbp(names, sizes, tb, cost, bytes_per_elem, startup)
+    if interference <= 0.0 or len(names) <= 1:
+        return base
+    if startup is None:
+        startup = getattr(cost, 'startup', None)
+    if startup is None:
+        a0 = cost(1) - (cost(2) - cost(1))
+        startup = lambda nbytes, _a=a0: _a  # noqa: E731
+    seen: Dict[str, MergeSchedule] = {}
+    table = []
+    best = None
+    for k in inflations:
+        if k == 1:
+            cand = base
+        else:
+            cand = groups_mgwfbp(names, sizes, tb, (lambda nb, _k=k: cost(nb) + (_k - 1.0) * startup(nb)), bytes_per_elem,
+                                 (lambda nb, _k=k: _k * startup(nb)))
+        sig = cand.digest()
+        if sig in seen:
+            continue
+        seen[sig] = cand
+        sim = simulate_contended(cand, names, sizes, tb, cost, interference, bytes_per_elem)
+        table.append((float(k), len(cand.groups), sim['finish']))
+        key = (sim['finish'], len(cand.groups))
+        if best is None or key < best[0]:
+            best = (key, cand, sim)
+    # fixed-size buckets (in elements) fill the range between the inflated schedules and one single message
+    for thr in list(buckets) + [1 << 62]:
+        cand = groups_by_threshold(names, sizes, thr)
+        sig = cand.digest()
+        if sig in seen:
+            continue
+        seen[sig] = cand
+        sim = simulate_contended(cand, names, sizes, tb, cost, interference, bytes_per_elem)
+        table.append((-float(thr), len(cand.groups), sim['finish']))
+        key = (sim['finish'], len(cand.groups))
+        if key < best[0]:
+            best = (key, cand, sim)
+    _, chosen, sim = best
+    predicted = dict(chosen.predicted)
+    predicted.update({'interference': float(interference), 'contended_finish': sim['finish'],
+                      'contended_backward_end': sim['backward_end'], 'merged_tc_sum': sim['merged_tc_sum'],
+                      'tb_sum': sim['tb_sum'], 'non_overlapped': sim['finish'] - sim['tb_sum'],
+                      'tb_plus_tc': sim['finish'], 'tc_sum': base.predicted.get('tc_sum', 0.0), 'candidates': table})
+    return MergeSchedule(chosen.groups, chosen.key_groupidx, chosen.offsets, chosen.group_sizes, predicted)

@@ -75,6 +75,14 @@ WRITE_BACK_GRADS = _env_flag('WRITE_BACK_GRADS', True)
 # while this is on.
 SHADOW_EVERY = int(_env_str('SHADOW', '0') or 0)
 
+# Fraction of a second that backward loses per second of all-reduce kernel running beside it (0 = overlapped
+# communication is free, the assumption of the MG-WFBP recurrences; 1 = it costs as much as exposed communication).
+# Used only with the fused NVLink data plane, whose kernels share SMs and memory bandwidth with backward.
+# Measured on B200 (2 GPUs, batch 64/32 per GPU): ResNet-50 12.34 ms/step with the plain MG-WFBP schedule (95
+# messages), 12.02 with three 32 MB buckets, 12.00 with one message; DenseNet-201 27.5 (402 messages) vs 24.7 ms
+# (one); i.e. overlap buys nothing there and every extra message costs, which is what 1.0 expresses.
+INTERFERENCE = float(_env_str('INTERFERENCE', '1.0'))
+
 # 'auto' | 'oneshot' | 'twoshot' | 'nvls'
 COMM_ALGO = _env_str('COMM_ALGO', 'auto')
 

@@ -134,7 +134,7 @@ def test_bounded_wait_reports_timeout_without_hanging(lib):
     table.refresh_grads([x])
     stage = torch.zeros(4 * 1024 * 4, device=dev)
     flags = torch.zeros(lib.mgw_flag_block_bytes() // 4, dtype=torch.int32, device=dev)
-    epoch = torch.zeros(64, dtype=torch.int32, device=dev)
+    epoch = torch.zeros(_lib.MAX_CTAS, dtype=torch.int32, device=dev)
     status = C.POINTER(C.c_int)()
     _lib.check(lib.mgw_host_status_alloc(8, C.byref(status)))
     a = _lib.MgwAllreduceArgs()
@@ -146,7 +146,7 @@ def test_bounded_wait_reports_timeout_without_hanging(lib):
     a.epoch = epoch.data_ptr()
     a.status = C.cast(status, C.c_void_p).value
     a.rank, a.world, a.algo, a.n_ctas, a.n_threads = 0, 2, _lib.ALGO_TWOSHOT, 1, 128
-    a.mode, a.first_step, a.inbox_stride = _lib.MODE_WRITEBACK, 0, table.n_vec
+    a.mode, a.first_step, a.inbox_stride, a.stage_slots = _lib.MODE_WRITEBACK, 0, table.n_vec, table.n_vec
     a.timeout_ns = 50_000_000        # 50 ms
     _lib.check(lib.mgw_allreduce_group(C.byref(a), torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()

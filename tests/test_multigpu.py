@@ -11,7 +11,8 @@ pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
 def _world():
-    return min(torch.cuda.device_count(), 4)
+    # 2..4 ranks by default; MGWFBP_TEST_WORLD=8 runs the same tests on all GPUs of an 8-GPU box
+    return min(torch.cuda.device_count(), int(os.environ.get('MGWFBP_TEST_WORLD', '4')))
 
 
 def _allreduce_sweep(rank, world):
@@ -57,9 +58,21 @@ def _fused_training(rank, world, policy, fused):
     hvd.broadcast_parameters(net.state_dict(), 0)
     ref.load_state_dict(net.state_dict())
     mk = lambda m: torch.optim.SGD(m.parameters(), lr=0.05, momentum=0.9, weight_decay=1e-4)
-    threshold = {'wfbp': 0, 'single': 524288000, 'bucket': 20000}[policy]
-    opt = hvd.DistributedOptimizer(mk(net), named_parameters=net.named_parameters(), threshold=threshold, fused_update=fused)
+    threshold = {'wfbp': 0, 'single': 524288000, 'bucket': 20000, 'mgwfbp': 0, 'mgwfbp-free': 0}[policy]
+    seq = times = None
+    if policy.startswith('mgwfbp'):
+        # measured-schedule path: forward-order names + per-layer backward times (made up, equal on all ranks)
+        settings.ADAPTIVE_MERGE = True
+        settings.INTERFERENCE = 1.0 if policy == 'mgwfbp' else 0.0
+        seq = [n for n, _ in net.named_parameters()]
+        times = [2e-5] * len(seq)
+    opt = hvd.DistributedOptimizer(mk(net), named_parameters=net.named_parameters(), threshold=threshold, fused_update=fused,
+                                   seq_layernames=seq, layerwise_times=times)
     assert opt._fused_comm and opt._fused_update == fused
+    if policy == 'mgwfbp':
+        assert len(opt.merge_schedule.groups) == 1          # full interference: one message
+    if policy == 'mgwfbp-free':
+        assert len(opt.merge_schedule.groups) > 1
     ropt = mk(ref)
     crit = torch.nn.CrossEntropyLoss()
     g = torch.Generator().manual_seed(5)
@@ -77,7 +90,8 @@ def _fused_training(rank, world, policy, fused):
     return {'dp': [p.detach().cpu() for p in net.parameters()], 'ref': [p.detach().cpu() for p in ref.parameters()]}
 
 
-@pytest.mark.parametrize('policy,fused', [('wfbp', True), ('single', True), ('bucket', True), ('bucket', False)])
+@pytest.mark.parametrize('policy,fused', [('wfbp', True), ('single', True), ('bucket', True), ('bucket', False),
+                                          ('mgwfbp', True), ('mgwfbp-free', True)])
 def test_fused_data_parallel_equals_large_batch(policy, fused):
     res = run_ranks(_fused_training, (policy, fused), world=_world())
     for dp, ref in zip(res[0]['dp'], res[0]['ref']):

@@ -171,3 +171,58 @@ def test_simulation_orders_policies_sensibly():
     sim_wf = simulate_schedule(wf, TOY_NAMES, TOY_SIZES, TOY_TB, ab)
     assert sim_mg['finish'] <= sim_wf['finish'] + 1e-12
     assert sim_mg['finish'] == pytest.approx(mg.predicted['tb_plus_tc'])
+
+
+# ----------------------------------------------------------------------------- interference-aware selection
+def _random_model(seed, L=60):
+    rng = np.random.RandomState(seed)
+    names = ['layer%d' % i for i in range(L)]
+    sizes = [int(rng.choice([64, 256, 2048, 36864, 147456, 589824, 2359296])) for _ in range(L)]
+    tb = [float(t) for t in rng.uniform(5e-6, 120e-6, L)]
+    return names, sizes, tb
+
+
+@pytest.mark.parametrize('seed', [0, 1, 2])
+def test_contended_selection_with_zero_interference_is_plain_mgwfbp(seed):
+    from mgwfbp_b200.parallel.scheduler import groups_mgwfbp_contended, simulate_contended
+    names, sizes, tb = _random_model(seed)
+    cost = AlphaBeta(12e-6, 3e-12)
+    plain = groups_mgwfbp(names, sizes, tb, cost)
+    assert groups_mgwfbp_contended(names, sizes, tb, cost, 0.0).groups == plain.groups
+    # without interference the contended timeline is the ordinary one
+    a = simulate_contended(plain, names, sizes, tb, cost, 0.0)
+    b = simulate_schedule(plain, names, sizes, tb, cost)
+    assert a['finish'] == pytest.approx(b['finish'], rel=1e-12)
+    assert a['backward_end'] == pytest.approx(sum(tb), rel=1e-12)
+
+
+@pytest.mark.parametrize('seed', [0, 1, 2])
+def test_full_interference_makes_every_message_cost_its_time_and_selects_one_group(seed):
+    from mgwfbp_b200.parallel.scheduler import groups_mgwfbp_contended, simulate_contended
+    names, sizes, tb = _random_model(seed)
+    cost = AlphaBeta(12e-6, 3e-12)
+    for sched in (groups_by_threshold(names, sizes, 0), groups_by_threshold(names, sizes, 1 << 20), groups_mgwfbp(names, sizes, tb, cost)):
+        sim = simulate_contended(sched, names, sizes, tb, cost, 1.0)
+        assert sim['finish'] == pytest.approx(sum(tb) + sim['merged_tc_sum'], rel=1e-9)
+    chosen = groups_mgwfbp_contended(names, sizes, tb, cost, 1.0)
+    assert len(chosen.groups) == 1 and sorted(chosen.groups[0]) == sorted(names)
+    assert chosen.predicted['contended_finish'] == pytest.approx(sum(tb) + cost(4 * sum(sizes)), rel=1e-9)
+    # every candidate that was looked at is listed, and the winner is the minimum
+    assert min(f for _, _, f in chosen.predicted['candidates']) == pytest.approx(chosen.predicted['contended_finish'])
+
+
+def test_contended_finish_grows_with_interference_and_partial_interference_keeps_some_overlap():
+    from mgwfbp_b200.parallel.scheduler import groups_mgwfbp_contended, simulate_contended
+    names, sizes, tb = _random_model(3, L=120)
+    cost = AlphaBeta(15e-6, 4e-12)
+    sched = groups_by_threshold(names, sizes, 1 << 21)
+    finishes = [simulate_contended(sched, names, sizes, tb, cost, r)['finish'] for r in (0.0, 0.25, 0.5, 0.75, 1.0)]
+    assert all(b >= a - 1e-15 for a, b in zip(finishes, finishes[1:]))
+    mid = groups_mgwfbp_contended(names, sizes, tb, cost, 0.25)
+    n_plain = len(groups_mgwfbp(names, sizes, tb, cost).groups)
+    assert 1 < len(mid.groups) < n_plain          # between the latency-only schedule and a single message
+    assert mid.predicted['interference'] == 0.25
+    # the chosen schedule is a valid partition in backward order
+    flat = [n for g in mid.groups for n in g]
+    assert flat == list(reversed(names))
+    assert mid.group_sizes == [sum(sizes[names.index(n)] for n in g) for g in mid.groups]

@@ -38,6 +38,21 @@ struct Smem {
     float red[32];
 };
 
+// Checked build: thread 0 of every CTA stamps the end of each phase of the most recent launch
+// (pack, first barrier, reduce, second barrier, consume), nanoseconds since the CTA started.
+#ifdef MGW_CHECKED
+__device__ unsigned long long g_mgw_phase_ns[MGW_MAX_CTAS][6];
+#define MGW_PHASE_BEGIN() const uint64_t phase_t0 = mgw_globaltimer_ns()
+#define MGW_PHASE_END(i)                                                                    \
+    do {                                                                                    \
+        __syncthreads();                                                                    \
+        if (threadIdx.x == 0) g_mgw_phase_ns[blockIdx.x][(i)] = mgw_globaltimer_ns() - phase_t0; \
+    } while (0)
+#else
+#define MGW_PHASE_BEGIN() do {} while (0)
+#define MGW_PHASE_END(i) do {} while (0)
+#endif
+
 __device__ __forceinline__ uint32_t* flag_slot(uint32_t* base, int phase, int cta, int src) {
     return base + ((size_t)(phase * MGW_MAX_CTAS + cta) * MGW_MAX_RANKS + src);
 }
@@ -89,7 +104,7 @@ template <int W, int ALGO>
 __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduceArgs a) {
     constexpr int WW = W > 0 ? W : MGW_MAX_RANKS;
     constexpr int U = kUnroll;                                  // pack / consume: one operand stream per slot
-    constexpr int UR = W == 2 ? 4 : (W == 4 ? 2 : 1);           // reduce: W peer loads per slot, keep ~8 in flight
+    constexpr int UR = (W == 1 || W == 2) ? 4 : (W == 4 ? 2 : 1);   // reduce: W peer loads per slot, keep ~8 in flight
     __shared__ Smem sm;
     const int world = W > 0 ? W : a.world;
     const int tid = threadIdx.x, nthr = blockDim.x, b = blockIdx.x;
@@ -105,6 +120,7 @@ __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduc
     const int c0 = min(g.n_vec, b * per);
     const int c1 = min(g.n_vec, c0 + per);
     float sumsq = 0.f;
+    MGW_PHASE_BEGIN();
     // checked build: the chunk must lie inside the region the host sized; otherwise this CTA does nothing
     bool ok = MGW_CHECK(c1 <= (ALGO == MGW_ALGO_ONESHOT ? a.inbox_stride : a.stage_slots), MGW_BOUNDS_STAGE, c1,
                         ALGO == MGW_ALGO_ONESHOT ? a.inbox_stride : a.stage_slots, 0);
@@ -163,7 +179,9 @@ __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduc
             for (int k = 0; k < U; ++k)
                 if (v0 + k * 32 < c1) mgw_st_peer(local + v0 + k * 32, x[k]);
         }
+        MGW_PHASE_END(0);
         ok = rank_barrier(a, 0, e, &sm);
+        MGW_PHASE_END(1);
         if (ok) {
             const int sub = per / world;
             const int s0 = min(c1, c0 + a.rank * sub);
@@ -208,7 +226,9 @@ __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduc
                     }
                 }
             }
+            MGW_PHASE_END(2);
             ok = rank_barrier(a, 1, e, &sm);
+            MGW_PHASE_END(3);
         }
         if (ok) {
             MgwCursor cc = mgw_cursor();
@@ -220,6 +240,7 @@ __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduc
                 mgw_consume_batch<U>(g, v0, 32, c1, cc, x, a.mode, a.hyper, a.first_step, sumsq);
             }
         }
+        MGW_PHASE_END(4);
     }
 
     if (a.mode & MGW_MODE_SUMSQ) {
@@ -234,6 +255,7 @@ template <int ALGO>
 cudaError_t launch_world(const MgwAllreduceArgs& a, cudaStream_t s) {
     dim3 grid(a.n_ctas), block(a.n_threads);
     switch (a.world) {
+        case 1: mgw_allreduce_kernel<1, ALGO><<<grid, block, 0, s>>>(a); break;
         case 2: mgw_allreduce_kernel<2, ALGO><<<grid, block, 0, s>>>(a); break;
         case 4: mgw_allreduce_kernel<4, ALGO><<<grid, block, 0, s>>>(a); break;
         case 8: mgw_allreduce_kernel<8, ALGO><<<grid, block, 0, s>>>(a); break;
@@ -245,6 +267,19 @@ cudaError_t launch_world(const MgwAllreduceArgs& a, cudaStream_t s) {
 }  // namespace
 
 MGW_DEFINE_BOUNDS_READER(mgw_bounds_allreduce)
+
+// Checked build: per-CTA phase stamps of the most recent two-shot / NVLS launch, out[cta * 6 + phase] in ns
+// (phases: pack, barrier, reduce, barrier, consume; slot 5 unused).  Zeros in the normal build.
+extern "C" int mgw_phase_times(unsigned long long* out, int n_ctas) {
+    if (out == nullptr || n_ctas < 1 || n_ctas > MGW_MAX_CTAS) return MGW_ERR_ARG;
+#ifdef MGW_CHECKED
+    MGW_CUDA_CHECK(cudaDeviceSynchronize());
+    MGW_CUDA_CHECK(cudaMemcpyFromSymbol(out, g_mgw_phase_ns, sizeof(unsigned long long) * 6 * n_ctas));
+#else
+    for (int i = 0; i < 6 * n_ctas; ++i) out[i] = 0ull;
+#endif
+    return MGW_OK;
+}
 
 extern "C" size_t mgw_flag_block_bytes(void) {
     return sizeof(uint32_t) * 2 * MGW_MAX_CTAS * MGW_MAX_RANKS;

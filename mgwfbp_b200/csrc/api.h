@@ -48,6 +48,8 @@ int mgw_allreduce_group(const MgwAllreduceArgs* args, void* stream);
 // multi_tensor_sgd.cu as {code, a, b, c, block, thread, 0, 0} (MGW_BOUNDS_*), cleared by the call.  All zeros otherwise.
 int mgw_bounds_allreduce(int* out8);
 int mgw_bounds_sgd(int* out8);
+// Checked build only: per-CTA phase stamps (ns since CTA start) of the most recent two-shot / NVLS launch.
+int mgw_phase_times(unsigned long long* out, int n_ctas);
 size_t mgw_flag_block_bytes(void);
 // staging bytes one rank needs for a group of n_vec float4 slots under `algo`
 size_t mgw_stage_bytes(int algo, int n_vec, int world);

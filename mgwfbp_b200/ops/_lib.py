@@ -70,6 +70,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.mgw_group_sumsq.argtypes = [C.POINTER(MgwGroup), C.c_void_p, C.c_int, C.c_void_p]
     lib.mgw_bounds_allreduce.argtypes = [C.POINTER(C.c_int)]
     lib.mgw_bounds_sgd.argtypes = [C.POINTER(C.c_int)]
+    lib.mgw_phase_times.argtypes = [C.POINTER(C.c_ulonglong), C.c_int]
     for name in ('mgw_bn_relu_fwd', 'mgw_bn_relu_bwd', 'mgw_lstm_cell_fwd', 'mgw_lstm_cell_bwd',
                  'mgw_wgrad_gemm', 'mgw_wgrad_gemm_supported', 'mgw_allgather_rows'):
         if hasattr(lib, name):
@@ -110,6 +111,14 @@ def is_checked() -> bool:
 BOUNDS_CODES = {1: 'slot index outside the group', 2: 'slot not inside the tensor found for it',
                 3: 'offset table and element count of a tensor disagree', 4: 'slot starts beyond the tensor\'s last element',
                 5: 'staging index beyond the sized region'}
+
+
+def phase_times(n_ctas: int) -> list:
+    """Checked build: for each CTA of the most recent two-shot / NVLS all-reduce launch, the time in ns from CTA
+    start to the end of (pack, first barrier, reduce, second barrier, consume).  Zeros in the normal build."""
+    buf = (C.c_ulonglong * (6 * n_ctas))()
+    check(load().mgw_phase_times(buf, n_ctas), 'phase times')
+    return [[int(buf[c * 6 + i]) for i in range(5)] for c in range(n_ctas)]
 
 
 def bounds_report() -> list:

@@ -48,6 +48,8 @@ for algo in ('oneshot', 'twoshot'):
     comm.synchronize(comm.allreduce_async_(x, algo=algo))
     torch.cuda.synchronize(); comm.check_status()
     res[algo] = bool(torch.equal(x, keep))
+stamps = _lib.phase_times(1)[0]              # the two-shot launch above: pack, barrier, reduce, barrier, consume
+out['phases_monotone'] = bool(stamps[0] > 0 and all(a <= b for a, b in zip(stamps, stamps[1:])))
 out['allreduce_ok'] = res
 out['allreduce_report'] = _lib.bounds_report()
 
@@ -75,6 +77,7 @@ def test_checked_build_is_silent_on_sound_tables_and_reports_a_bad_one():
     out = json.loads(line[len('RESULT '):])
     assert out['sgd_ok'] and out['sgd_report'] == []
     assert out['allreduce_ok'] == {'oneshot': True, 'twoshot': True} and out['allreduce_report'] == []
+    assert out['phases_monotone']
     assert out['tail_untouched']
     assert len(out['bad_report']) == 1 and out['bad_report'][0]['unit'] == 'multi_tensor_sgd'
     assert out['bad_report'][0]['code'] in (3, 4)

@@ -39,7 +39,8 @@ struct Smem {
 };
 
 // Checked build: thread 0 of every CTA stamps the end of each phase of the most recent launch
-// (pack, first barrier, reduce, second barrier, consume), nanoseconds since the CTA started.
+// (pack, first barrier, reduce, second barrier, consume of the FIRST piece, then the end of the last piece),
+// nanoseconds since the CTA started.
 #ifdef MGW_CHECKED
 __device__ unsigned long long g_mgw_phase_ns[MGW_MAX_CTAS][6];
 #define MGW_PHASE_BEGIN() const uint64_t phase_t0 = mgw_globaltimer_ns()
@@ -112,13 +113,16 @@ __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduc
     if (tid == 0) sm.failed = 0;
     const uint32_t e = a.epoch[b] + 1u;
     const MgwGroup& g = a.group;
-    const float inv = 1.f / (float)world;
+    const float inv = a.grad_scale / (float)world;
 
     // chunk of this CTA, a multiple of `world` slots so that sub-chunks are equal
     int per = (g.n_vec + gridDim.x - 1) / gridDim.x;
     per = (per + world - 1) / world * world;
     const int c0 = min(g.n_vec, b * per);
     const int c1 = min(g.n_vec, c0 + per);
+    // two-shot / NVLS: number of pieces the chunk is processed in (same on every rank: it depends on the group's size
+    // and the grid only); each piece uses one value of the CTA's launch counter
+    const int pieces = ALGO == MGW_ALGO_ONESHOT ? 1 : max(1, min(a.max_pieces, per / max(a.piece_slots, 1)));
     float sumsq = 0.f;
     MGW_PHASE_BEGIN();
     // checked build: the chunk must lie inside the region the host sized; otherwise this CTA does nothing
@@ -170,22 +174,32 @@ __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduc
             }
         }
     } else {
+        // The chunk is cut into `pieces` consecutive pieces that go through pack / barrier / reduce / barrier /
+        // consume one after another, each with its own flag value.  CTAs drift apart within a few pieces, so while
+        // some wait on NVLink in the reduce phase others stream HBM in pack or consume, and with two CTAs per SM
+        // a CTA that waits at a barrier leaves the SM to its neighbour.
         float4* local = reinterpret_cast<float4*>(a.stage[a.rank]);
-        MgwCursor cl = mgw_cursor();
-        for (int v0 = c0 + warp * 32 * U + lane; v0 < c1; v0 += nthr * U) {
-            float4 x[U];
-            mgw_load_grad_batch<U>(g, v0, 32, c1, cl, 1.f, x);
+        int plen = (per + pieces - 1) / pieces;
+        plen = (plen + world - 1) / world * world;
+        MgwCursor cur = mgw_cursor();          // one table cursor serves the pack and the consume loops of a piece
+        for (int piece = 0; piece < pieces && ok; ++piece) {
+            const uint32_t ep = e + (uint32_t)piece;
+            const int p0 = min(c1, c0 + piece * plen);
+            const int p1 = min(c1, p0 + plen);
+            for (int v0 = p0 + warp * 32 * U + lane; v0 < p1; v0 += nthr * U) {
+                float4 x[U];
+                mgw_load_grad_batch<U>(g, v0, 32, p1, cur, 1.f, x);
 #pragma unroll
-            for (int k = 0; k < U; ++k)
-                if (v0 + k * 32 < c1) mgw_st_peer(local + v0 + k * 32, x[k]);
-        }
-        MGW_PHASE_END(0);
-        ok = rank_barrier(a, 0, e, &sm);
-        MGW_PHASE_END(1);
-        if (ok) {
-            const int sub = per / world;
-            const int s0 = min(c1, c0 + a.rank * sub);
-            const int s1 = min(c1, s0 + sub);
+                for (int k = 0; k < U; ++k)
+                    if (v0 + k * 32 < p1) mgw_st_peer(local + v0 + k * 32, x[k]);
+            }
+            if (piece == 0) MGW_PHASE_END(0);
+            ok = rank_barrier(a, 0, ep, &sm);
+            if (piece == 0) MGW_PHASE_END(1);
+            if (!ok) break;
+            const int sub = plen / world;
+            const int s0 = min(p1, p0 + a.rank * sub);
+            const int s1 = min(p1, s0 + sub);
             if (ALGO == MGW_ALGO_NVLS) {
                 float4* mc = reinterpret_cast<float4*>(a.mc_stage);
                 for (int v0 = s0 + warp * 32 * U + lane; v0 < s1; v0 += nthr * U) {
@@ -226,21 +240,20 @@ __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduc
                     }
                 }
             }
-            MGW_PHASE_END(2);
-            ok = rank_barrier(a, 1, e, &sm);
-            MGW_PHASE_END(3);
-        }
-        if (ok) {
-            MgwCursor cc = mgw_cursor();
-            for (int v0 = c0 + warp * 32 * U + lane; v0 < c1; v0 += nthr * U) {
+            if (piece == 0) MGW_PHASE_END(2);
+            ok = rank_barrier(a, 1, ep, &sm);
+            if (piece == 0) MGW_PHASE_END(3);
+            if (!ok) break;
+            for (int v0 = p0 + warp * 32 * U + lane; v0 < p1; v0 += nthr * U) {
                 float4 x[U];
 #pragma unroll
                 for (int k = 0; k < U; ++k)
-                    if (v0 + k * 32 < c1) x[k] = mgw_ld_peer(local + v0 + k * 32);
-                mgw_consume_batch<U>(g, v0, 32, c1, cc, x, a.mode, a.hyper, a.first_step, sumsq);
+                    if (v0 + k * 32 < p1) x[k] = mgw_ld_peer(local + v0 + k * 32);
+                mgw_consume_batch<U>(g, v0, 32, p1, cur, x, a.mode, a.hyper, a.first_step, sumsq);
             }
+            if (piece == 0) MGW_PHASE_END(4);
         }
-        MGW_PHASE_END(4);
+        MGW_PHASE_END(5);
     }
 
     if (a.mode & MGW_MODE_SUMSQ) {
@@ -248,7 +261,7 @@ __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduc
         if (tid == 0) a.sumsq_partials[b] = r;
     }
     __syncthreads();
-    if (tid == 0) a.epoch[b] = e;          // advance even after a timeout: the launch counter stays in step
+    if (tid == 0) a.epoch[b] = e + (uint32_t)(pieces - 1);      // advance even after a timeout: the launch counter stays in step
 }
 
 template <int ALGO>
@@ -302,6 +315,8 @@ extern "C" int mgw_allreduce_group(const MgwAllreduceArgs* args, void* stream) {
     if (a.algo == MGW_ALGO_NVLS && a.mc_stage == nullptr) return MGW_ERR_ARG;
     if (a.algo == MGW_ALGO_ONESHOT && a.inbox_stride < a.group.n_vec) return MGW_ERR_TOO_LARGE;
     if (a.algo != MGW_ALGO_ONESHOT && a.stage_slots < a.group.n_vec) return MGW_ERR_TOO_LARGE;
+    if (a.algo != MGW_ALGO_ONESHOT && (a.max_pieces < 1 || a.piece_slots < 1)) return MGW_ERR_ARG;
+    if (!(a.grad_scale > 0.f)) return MGW_ERR_ARG;
     for (int r = 0; r < a.world; ++r)
         if (a.stage[r] == nullptr || a.flags[r] == nullptr) return MGW_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;

@@ -40,6 +40,9 @@ typedef struct {
     int mode, first_step;
     int inbox_stride;                   // one-shot: float4 slots between consecutive inbox rows (>= n_vec)
     int stage_slots;                    // two-shot / NVLS: float4 slots the staging area holds (>= n_vec)
+    int max_pieces;                     // two-shot / NVLS: the chunk of a CTA is processed in at most this many pieces ...
+    int piece_slots;                    // ... of at least this many float4 slots (1, anything: no pipelining)
+    float grad_scale;                   // multiplies the summed gradient together with 1/world (1 / loss scale)
     unsigned long long timeout_ns;
 } MgwAllreduceArgs;
 

@@ -4,7 +4,7 @@
 #include <stdint.h>
 
 #define MGW_MAX_RANKS 16
-#define MGW_MAX_CTAS 128
+#define MGW_MAX_CTAS 296
 #define MGW_MAX_PARAM_GROUPS 16
 
 // return codes of the host entry points

@@ -70,7 +70,7 @@ class TrainStep:
             # gradient-accumulator nodes (and their stream) alive into the next step / a later capture
             from .models.lstm import repackage_hidden
             self._hidden = repackage_hidden(hidden)
-        loss.backward()
+        t.backward(loss)
         t.optimizer.step()
         return loss.detach()
 
@@ -88,7 +88,7 @@ class TrainStep:
             self._hidden = None
         with torch.cuda.graph(g):
             loss, _o, _l, hid = t.forward_loss(self._static_batch, self._static_hidden, on_device=True)
-            loss.backward()
+            t.backward(loss)
             t.optimizer.step()
             self._static_loss = loss.detach()
             if self._static_hidden is not None:

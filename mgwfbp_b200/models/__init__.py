@@ -103,8 +103,10 @@ def create_net(num_classes, dnn='resnet20', fuse=False, channels_last=False, **k
     if fuse and dnn not in ('lstm',):
         from .fuse import fuse_model
         net = fuse_model(net)
-    if fuse:
+    from .. import settings as _settings
+    if fuse and not _settings.FP16:
         # large fully-connected layers: exchange activations instead of all-reducing the weight gradient
+        # (fp32 / TF32 kernels; under FP16 autocast the layers stay torch.nn.Linear)
         from ..ops.wgrad import convert_large_linears
         convert_large_linears(net)
     if channels_last:

@@ -14,7 +14,7 @@ from typing import Optional
 from .build import CHECKED_LIB_PATH, LIB_PATH, build
 
 MAX_RANKS = 16
-MAX_CTAS = 128
+MAX_CTAS = 296
 MAX_PARAM_GROUPS = 16
 
 MODE_UPDATE, MODE_WRITEBACK, MODE_SUMSQ = 1, 2, 4
@@ -40,6 +40,7 @@ class MgwAllreduceArgs(C.Structure):
                 ('algo', C.c_int), ('n_ctas', C.c_int), ('n_threads', C.c_int),
                 ('mode', C.c_int), ('first_step', C.c_int),
                 ('inbox_stride', C.c_int), ('stage_slots', C.c_int),
+                ('max_pieces', C.c_int), ('piece_slots', C.c_int), ('grad_scale', C.c_float),
                 ('timeout_ns', C.c_ulonglong)]
 
 
@@ -115,10 +116,11 @@ BOUNDS_CODES = {1: 'slot index outside the group', 2: 'slot not inside the tenso
 
 def phase_times(n_ctas: int) -> list:
     """Checked build: for each CTA of the most recent two-shot / NVLS all-reduce launch, the time in ns from CTA
-    start to the end of (pack, first barrier, reduce, second barrier, consume).  Zeros in the normal build."""
+    start to the end of (pack, first barrier, reduce, second barrier, consume) of the chunk's first piece and to the
+    end of its last piece.  Zeros in the normal build."""
     buf = (C.c_ulonglong * (6 * n_ctas))()
     check(load().mgw_phase_times(buf, n_ctas), 'phase times')
-    return [[int(buf[c * 6 + i]) for i in range(5)] for c in range(n_ctas)]
+    return [[int(buf[c * 6 + i]) for i in range(6)] for c in range(n_ctas)]
 
 
 def bounds_report() -> list:

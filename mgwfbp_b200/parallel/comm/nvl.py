@@ -134,6 +134,7 @@ class _GroupPlan:
     __slots__ = ('table', 'params', 'algo', 'n_ctas', 'stage_off', 'args', 'partials_off', 'heap')
 
 
+
 class NvlComm(Communicator):
     fused = True
     _shared: Optional['NvlComm'] = None
@@ -151,6 +152,12 @@ class NvlComm(Communicator):
         self.max_ctas_oneshot = min(_env_int('MGWFBP_ONESHOT_CTAS', 8), _lib.MAX_CTAS)
         self.max_ctas_twoshot = min(_env_int('MGWFBP_TWOSHOT_CTAS', 128), _lib.MAX_CTAS)
         self.n_threads = _env_int('MGWFBP_COMM_THREADS', 512)
+        # two-shot / NVLS kernels work through a CTA's chunk in pieces (pack, reduce and update of successive pieces
+        # of different CTAs overlap); large messages use narrower CTAs, two of which fit on an SM
+        self.max_pieces = max(1, _env_int('MGWFBP_PIECES', 1))
+        self.piece_slots = max(1, _env_int('MGWFBP_PIECE_SLOTS', 4096))
+        self.big_threads = _env_int('MGWFBP_BIG_THREADS', 512)
+        self.big_bytes = _env_int('MGWFBP_BIG_BYTES', 8 << 20)
         # control block: flag rows + per-CTA launch counters, in a heap of its own
         self._flag_bytes = int(self.lib.mgw_flag_block_bytes())
         self._ctl = make_heap(self.lib, 2 * (self._flag_bytes + 4 * _lib.MAX_CTAS + _ALIGN))
@@ -165,6 +172,7 @@ class NvlComm(Communicator):
         self._heaps: List[object] = []
         self._scratch = None            # (heap, stage_off, capacity_vec) for allreduce_async_
         self._scratch_tables: Dict[Tuple[int, int], GroupTable] = {}
+        self._scratch_geometry = None
         self._done_event = torch.cuda.Event()
         self._plans: Dict[int, List[_GroupPlan]] = {}
         self._hyper: Dict[int, HyperTable] = {}
@@ -229,9 +237,14 @@ class NvlComm(Communicator):
             per_cta = 2 * self.n_threads
             n_ctas = max(1, min(self.max_ctas_oneshot, (n_vec + per_cta - 1) // per_cta))
         else:
-            per_cta = 8 * self.n_threads
+            per_cta = 8 * self._threads_for(algo, n_vec)
             n_ctas = max(1, min(self.max_ctas_twoshot, (n_vec + per_cta - 1) // per_cta))
         return algo, n_ctas
+
+    def _threads_for(self, algo: int, n_vec: int) -> int:
+        if algo != _lib.ALGO_ONESHOT and 16 * n_vec >= self.big_bytes:
+            return self.big_threads
+        return self.n_threads
 
     def _fill_args(self, plan: _GroupPlan, heap, hyper_ptr: int, partials_ptr: int,
                    inbox_stride: Optional[int] = None, stage_slots: Optional[int] = None) -> None:
@@ -246,7 +259,9 @@ class NvlComm(Communicator):
         a.sumsq_partials = partials_ptr or None
         a.status = C.cast(self._status, C.c_void_p).value
         a.rank, a.world = self._rank, self._world
-        a.algo, a.n_ctas, a.n_threads = plan.algo, plan.n_ctas, self.n_threads
+        a.algo, a.n_ctas, a.n_threads = plan.algo, plan.n_ctas, self._threads_for(plan.algo, plan.table.n_vec)
+        a.max_pieces, a.piece_slots = self.max_pieces, self.piece_slots
+        a.grad_scale = 1.0
         a.mode, a.first_step = 0, 0
         a.inbox_stride = plan.table.n_vec if inbox_stride is None else inbox_stride
         a.stage_slots = plan.table.n_vec if stage_slots is None else stage_slots
@@ -342,6 +357,7 @@ class NvlComm(Communicator):
         a = plan.args
         a.mode = opt._nvl_mode
         a.first_step = int(opt._nvl_first_step)
+        a.grad_scale = float(getattr(opt, '_grad_scale', 1.0))
         _lib.check(self.lib.mgw_allreduce_group(C.byref(a), self.stream.cuda_stream), 'allreduce_group')
         opt._nvl_held.append(grads)
         self.launches += 1
@@ -453,7 +469,7 @@ class NvlComm(Communicator):
                     p.grad = torch.empty_like(p)
                 grad_out = p.grad
             wgrad.wgrad_sgd_(dy_all, x_all, st['param'].data, st['mom'], self._hyper[id(opt)].data_ptr(), st['pg'],
-                             scale=1.0 / w, first_step=bool(st['first']), grad_out=grad_out, stream=self.stream)
+                             scale=float(getattr(opt, '_grad_scale', 1.0)) / w, first_step=bool(st['first']), grad_out=grad_out, stream=self.stream)
         st['first'] = False
         opt._nvl_held.append((dy, x))
         opt._synchronized = False
@@ -509,6 +525,15 @@ class NvlComm(Communicator):
         if n_ctas is not None:
             plan.n_ctas = n_ctas
         plan.stage_off = sc['os_off'] if plan.algo == _lib.ALGO_ONESHOT else sc['ts_off']
+        geometry = (plan.algo, n_vec, plan.n_ctas)
+        if geometry != self._scratch_geometry:
+            # Calls of different shapes cut the shared scratch area into different per-CTA chunks, and the
+            # flag protocol only orders a CTA against the SAME CTA of its peers.  Every rank sees the change at
+            # the same call, so all of them drain their queues and meet here before the area is reused.
+            if not torch.cuda.is_current_stream_capturing():
+                torch.cuda.synchronize()
+                runtime.barrier()
+            self._scratch_geometry = geometry
         self._fill_args(plan, sc['heap'], 0, 0, inbox_stride=sc['os_cap'], stage_slots=sc['ts_cap'])
         compute = torch.cuda.current_stream()
         ready = torch.cuda.Event()

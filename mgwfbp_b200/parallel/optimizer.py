@@ -106,6 +106,7 @@ class _DistributedMixin:
         want_fused = settings.FUSED_UPDATE if fused_update is None else bool(fused_update)
         self._fused_comm = bool(getattr(self._comm, 'fused', False))
         self._fused_update = bool(want_fused and self._fused_comm and self._base_is_sgd and norm_clip is None)
+        self._grad_scale = 1.0           # see set_grad_scale
         self._shadow = None
         if settings.SHADOW_EVERY > 0 and self._fused_comm and self._base_is_sgd:
             from ..utils.consistency import ShadowChecker
@@ -374,8 +375,14 @@ class _DistributedMixin:
         if self._norm_clip is not None and not self.local and getattr(self, '_fast_sgd', None) is None:
             # global L2-norm clip of the averaged gradient (the reference's loop calls
             # clip_grad_norm_ between synchronize() and step(), dist_trainer.py:89-94)
-            params = [p for g in self.param_groups for p in g['params'] if p.grad is not None]
-            torch.nn.utils.clip_grad_norm_(params, self._norm_clip)
+            self._unscale_grads_()
+            scale, self._grad_scale = self._grad_scale, 1.0          # already divided out
+            try:
+                params = [p for g in self.param_groups for p in g['params'] if p.grad is not None]
+                torch.nn.utils.clip_grad_norm_(params, self._norm_clip)
+                return self._local_step(closure)
+            finally:
+                self._grad_scale = scale
         return self._local_step(closure)
 
     def _print_profiling(self) -> None:
@@ -410,10 +417,26 @@ class _DistributedMixin:
                                'weight-gradient layers; construct the model with MGWFBP_GATHERED_WGRAD=0')
         self._local = bool(value)
 
+    def set_grad_scale(self, scale: float) -> None:
+        """Gradients arrive multiplied by ``1 / scale`` (a static loss scale): every update path divides it out --
+        inside the fused all-reduce kernel and the multi-tensor SGD kernel, by one ``_foreach_mul_`` elsewhere."""
+        if not scale > 0.0:
+            raise ValueError('gradient scale must be positive')
+        self._grad_scale = float(scale)
+
+    def _unscale_grads_(self) -> None:
+        grads = [p.grad for g in self.param_groups for p in g['params'] if p.grad is not None]
+        if grads and self._grad_scale != 1.0:
+            torch._foreach_mul_(grads, self._grad_scale)
+
     def _local_step(self, closure=None):
         fast = getattr(self, '_fast_sgd', None)
         if fast is not None and closure is None:
-            return fast.step(self)
+            if self._norm_clip is not None and self._grad_scale != 1.0:
+                self._unscale_grads_()           # the clip needs the norm of the true gradient
+                return fast.step(self)
+            return fast.step(self, grad_scale=self._grad_scale)
+        self._unscale_grads_()
         return self._base_cls.step(self, closure)
 
     def zero_grad(self, set_to_none: Optional[bool] = None):

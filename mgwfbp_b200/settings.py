@@ -42,7 +42,12 @@ WARMUP = _env_flag('WARMUP', True)
 # peer-to-peer kernels of this package on an NVSwitch box.
 CONNECTION = _env_str('CONNECTION', 'NVLink5')
 
+# Mixed precision in the sense of the reference's ``FP16`` switch (apex amp O2 with a static loss scale of 128,
+# reference dl_trainer.py:278-281,821): fp32 master weights and fp32 gradients, half-precision forward / backward
+# math (``torch.autocast``), the loss multiplied by ``LOSS_SCALE`` before backward and the gradients divided by it
+# inside the update kernels.
 FP16 = _env_flag('FP16', False)
+LOSS_SCALE = float(_env_str('LOSS_SCALE', '128.0'))
 ADAPTIVE_MERGE = _env_flag('ADAPTIVE_MERGE', True)
 ORIGINAL_HOROVOD = _env_flag('ORIGINAL_HOROVOD', False)
 

@@ -15,6 +15,7 @@ checkpoint whose file name the reference computes is actually written.
 """
 from __future__ import annotations
 
+import contextlib
 import math
 import os
 import time
@@ -56,6 +57,8 @@ class DLTrainer:
         self.data_dir = data_dir
         self.is_cuda = ngpus > 0 and torch.cuda.is_available()
         self.device = torch.device('cuda', torch.cuda.current_device()) if self.is_cuda else torch.device('cpu')
+        self.fp16 = bool(settings.FP16 and self.is_cuda)
+        self.loss_scale = float(settings.LOSS_SCALE) if self.fp16 else 1.0
         self.fuse = (self.is_cuda and settings.FUSE_MODULES) if fuse is None else bool(fuse)
         self.channels_last = (self.is_cuda and settings.CHANNELS_LAST) if channels_last is None else bool(channels_last)
         if seed is not None:
@@ -178,6 +181,23 @@ class DLTrainer:
 
     def update_optimizer(self, optimizer):
         self.optimizer = optimizer
+        if self.loss_scale != 1.0:
+            if not hasattr(optimizer, 'set_grad_scale'):
+                raise ValueError('FP16 training scales the loss; wrap the optimizer in DistributedOptimizer so the update divides it out')
+            optimizer.set_grad_scale(1.0 / self.loss_scale)
+
+    def autocast(self):
+        """Context of the forward pass: half-precision math when ``settings.FP16`` (reference: apex amp O2)."""
+        if self.fp16:
+            return torch.autocast('cuda', dtype=torch.float16)
+        return contextlib.nullcontext()
+
+    def backward(self, loss) -> None:
+        """``loss.backward()`` with the static loss scale of the FP16 mode (reference dl_trainer.py:821)."""
+        if self.loss_scale != 1.0:
+            (loss * self.loss_scale).backward()
+        else:
+            loss.backward()
 
     def zero_grad(self):
         self.optimizer.zero_grad()
@@ -498,17 +518,19 @@ class DLTrainer:
             if hidden is None or (isinstance(hidden, str) and hidden == 'fresh'):
                 hidden = self.net.init_hidden()
             hidden = repackage_hidden(hidden)
-            outputs, hidden = self.net(inputs, hidden)
-            loss = self.criterion(outputs.view(-1, self.net.vocab_size), labels.reshape(-1))
-            return loss, outputs, labels, hidden
+            with self.autocast():
+                outputs, hidden = self.net(inputs, hidden)
+                loss = self.criterion(outputs.view(-1, self.net.vocab_size), labels.reshape(-1))
+            return loss.float(), outputs, labels, hidden
         inputs, labels = batch
-        outputs = self.net(inputs)
-        if isinstance(outputs, tuple):               # inception-v3 with auxiliary logits
-            loss = self.criterion(outputs[0], labels) + 0.4 * sum(self.criterion(o, labels) for o in outputs[1:])
-            outputs = outputs[0]
-        else:
-            loss = self.criterion(outputs, labels)
-        return loss, outputs, labels, None
+        with self.autocast():
+            outputs = self.net(inputs)
+            if isinstance(outputs, tuple):               # inception-v3 with auxiliary logits
+                loss = self.criterion(outputs[0], labels) + 0.4 * sum(self.criterion(o, labels) for o in outputs[1:])
+                outputs = outputs[0]
+            else:
+                loss = self.criterion(outputs, labels)
+        return loss.float(), outputs, labels, None
 
     # ------------------------------------------------------------------ training
     def _on_epoch_boundary(self):
@@ -543,7 +565,7 @@ class DLTrainer:
             loss, outputs, labels, hidden = self.forward_loss(batch, hidden, on_device=True)
             self.forwardtime += time.time() - sf
             sb = time.time()
-            loss.backward()
+            self.backward(loss)
             self.backwardtime += time.time() - sb
             ld = loss.detach()
             loss_acc = ld if loss_acc is None else loss_acc + ld

@@ -147,6 +147,7 @@ def test_bounded_wait_reports_timeout_without_hanging(lib):
     a.status = C.cast(status, C.c_void_p).value
     a.rank, a.world, a.algo, a.n_ctas, a.n_threads = 0, 2, _lib.ALGO_TWOSHOT, 1, 128
     a.mode, a.first_step, a.inbox_stride, a.stage_slots = _lib.MODE_WRITEBACK, 0, table.n_vec, table.n_vec
+    a.max_pieces, a.piece_slots, a.grad_scale = 1, 4096, 1.0
     a.timeout_ns = 50_000_000        # 50 ms
     _lib.check(lib.mgw_allreduce_group(C.byref(a), torch.cuda.current_stream().cuda_stream))
     torch.cuda.synchronize()

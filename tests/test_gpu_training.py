@@ -56,3 +56,40 @@ def test_graph_replay_matches_eager_trajectory():
     finally:
         torch.backends.cudnn.allow_tf32 = True
         torch.backends.cudnn.deterministic = False
+
+
+def test_fp16_mode_trains_and_tracks_fp32():
+    """``settings.FP16``: half-precision forward/backward under autocast, static loss scale 128 divided out inside the
+    update kernel.  The fp32 master weights after a few steps stay close to those of an fp32 run from the same start."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
+    from mgwfbp_b200.trainer import DLTrainer
+    results = {}
+    old = settings.FP16
+    try:
+        for fp16 in (False, True):
+            settings.FP16 = fp16
+            torch.manual_seed(0)
+            trainer = DLTrainer(0, 1, dist=False, batch_size=16, ngpus=1, data_dir='synthetic', dataset='cifar10', dnn='resnet20',
+                                lr=0.05, nworkers=1, seed=0)
+            assert trainer.fp16 == fp16 and trainer.loss_scale == (128.0 if fp16 else 1.0)
+            opt = hvd.DistributedOptimizer(trainer.optimizer, named_parameters=trainer.net.named_parameters())
+            trainer.update_optimizer(opt)
+            assert opt._grad_scale == (1.0 / 128.0 if fp16 else 1.0)
+            losses = []
+            for _ in range(6):
+                opt.zero_grad()
+                trainer.train(1)
+                trainer.update_model()
+                losses.append(trainer.loss)
+            torch.cuda.synchronize()
+            results[fp16] = (losses, [p.detach().float().clone() for p in trainer.net.parameters()])
+    finally:
+        settings.FP16 = old
+    l32, p32 = results[False]
+    l16, p16 = results[True]
+    assert all(l == l and l < 20 for l in l16)
+    assert abs(l16[0] - l32[0]) < 0.05 * abs(l32[0]) + 1e-2          # same data, same start: first loss agrees to fp16 accuracy
+    num = sum(float((a - b).pow(2).sum()) for a, b in zip(p16, p32))
+    den = sum(float(b.pow(2).sum()) for b in p32)
+    assert (num / den) ** 0.5 < 2e-2, 'fp16 run drifted from the fp32 run: relative distance %.4f' % ((num / den) ** 0.5)

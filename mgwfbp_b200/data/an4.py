@@ -14,7 +14,7 @@ from __future__ import annotations
 import csv
 import math
 import wave
-from typing import List, Sequence, Tuple
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -134,6 +134,23 @@ class GreedyDecoder:
     @staticmethod
     def cer(s1: str, s2: str) -> int:
         return _edit_distance(s1.replace(' ', ''), s2.replace(' ', ''))
+
+
+def wav_duration(path: str) -> float:
+    """Length of a PCM wave file in seconds, from its header (the reference shells out to ``soxi -D``)."""
+    with wave.open(path, 'rb') as w:
+        return w.getnframes() / float(w.getframerate())
+
+
+def order_and_prune_files(file_paths: Sequence[str], min_duration: Optional[float] = None,
+                          max_duration: Optional[float] = None) -> List[str]:
+    """Audio files sorted by duration, shortest first; with both bounds given, files outside
+    ``[min_duration, max_duration]`` seconds are dropped (reference ``audio_data/utils.py:24-37``)."""
+    timed = [(p.strip(), wav_duration(p.strip())) for p in file_paths]
+    if min_duration and max_duration:
+        timed = [(p, d) for p, d in timed if min_duration <= d <= max_duration]
+    timed.sort(key=lambda pd: pd[1])
+    return [p for p, _ in timed]
 
 
 def create_manifest(data_path: str, tag: str, ordered: bool = True, out_dir: str = '.') -> str:

@@ -256,3 +256,19 @@ def test_speech_and_language_model_paths_train_on_synthetic_data():
     assert t.loss == t.loss and hidden[0].shape == (2, 4, 1500)
     step = (t.net.sm_fc.weight.detach() - before).norm()
     assert 0 < float(step) <= 22.0 * 0.25 * 2 + 1e-3       # clipped gradient norm bounds each update
+
+
+def test_order_and_prune_files_by_duration(tmp_path):
+    import wave
+    import numpy as np
+    from mgwfbp_b200.data.an4 import order_and_prune_files, wav_duration
+    paths = []
+    for i, seconds in enumerate([0.8, 0.2, 1.5, 0.5]):
+        p = tmp_path / ('u%d.wav' % i)
+        with wave.open(str(p), 'wb') as w:
+            w.setnchannels(1); w.setsampwidth(2); w.setframerate(16000)
+            w.writeframes(np.zeros(int(16000 * seconds), dtype=np.int16).tobytes())
+        paths.append(str(p))
+    assert abs(wav_duration(paths[2]) - 1.5) < 1e-6
+    assert order_and_prune_files(paths) == [paths[1], paths[3], paths[0], paths[2]]
+    assert order_and_prune_files(paths, 0.4, 1.0) == [paths[3], paths[0]]

@@ -188,6 +188,30 @@ def _absent_rank(rank, world):
         return {'error': type(e).__name__, 'waited': time.time() - t0}
 
 
+def _flat_ddp(rank, world):
+    """The whole-model gradient-averaging wrapper: state broadcast, one reduction per backward, large-batch equality."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200.parallel.flat_ddp import DistributedDataParallel, reduce_tensor
+    torch.manual_seed(rank)                              # ranks start different; construction must align them
+    net = torch.nn.Sequential(torch.nn.Linear(12, 20), torch.nn.Tanh(), torch.nn.Linear(20, 3))
+    ddp = DistributedDataParallel(net)
+    torch.manual_seed(0)
+    ref = torch.nn.Sequential(torch.nn.Linear(12, 20), torch.nn.Tanh(), torch.nn.Linear(20, 3))
+    opt, ropt = torch.optim.SGD(net.parameters(), lr=0.1), torch.optim.SGD(ref.parameters(), lr=0.1)
+    g = torch.Generator().manual_seed(3)
+    for _ in range(3):
+        x = torch.randn(world * 4, 12, generator=g)
+        opt.zero_grad()
+        ddp(x[rank * 4:(rank + 1) * 4]).pow(2).mean().backward()
+        opt.step()
+        ropt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        ropt.step()
+    mean_rank = reduce_tensor(torch.tensor([float(rank)]))
+    return {'dp': [p.detach().clone() for p in net.parameters()], 'ref': [p.detach().clone() for p in ref.parameters()],
+            'reductions': ddp.reductions, 'mean_rank': float(mean_rank)}
+
+
 # ----------------------------------------------------------------------------- tests
 @pytest.fixture(scope='module')
 def resnet20_runs():
@@ -263,3 +287,13 @@ def test_absent_rank_surfaces_as_timeout_not_hang(monkeypatch):
     monkeypatch.setenv('MGWFBP_TEST_TIMEOUT_S', '3')
     r0, r1 = run_ranks(_absent_rank)
     assert r0['error'] is not None and r0['waited'] < 30
+
+
+def test_flat_allreduce_wrapper_matches_large_batch():
+    res = run_ranks(_flat_ddp, (), world=2)
+    for r in res:
+        assert r['reductions'] == 3 and r['mean_rank'] == 0.5
+        for a, b in zip(r['dp'], r['ref']):
+            torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
+    for a, b in zip(res[0]['dp'], res[1]['dp']):
+        assert torch.equal(a, b)

@@ -67,6 +67,11 @@ int mgw_clip_coef(const float* partials, int n, float max_norm, float* out2, voi
 // Sum of squares of the gradients of a group (one partial per CTA, deterministic).
 int mgw_group_sumsq(const MgwGroup* group, float* partials, int n_ctas, void* stream);
 
+// ---- stem convolution input rearrangement (stem_s2d.cu) ---------------------------------------------
+// x [N, H, W, 3] channels-last image batch (H, W even) -> out [N, H/2 + 3, W/2 + 3, 12], zero padded:
+// out[n, j, i, p*6 + q*3 + c] = x[n, 2j + p - 4, 2i + q - 4, c].
+int mgw_s2d_stem_input(const float* x, float* out, int N, int H, int W, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

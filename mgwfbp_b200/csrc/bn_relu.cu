@@ -198,11 +198,11 @@ bn_bwd_finalize_kernel(const float* __restrict__ partials, int n_splits, int C, 
     }
 }
 
-template <int VEC>
+template <int VEC, bool BITS>
 __global__ void __launch_bounds__(kThreads, 4)
 bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ residual, float* __restrict__ y, long long M, int C,
                 int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta, int relu,
-                const float* __restrict__ save_mean, const float* __restrict__ save_invstd) {
+                const float* __restrict__ save_mean, const float* __restrict__ save_invstd, unsigned char* __restrict__ bits) {
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int c0 = (blockIdx.x * TX + tx) * VEC;
@@ -229,6 +229,12 @@ bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ residual,
         } else {
 #pragma unroll
             for (int k = 0; k < VEC; ++k) o[k] = fmaf(v[k], sc[k], sh[k]);
+        }
+        if (VEC == 4 && BITS) {
+            // which of the four outputs the ReLU lets through, one byte per float4: backward reads this
+            // instead of the whole output tensor
+            bits[(r * C + c0) >> 2] = (unsigned char)((o[0] > 0.f ? 1 : 0) | (o[1 % VEC] > 0.f ? 2 : 0) |
+                                                      (o[2 % VEC] > 0.f ? 4 : 0) | (o[3 % VEC] > 0.f ? 8 : 0));
         }
         if (relu) {
 #pragma unroll
@@ -279,11 +285,16 @@ __device__ __forceinline__ void pooled_grad(float (&g)[VEC], const PoolArgs& pa,
 
 // Gradient entering the normalisation for one vector of channels: dy, masked by the ReLU.
 // mask_mode 0: no ReLU; 1: mask from the saved output y; 2: mask recomputed from x (bitwise the same
-// fused multiply-add as the forward pass, so the sign test agrees with what the forward pass clipped).
+// fused multiply-add as the forward pass, so the sign test agrees with what the forward pass clipped);
+// 3: mask from the byte the forward pass stored for this float4 (y_row then points at that byte).
 template <int VEC>
 __device__ __forceinline__ void masked_grad(float (&g)[VEC], const float (&xv)[VEC], const float* __restrict__ y_row, int mask_mode,
                                             const float (&sc)[VEC], const float (&sh)[VEC]) {
-    if (mask_mode == 1) {
+    if (mask_mode == 3) {
+        const unsigned b = *reinterpret_cast<const unsigned char*>(y_row);
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) g[k] = ((b >> k) & 1u) ? g[k] : 0.f;
+    } else if (mask_mode == 1) {
         float yv[VEC];
         load_vec<VEC>(y_row, yv);
 #pragma unroll
@@ -312,8 +323,8 @@ __device__ __forceinline__ void load_channel_consts(int c0, int C, const float* 
 
 template <int VEC, bool POOL>
 __global__ void __launch_bounds__(kThreads, 2)
-bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2, const float* __restrict__ y, const float* __restrict__ x,
-                     float* __restrict__ dz,
+bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2, const float* __restrict__ y,
+                     const unsigned char* __restrict__ bits, const float* __restrict__ x, float* __restrict__ dz,
                      long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                      const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
                      float* __restrict__ partials, const PoolArgs pool) {
@@ -340,7 +351,9 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) g[k] += h[k];
             }
-            masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0 : nullptr, mask_mode, sc, sh);
+            masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0
+                                               : (mask_mode == 3 ? reinterpret_cast<const float*>(bits + ((r * C + c0) >> 2)) : nullptr),
+                             mask_mode, sc, sh);
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
                 s[k] += g[k];
@@ -365,8 +378,8 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
 // gsrc is dz (mask already applied, mask_mode 0) or dy (mask applied here again, mask_mode 1 / 2).
 template <int VEC, bool POOL>
 __global__ void __launch_bounds__(kThreads, 2)
-bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gsrc2, const float* __restrict__ y, const float* __restrict__ x,
-                    float* __restrict__ dx,
+bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gsrc2, const float* __restrict__ y,
+                    const unsigned char* __restrict__ bits, const float* __restrict__ x, float* __restrict__ dx,
                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                     const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
                     const float* __restrict__ dgamma, const float* __restrict__ dbeta, const PoolArgs pool) {
@@ -395,7 +408,9 @@ bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gs
 #pragma unroll
             for (int k = 0; k < VEC; ++k) g[k] += h[k];
         }
-        masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0 : nullptr, mask_mode, sc, sh);
+        masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0
+                                               : (mask_mode == 3 ? reinterpret_cast<const float*>(bits + ((r * C + c0) >> 2)) : nullptr),
+                             mask_mode, sc, sh);
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
             const float xhat = (xv[k] - mean[k]) * istd[k];
@@ -465,9 +480,10 @@ size_t mgw_bn_partials_floats(long long M, int C) {
 
 int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M, int C, const float* gamma, const float* beta,
                     float* running_mean, float* running_var, long long* num_batches_tracked, float momentum, float eps,
-                    int relu, float* save_mean, float* save_invstd, float* partials, void* stream) {
+                    int relu, float* save_mean, float* save_invstd, float* partials, unsigned char* relu_bits, void* stream) {
     if (x == nullptr || y == nullptr || M <= 0 || C <= 0 || save_mean == nullptr || save_invstd == nullptr || partials == nullptr)
         return MGW_ERR_ARG;
+    if (relu_bits != nullptr && (C % 4 != 0 || !relu)) return MGW_ERR_ARG;
     const int vec = (C % 4 == 0) ? 4 : 1;
     const Tiling t = make_tiling(M, C, vec);
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
@@ -478,12 +494,15 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
         bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
         bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
                                                         momentum, eps, save_mean, save_invstd);
-        bn_apply_kernel<4><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd);
+        if (relu_bits)
+            bn_apply_kernel<4, true><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd, relu_bits);
+        else
+            bn_apply_kernel<4, false><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd, nullptr);
     } else {
         bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
         bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
                                                         momentum, eps, save_mean, save_invstd);
-        bn_apply_kernel<1><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd);
+        bn_apply_kernel<1, false><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd, nullptr);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
@@ -494,14 +513,17 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
 // add kernel.  With dz != null the masked gradient dy * (y > 0) is written there (it is also the gradient
 // of the residual input) and the ReLU mask comes from y; dx may alias dz.  With dz == null nothing is
 // materialised: both passes read dy and x and rebuild the mask from x (gamma / beta must be the forward
-// values), which saves one read and one write of the activation.
+// values), which saves one read and one write of the activation.  relu_bits (may be null; needs C % 4 == 0)
+// is the byte-per-float4 ReLU mask the forward pass recorded: with it the reduce pass reads M*C/4 bytes
+// instead of the M*C floats of y.
 int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const float* x, float* dz, float* dx, long long M, int C, const float* gamma,
                     const float* beta, const float* save_mean, const float* save_invstd, int relu, float* dgamma, float* dbeta,
-                    float* partials, void* stream) {
+                    float* partials, const unsigned char* relu_bits, void* stream) {
     if (dy == nullptr || x == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
+    if (relu_bits != nullptr && (C % 4 != 0 || !relu)) return MGW_ERR_ARG;
     if (dgamma == nullptr || dbeta == nullptr || save_mean == nullptr || save_invstd == nullptr) return MGW_ERR_ARG;
     const PoolArgs pool = {nullptr, nullptr, 0, 0, 0, 0};
-    const int mask1 = !relu ? 0 : (y != nullptr ? 1 : 2);          // mask used by the reduce pass
+    const int mask1 = !relu ? 0 : (relu_bits != nullptr ? 3 : (y != nullptr ? 1 : 2));          // mask used by the reduce pass
     const int mask2 = dz != nullptr ? 0 : mask1;                   // apply pass: dz already carries the mask
     const float* gsrc = dz != nullptr ? dz : dy;
     const float* gsrc2 = dz != nullptr ? nullptr : dy2;        // dz already holds the sum of both gradients
@@ -512,13 +534,13 @@ int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const flo
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     if (vec == 4) {
-        bn_bwd_reduce_kernel<4, false><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
+        bn_bwd_reduce_kernel<4, false><<<grid, block, smem_red, s>>>(dy, dy2, y, relu_bits, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<4, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, relu_bits, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     } else {
-        bn_bwd_reduce_kernel<1, false><<<grid, block, smem_red, s>>>(dy, dy2, y, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
+        bn_bwd_reduce_kernel<1, false><<<grid, block, smem_red, s>>>(dy, dy2, y, relu_bits, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<1, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, relu_bits, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
@@ -572,13 +594,13 @@ int mgw_bn_relu_maxpool_bwd(const float* dp, const unsigned char* idx, const flo
     const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     if (vec == 4) {
-        bn_bwd_reduce_kernel<4, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
+        bn_bwd_reduce_kernel<4, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<4, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     } else {
-        bn_bwd_reduce_kernel<1, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
+        bn_bwd_reduce_kernel<1, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<1, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;

@@ -21,6 +21,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 
 from ..ops.bn_relu import FusedBatchNorm1d, FusedBatchNorm2d, bn_relu_maxpool
+from ..ops.stem import convert_stem
 
 
 def _to_fused(bn: nn.Module, relu: bool) -> nn.Module:
@@ -134,12 +135,14 @@ def fuse_model(net: nn.Module) -> nn.Module:
             _bind(m, _tv_basicblock_forward)
         elif ResNet and isinstance(m, ResNet):
             _to_fused(m.bn1, True)
+            m.conv1 = convert_stem(m.conv1)          # 7x7 / stride 2 on 3 channels as 4x4 on the space-to-depth input
             _bind(m, _tv_resnet_forward_impl)
         elif _DenseLayer and isinstance(m, _DenseLayer) and not m.memory_efficient:
             _to_fused(m.norm1, True), _to_fused(m.norm2, True)
             _bind(m, _tv_denselayer_forward)
         elif DenseNet and isinstance(m, DenseNet):
             _to_fused(m.features.norm0, True)
+            m.features.conv0 = convert_stem(m.features.conv0)
             m.features.relu0 = nn.Identity()
             _to_fused(m.features.norm5, True)
             _bind(m, _tv_densenet_forward)

@@ -72,6 +72,7 @@ def _declare(lib: C.CDLL) -> None:
     lib.mgw_bounds_allreduce.argtypes = [C.POINTER(C.c_int)]
     lib.mgw_bounds_sgd.argtypes = [C.POINTER(C.c_int)]
     lib.mgw_phase_times.argtypes = [C.POINTER(C.c_ulonglong), C.c_int]
+    lib.mgw_s2d_stem_input.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
     for name in ('mgw_bn_relu_fwd', 'mgw_bn_relu_bwd', 'mgw_lstm_cell_fwd', 'mgw_lstm_cell_bwd',
                  'mgw_wgrad_gemm', 'mgw_wgrad_gemm_supported', 'mgw_allgather_rows'):
         if hasattr(lib, name):

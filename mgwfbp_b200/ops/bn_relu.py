@@ -43,10 +43,10 @@ def _declare(lib) -> None:
     lib.mgw_bn_partials_floats.argtypes = [C.c_longlong, C.c_int]
     lib.mgw_bn_relu_fwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_void_p,
-                                    C.c_void_p, C.c_void_p, C.c_void_p]
+                                    C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.mgw_bn_relu_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
-                                    C.c_void_p, C.c_void_p]
+                                    C.c_void_p, C.c_void_p, C.c_void_p]
     _declared = True
 
 
@@ -65,13 +65,17 @@ class _BNReLU(torch.autograd.Function):
         invstd = torch.empty(Cc, dtype=torch.float32, device=x.device)
         partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
         s = torch.cuda.current_stream().cuda_stream
+        # With a residual the ReLU mask cannot be rebuilt from x alone.  The forward kernel then records it as
+        # one byte per float4 (1/16 of the tensor) and backward reads that instead of the output tensor; when
+        # the channel count is not a multiple of 4 the output itself is kept.
+        needs_mask = bool(relu and residual is not None)
+        bits = torch.empty((M * Cc) // 4, dtype=torch.uint8, device=x.device) if (needs_mask and Cc % 4 == 0) else None
         _lib.check(lib.mgw_bn_relu_fwd(x.data_ptr(), _ptr(residual), y.data_ptr(), M, Cc, _ptr(weight), _ptr(bias),
                                        _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
                                        float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
-                                       partials.data_ptr(), s), 'bn_relu_fwd')
+                                       partials.data_ptr(), _ptr(bits), s), 'bn_relu_fwd')
         counters.bump('bn_relu_fwd', 3)
-        # the output is only needed to rebuild the ReLU mask when a residual was added
-        ctx.save_for_backward(x, y if (relu and residual is not None) else None, weight, bias, mean, invstd)
+        ctx.save_for_backward(x, y if (needs_mask and bits is None) else None, weight, bias, mean, invstd, bits)
         ctx.relu, ctx.has_residual, ctx.rows = bool(relu), residual is not None, (M, Cc)
         ctx.mark_non_differentiable(*[t for t in (running_mean, running_var, num_batches_tracked) if t is not None])
         if dual:
@@ -85,7 +89,7 @@ class _BNReLU(torch.autograd.Function):
         lib = _lib.load(allow_build=False)
         if dy is None:
             dy, dy2 = dy2, None
-        x, y, weight, bias, mean, invstd = ctx.saved_tensors
+        x, y, weight, bias, mean, invstd, bits = ctx.saved_tensors
         M, Cc = ctx.rows
         if _as_rows(dy) is None or dy.stride() != x.stride():
             dy = dy.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else dy.contiguous()
@@ -99,7 +103,7 @@ class _BNReLU(torch.autograd.Function):
         s = torch.cuda.current_stream().cuda_stream
         _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
                                        _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
-                                       dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), s), 'bn_relu_bwd')
+                                       dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), _ptr(bits), s), 'bn_relu_bwd')
         counters.bump('bn_relu_bwd', 3)
         need = ctx.needs_input_grad
         return (dx if need[0] else None, dgamma if (weight is not None and need[1]) else None,

@@ -311,3 +311,36 @@ def test_bn_relu_maxpool_stem_matches_pytorch(shape):
     torch.testing.assert_close(x.grad, x2.grad, rtol=1e-3, atol=2e-4)
     torch.testing.assert_close(bn.weight.grad, ref.weight.grad, rtol=1e-3, atol=1e-3)
     torch.testing.assert_close(bn.bias.grad, ref.bias.grad, rtol=1e-3, atol=1e-3)
+
+
+# ----------------------------------------------------------------------------- stem convolution
+def test_s2d_stem_matches_conv2d():
+    """The 7x7/2 stem as a 4x4 convolution over the space-to-depth input: rearrangement kernel against tensor ops,
+    forward and weight gradient against ``nn.Conv2d`` in full fp32."""
+    from mgwfbp_b200.ops.stem import S2DStemConv2d, convert_stem, s2d_input, s2d_input_reference
+    torch.manual_seed(0)
+    old = torch.backends.cudnn.allow_tf32
+    torch.backends.cudnn.allow_tf32 = False
+    try:
+        for shape in [(4, 3, 64, 64), (2, 3, 224, 224), (3, 3, 32, 96)]:
+            x = torch.randn(*shape, device='cuda').contiguous(memory_format=torch.channels_last)
+            assert torch.equal(s2d_input(x), s2d_input_reference(x))
+            ref = torch.nn.Conv2d(3, 16, 7, stride=2, padding=3, bias=False).cuda()
+            new = convert_stem(ref)
+            assert isinstance(new, S2DStemConv2d) and new.weight is ref.weight
+            assert list(new.state_dict().keys()) == ['weight']
+            y_ref = torch.nn.functional.conv2d(x, ref.weight, None, 2, 3)
+            y_new = new(x)
+            assert y_new.shape == y_ref.shape
+            torch.testing.assert_close(y_new, y_ref, rtol=1e-4, atol=1e-4)
+            dy = torch.randn_like(y_ref)
+            g_ref, = torch.autograd.grad(y_ref, ref.weight, dy)
+            g_new, = torch.autograd.grad(y_new, new.weight, dy)
+            torch.testing.assert_close(g_new, g_ref, rtol=1e-4, atol=1e-3)
+        # anything that is not the ImageNet stem is left alone, and odd sizes fall back to the parent
+        other = torch.nn.Conv2d(3, 8, 3, padding=1)
+        assert convert_stem(other) is other
+        odd = torch.randn(2, 3, 33, 33, device='cuda').contiguous(memory_format=torch.channels_last)
+        torch.testing.assert_close(new(odd), torch.nn.functional.conv2d(odd, ref.weight, None, 2, 3), rtol=1e-4, atol=1e-4)
+    finally:
+        torch.backends.cudnn.allow_tf32 = old

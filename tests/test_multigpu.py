@@ -15,9 +15,14 @@ def _world():
     return min(torch.cuda.device_count(), int(os.environ.get('MGWFBP_TEST_WORLD', '4')))
 
 
-def _allreduce_sweep(rank, world):
+def _allreduce_sweep(rank, world, pieces=1):
+    if pieces > 1:
+        # the two-shot kernel walks each CTA's chunk in several pieces, one flag value per piece
+        os.environ['MGWFBP_PIECES'] = str(pieces)
+        os.environ['MGWFBP_PIECE_SLOTS'] = '64'
     from mgwfbp_b200.parallel.comm.nvl import NvlComm
     comm = NvlComm.shared()
+    assert comm.max_pieces == pieces
     out = {}
     for algo in ('oneshot', 'twoshot'):
         for numel in (1, 7, 1024, 32771, 1 << 17, (1 << 22) + 3):
@@ -35,9 +40,10 @@ def _allreduce_sweep(rank, world):
     return out
 
 
-def test_allreduce_matches_cpu_sum_and_is_deterministic():
+@pytest.mark.parametrize('pieces', [1, 4])
+def test_allreduce_matches_cpu_sum_and_is_deterministic(pieces):
     world = _world()
-    res = run_ranks(_allreduce_sweep, (), world=world)
+    res = run_ranks(_allreduce_sweep, (pieces,), world=world)
     for key in res[0]:
         want = sum(r[key][0].double() for r in res) / world
         for r in res:

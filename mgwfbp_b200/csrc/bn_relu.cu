@@ -287,10 +287,10 @@ __device__ __forceinline__ void pooled_grad(float (&g)[VEC], const PoolArgs& pa,
 // mask_mode 0: no ReLU; 1: mask from the saved output y; 2: mask recomputed from x (bitwise the same
 // fused multiply-add as the forward pass, so the sign test agrees with what the forward pass clipped);
 // 3: mask from the byte the forward pass stored for this float4 (y_row then points at that byte).
-template <int VEC>
+template <int VEC, bool BYTE_MASK = false>
 __device__ __forceinline__ void masked_grad(float (&g)[VEC], const float (&xv)[VEC], const float* __restrict__ y_row, int mask_mode,
                                             const float (&sc)[VEC], const float (&sh)[VEC]) {
-    if (mask_mode == 3) {
+    if (BYTE_MASK && mask_mode == 3) {
         const unsigned b = *reinterpret_cast<const unsigned char*>(y_row);
 #pragma unroll
         for (int k = 0; k < VEC; ++k) g[k] = ((b >> k) & 1u) ? g[k] : 0.f;
@@ -351,9 +351,9 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
 #pragma unroll
                 for (int k = 0; k < VEC; ++k) g[k] += h[k];
             }
-            masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0
-                                               : (mask_mode == 3 ? reinterpret_cast<const float*>(bits + ((r * C + c0) >> 2)) : nullptr),
-                             mask_mode, sc, sh);
+            masked_grad<VEC, true>(g, xv, mask_mode == 1 ? y + r * C + c0
+                                                     : (mask_mode == 3 ? reinterpret_cast<const float*>(bits + ((r * C + c0) >> 2)) : nullptr),
+                                   mask_mode, sc, sh);
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
                 s[k] += g[k];
@@ -378,8 +378,8 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
 // gsrc is dz (mask already applied, mask_mode 0) or dy (mask applied here again, mask_mode 1 / 2).
 template <int VEC, bool POOL>
 __global__ void __launch_bounds__(kThreads, 2)
-bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gsrc2, const float* __restrict__ y,
-                    const unsigned char* __restrict__ bits, const float* __restrict__ x, float* __restrict__ dx,
+bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gsrc2, const float* __restrict__ y, const float* __restrict__ x,
+                    float* __restrict__ dx,
                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                     const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
                     const float* __restrict__ dgamma, const float* __restrict__ dbeta, const PoolArgs pool) {
@@ -408,9 +408,7 @@ bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gs
 #pragma unroll
             for (int k = 0; k < VEC; ++k) g[k] += h[k];
         }
-        masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0
-                                               : (mask_mode == 3 ? reinterpret_cast<const float*>(bits + ((r * C + c0) >> 2)) : nullptr),
-                             mask_mode, sc, sh);
+        masked_grad<VEC>(g, xv, mask_mode == 1 ? y + r * C + c0 : nullptr, mask_mode, sc, sh);
 #pragma unroll
         for (int k = 0; k < VEC; ++k) {
             const float xhat = (xv[k] - mean[k]) * istd[k];
@@ -520,7 +518,8 @@ int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const flo
                     const float* beta, const float* save_mean, const float* save_invstd, int relu, float* dgamma, float* dbeta,
                     float* partials, const unsigned char* relu_bits, void* stream) {
     if (dy == nullptr || x == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
-    if (relu_bits != nullptr && (C % 4 != 0 || !relu)) return MGW_ERR_ARG;
+    // the byte mask serves the reduce pass; the apply pass then reads the masked gradient dz, which must exist
+    if (relu_bits != nullptr && (C % 4 != 0 || !relu || dz == nullptr)) return MGW_ERR_ARG;
     if (dgamma == nullptr || dbeta == nullptr || save_mean == nullptr || save_invstd == nullptr) return MGW_ERR_ARG;
     const PoolArgs pool = {nullptr, nullptr, 0, 0, 0, 0};
     const int mask1 = !relu ? 0 : (relu_bits != nullptr ? 3 : (y != nullptr ? 1 : 2));          // mask used by the reduce pass
@@ -536,11 +535,11 @@ int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const flo
     if (vec == 4) {
         bn_bwd_reduce_kernel<4, false><<<grid, block, smem_red, s>>>(dy, dy2, y, relu_bits, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, relu_bits, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<4, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     } else {
         bn_bwd_reduce_kernel<1, false><<<grid, block, smem_red, s>>>(dy, dy2, y, relu_bits, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, relu_bits, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<1, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
@@ -596,11 +595,11 @@ int mgw_bn_relu_maxpool_bwd(const float* dp, const unsigned char* idx, const flo
     if (vec == 4) {
         bn_bwd_reduce_kernel<4, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<4, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     } else {
         bn_bwd_reduce_kernel<1, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
         bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
+        bn_bwd_apply_kernel<1, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;

@@ -64,6 +64,8 @@ FUSE_MODULES = _env_flag('FUSE', True)
 # The PTB model's recurrent part: torch.nn.LSTM (cuDNN's persistent kernels, faster at batch 20) unless this is set,
 # in which case mgwfbp_b200.ops.lstm.FusedLSTM (this package's cell kernels) is used.
 FUSE_LSTM = _env_flag('FUSE_LSTM', False)
+# How many algorithms cuDNN's benchmark mode may time per convolution shape (-1: leave PyTorch's default of 10, 0: all).
+CUDNN_BENCHMARK_LIMIT = int(_env_str('CUDNN_BENCHMARK_LIMIT', '-1'))
 # Keep convolutional models and their inputs in channels-last (NHWC) memory format on the GPU.
 CHANNELS_LAST = _env_flag('CHANNELS_LAST', True)
 

@@ -57,6 +57,12 @@ class DLTrainer:
         self.data_dir = data_dir
         self.is_cuda = ngpus > 0 and torch.cuda.is_available()
         self.device = torch.device('cuda', torch.cuda.current_device()) if self.is_cuda else torch.device('cpu')
+        if self.is_cuda:
+            # as the reference does at import time (dl_trainer.py:19-21): let cuDNN time its algorithms per shape;
+            # MGWFBP_CUDNN_BENCHMARK_LIMIT widens (0 = all) or narrows how many candidates it tries
+            torch.backends.cudnn.benchmark = True
+            if settings.CUDNN_BENCHMARK_LIMIT >= 0:
+                torch.backends.cudnn.benchmark_limit = settings.CUDNN_BENCHMARK_LIMIT
         self.fp16 = bool(settings.FP16 and self.is_cuda)
         self.loss_scale = float(settings.LOSS_SCALE) if self.fp16 else 1.0
         self.fuse = (self.is_cuda and settings.FUSE_MODULES) if fuse is None else bool(fuse)

@@ -272,3 +272,18 @@ def test_order_and_prune_files_by_duration(tmp_path):
     assert abs(wav_duration(paths[2]) - 1.5) < 1e-6
     assert order_and_prune_files(paths) == [paths[1], paths[3], paths[0], paths[2]]
     assert order_and_prune_files(paths, 0.4, 1.0) == [paths[3], paths[0]]
+
+
+def test_s2d_stem_algebra_on_cpu():
+    """4x4 / stride 1 over the space-to-depth input == 7x7 / stride 2 / padding 3, and the module keeps Conv2d's state."""
+    import torch.nn.functional as F
+    from mgwfbp_b200.ops.stem import S2DStemConv2d, convert_stem, s2d_input_reference, s2d_weight
+    torch.manual_seed(0)
+    x, w = torch.randn(2, 3, 32, 48), torch.randn(8, 3, 7, 7)
+    torch.testing.assert_close(F.conv2d(s2d_input_reference(x), s2d_weight(w), None, 1, 0), F.conv2d(x, w, None, 2, 3),
+                               rtol=1e-4, atol=1e-4)
+    conv = torch.nn.Conv2d(3, 8, 7, stride=2, padding=3, bias=False)
+    new = convert_stem(conv)
+    assert isinstance(new, S2DStemConv2d) and new.weight is conv.weight and list(new.state_dict()) == ['weight']
+    torch.testing.assert_close(new(x), conv(x))                       # CPU input: the parent's path
+    assert convert_stem(torch.nn.Conv2d(3, 8, 3)) is not None and not isinstance(convert_stem(torch.nn.Conv2d(3, 8, 3)), S2DStemConv2d)

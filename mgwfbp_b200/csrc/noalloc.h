@@ -17,7 +17,7 @@ extern "C" {
 //   out2[0] = sqrt(sum of squares),  out2[1] = min(1, max_norm / (out2[0] + 1e-6))     (device memory)
 //
 // Who needs this: code that is not allowed to call cudaMalloc (or any allocating routine) at the point
-// where it wants the norm -- a host application that gave this library a fixed memory budget and owns
+// where it wants the norm -- a host application that gave this library a fixed amount of memory and owns
 // every other byte of the device, or a latency-critical section in which an allocation could stall
 // the device.  The call itself allocates nothing, frees nothing and calls no library that might.
 //

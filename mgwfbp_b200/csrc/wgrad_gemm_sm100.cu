@@ -71,7 +71,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
 
-// Bounded parity wait.  Returns false when the phase did not complete within the spin budget.
+// Bounded parity wait.  Returns false when the phase did not complete within the spin limit.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     const uint32_t addr = smem_u32(bar);
     for (uint32_t spin = 0; spin < kWaitSpins; ++spin) {

@@ -7,7 +7,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-REFERENCE_DIR = os.environ.get('MGWFBP_REFERENCE_DIR', '/root/reference')
+# the reference checkout sits beside this repository unless MGWFBP_REFERENCE_DIR says otherwise
+REFERENCE_DIR = os.environ.get('MGWFBP_REFERENCE_DIR') or os.path.join(os.path.dirname(ROOT), 'reference')
 
 
 def pytest_configure(config):

@@ -1,7 +1,7 @@
 """The allocation-free norm / clip-coefficient entry point, called through its exported C symbol.
 
 Some hosts of this library may not allocate device memory when they need the gradient norm (a fixed
-memory budget, or a section where an allocation could stall the GPU).  For them the library keeps the
+amount of memory, or a section where an allocation could stall the GPU).  For them the library keeps the
 partial sums in a small built-in array.  This test checks that variant against the regular entry points,
 which take a caller-allocated buffer, on two calls in a row with different data (the shared array keeps
 the previous call's contents, which must not leak into the next result).

@@ -13,6 +13,7 @@ reference gets the same math from separate cuDNN BatchNorm, add and ReLU kernels
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -47,7 +48,23 @@ def _declare(lib) -> None:
     lib.mgw_bn_relu_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.mgw_bn_cluster_supported.argtypes = [C.c_longlong, C.c_int]
+    lib.mgw_bn_relu_fwd_cluster.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p,
+                                            C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_void_p,
+                                            C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.mgw_bn_relu_bwd_cluster.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong,
+                                            C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p,
+                                            C.c_void_p, C.c_void_p, C.c_void_p]
     _declared = True
+
+
+# Small activations (at most 16384 rows, channels a multiple of 16) take the one-launch cluster kernels
+# (csrc/bn_relu_cluster.cu) when MGWFBP_BN_CLUSTER=1; otherwise everything stays on the three-launch kernels.
+_CLUSTER = os.environ.get('MGWFBP_BN_CLUSTER', '0').strip().lower() not in ('0', 'false', 'no', 'off', '')
+
+
+def _use_cluster(lib, M: int, Cc: int) -> bool:
+    return _CLUSTER and bool(lib.mgw_bn_cluster_supported(M, Cc))
 
 
 def _ptr(t: Optional[torch.Tensor]):
@@ -63,18 +80,25 @@ class _BNReLU(torch.autograd.Function):
         y = torch.empty_like(x)
         mean = torch.empty(Cc, dtype=torch.float32, device=x.device)
         invstd = torch.empty(Cc, dtype=torch.float32, device=x.device)
-        partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
         s = torch.cuda.current_stream().cuda_stream
         # With a residual the ReLU mask cannot be rebuilt from x alone.  The forward kernel then records it as
         # one byte per float4 (1/16 of the tensor) and backward reads that instead of the output tensor; when
         # the channel count is not a multiple of 4 the output itself is kept.
         needs_mask = bool(relu and residual is not None)
         bits = torch.empty((M * Cc) // 4, dtype=torch.uint8, device=x.device) if (needs_mask and Cc % 4 == 0) else None
-        _lib.check(lib.mgw_bn_relu_fwd(x.data_ptr(), _ptr(residual), y.data_ptr(), M, Cc, _ptr(weight), _ptr(bias),
-                                       _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
-                                       float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
-                                       partials.data_ptr(), _ptr(bits), s), 'bn_relu_fwd')
-        counters.bump('bn_relu_fwd', 3)
+        if _use_cluster(lib, M, Cc):
+            _lib.check(lib.mgw_bn_relu_fwd_cluster(x.data_ptr(), _ptr(residual), y.data_ptr(), M, Cc, _ptr(weight), _ptr(bias),
+                                                   _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
+                                                   float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
+                                                   _ptr(bits), s), 'bn_relu_fwd_cluster')
+            counters.bump('bn_relu_fwd_cluster', 1)
+        else:
+            partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
+            _lib.check(lib.mgw_bn_relu_fwd(x.data_ptr(), _ptr(residual), y.data_ptr(), M, Cc, _ptr(weight), _ptr(bias),
+                                           _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
+                                           float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
+                                           partials.data_ptr(), _ptr(bits), s), 'bn_relu_fwd')
+            counters.bump('bn_relu_fwd', 3)
         ctx.save_for_backward(x, y if (needs_mask and bits is None) else None, weight, bias, mean, invstd, bits)
         ctx.relu, ctx.has_residual, ctx.rows = bool(relu), residual is not None, (M, Cc)
         ctx.mark_non_differentiable(*[t for t in (running_mean, running_var, num_batches_tracked) if t is not None])
@@ -99,12 +123,18 @@ class _BNReLU(torch.autograd.Function):
         dx = torch.empty_like(x)
         dgamma = torch.empty(Cc, dtype=torch.float32, device=x.device)
         dbeta = torch.empty(Cc, dtype=torch.float32, device=x.device)
-        partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
         s = torch.cuda.current_stream().cuda_stream
-        _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
-                                       _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
-                                       dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), _ptr(bits), s), 'bn_relu_bwd')
-        counters.bump('bn_relu_bwd', 3)
+        if _use_cluster(lib, M, Cc):
+            _lib.check(lib.mgw_bn_relu_bwd_cluster(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
+                                                   _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
+                                                   dgamma.data_ptr(), dbeta.data_ptr(), _ptr(bits), s), 'bn_relu_bwd_cluster')
+            counters.bump('bn_relu_bwd_cluster', 1)
+        else:
+            partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
+            _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
+                                           _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
+                                           dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), _ptr(bits), s), 'bn_relu_bwd')
+            counters.bump('bn_relu_bwd', 3)
         need = ctx.needs_input_grad
         return (dx if need[0] else None, dgamma if (weight is not None and need[1]) else None,
                 dbeta if need[2] else None, None, None, None, dz if (ctx.has_residual and need[6]) else None,

@@ -1,5 +1,5 @@
-// BatchNorm(+add)+ReLU for SMALL activations (at most 16384 rows, channels a multiple of 16): one kernel per
-// direction instead of three.
+// BatchNorm(+add)+ReLU for SMALL activations (at most 8192 rows, channels a multiple of 16, one resident wave of
+// clusters): one kernel per direction instead of three.
 //
 // The three-launch kernels of bn_relu.cu are bandwidth-bound on large tensors, but on the 14x14 and 7x7 stages of a
 // ResNet / DenseNet each launch takes 4-5 us for 1-3 us worth of data, and the tensor is read twice.  Here a
@@ -26,6 +26,9 @@ constexpr int kThreads = 512;
 constexpr int kLanes = 4;                       // float4 lanes per row of a slab
 constexpr int kSlab = 16;                       // channels per cluster
 constexpr int kRowsPerPass = kThreads / kLanes; // 128
+// Largest number of rows a thread holds for which the dispatcher picks these kernels.  The R = 16 instantiations (a full
+// register file per CTA, 128 CTAs for 256 channels) were measured equal or slower inside a ResNet-50 step.
+constexpr int kMaxRowsPerThread = 8;
 
 struct Sums {
     float part[2][kSlab];       // this CTA's partial sums, read by the whole cluster
@@ -265,9 +268,14 @@ int rows_per_thread(long long M) {
 
 extern "C" {
 
-// 1 when the cluster kernels take an [M, C] problem (M <= 16384 rows, C a multiple of 16) on the current device.
+// 1 when the dispatcher should give an [M, C] problem to the cluster kernels on the current device: at most 8192 rows,
+// C a multiple of 16 and at most 288 (one CTA per SM holds all clusters).  Measured inside training steps on B200:
+// DenseNet-201's 128-channel layers (64 CTAs) gain 2-3 % of the step; 256 channels with 16 rows per thread (a full
+// register file per CTA) and 512 channels (256 CTAs, two per SM) were equal or slower than the three-launch kernels, and
+// 1024+ channels (several waves of clusters) clearly slower (51 MB: 88 us against 56 us).
 int mgw_bn_cluster_supported(long long M, int C) {
-    return (M > 0 && M <= 16LL * kRowsPerPass * kClusterSize && C > 0 && C % kSlab == 0 && clusters_fit()) ? 1 : 0;
+    if (!(M > 0 && M <= (long long)kMaxRowsPerThread * kRowsPerPass * kClusterSize && C > 0 && C % kSlab == 0)) return 0;
+    return ((C / kSlab) * kClusterSize <= 148 && clusters_fit()) ? 1 : 0;
 }
 
 int mgw_bn_relu_fwd_cluster(const float* x, const float* residual, float* y, long long M, int C, const float* gamma, const float* beta,

@@ -58,9 +58,9 @@ def _declare(lib) -> None:
     _declared = True
 
 
-# Small activations (at most 16384 rows, channels a multiple of 16) take the one-launch cluster kernels
-# (csrc/bn_relu_cluster.cu) when MGWFBP_BN_CLUSTER=1; otherwise everything stays on the three-launch kernels.
-_CLUSTER = os.environ.get('MGWFBP_BN_CLUSTER', '0').strip().lower() not in ('0', 'false', 'no', 'off', '')
+# Small activations (at most 8192 rows, at most 288 channels in multiples of 16) take the one-launch cluster kernels
+# (csrc/bn_relu_cluster.cu); MGWFBP_BN_CLUSTER=0 keeps everything on the three-launch kernels.
+_CLUSTER = os.environ.get('MGWFBP_BN_CLUSTER', '1').strip().lower() not in ('0', 'false', 'no', 'off', '')
 
 
 def _use_cluster(lib, M: int, Cc: int) -> bool:

@@ -26,8 +26,8 @@ constexpr int kThreads = 512;
 constexpr int kLanes = 4;                       // float4 lanes per row of a slab
 constexpr int kSlab = 16;                       // channels per cluster
 constexpr int kRowsPerPass = kThreads / kLanes; // 128
-// Largest number of rows a thread holds for which the dispatcher picks these kernels.  The R = 16 instantiations (a full
-// register file per CTA, 128 CTAs for 256 channels) were measured equal or slower inside a ResNet-50 step.
+// Largest number of rows a thread holds.  Sixteen rows (a full register file per CTA, 128 CTAs for 256 channels) were
+// measured equal or slower than the three-launch kernels inside a ResNet-50 step and are not built.
 constexpr int kMaxRowsPerThread = 8;
 
 struct Sums {
@@ -238,7 +238,7 @@ bn_bwd_cluster_kernel(const float* __restrict__ dy, const float* __restrict__ dy
     cluster.sync();
 }
 
-// Can the device place a cluster of the heaviest instantiations (R = 16: a full register file per CTA)?  Asked once.
+// Can the device place a cluster of the heaviest instantiations (most rows per thread)?  Asked once.
 bool clusters_fit() {
     static const bool ok = [] {
         cudaLaunchConfig_t cfg = {};
@@ -252,8 +252,8 @@ bool clusters_fit() {
         cfg.attrs = &attr;
         cfg.numAttrs = 1;
         int nf = 0, nb = 0;
-        if (cudaOccupancyMaxActiveClusters(&nf, bn_fwd_cluster_kernel<16>, &cfg) != cudaSuccess) { cudaGetLastError(); return false; }
-        if (cudaOccupancyMaxActiveClusters(&nb, bn_bwd_cluster_kernel<16>, &cfg) != cudaSuccess) { cudaGetLastError(); return false; }
+        if (cudaOccupancyMaxActiveClusters(&nf, bn_fwd_cluster_kernel<kMaxRowsPerThread>, &cfg) != cudaSuccess) { cudaGetLastError(); return false; }
+        if (cudaOccupancyMaxActiveClusters(&nb, bn_bwd_cluster_kernel<kMaxRowsPerThread>, &cfg) != cudaSuccess) { cudaGetLastError(); return false; }
         return nf >= 1 && nb >= 1;
     }();
     return ok;
@@ -291,8 +291,7 @@ int mgw_bn_relu_fwd_cluster(const float* x, const float* residual, float* y, lon
                                                      num_batches_tracked, momentum, eps, relu, save_mean, save_invstd, relu_bits)
     if (R <= 2) MGW_LAUNCH_FWD(2);
     else if (R <= 4) MGW_LAUNCH_FWD(4);
-    else if (R <= 8) MGW_LAUNCH_FWD(8);
-    else MGW_LAUNCH_FWD(16);
+    else MGW_LAUNCH_FWD(8);
 #undef MGW_LAUNCH_FWD
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
@@ -314,8 +313,7 @@ int mgw_bn_relu_bwd_cluster(const float* dy, const float* dy2, const float* y, c
                                                      save_invstd, mask_mode, dgamma, dbeta)
     if (R <= 2) MGW_LAUNCH_BWD(2);
     else if (R <= 4) MGW_LAUNCH_BWD(4);
-    else if (R <= 8) MGW_LAUNCH_BWD(8);
-    else MGW_LAUNCH_BWD(16);
+    else MGW_LAUNCH_BWD(8);
 #undef MGW_LAUNCH_BWD
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;

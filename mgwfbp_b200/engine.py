@@ -190,6 +190,14 @@ class TrainStep:
             self.losses.append(float(slot[0]))
             self._pending.pop(0)
 
+    def reset_state(self) -> None:
+        """Forget the recurrent state carried between steps (the reference starts every epoch of the PTB model from
+        ``init_hidden()``, ``dist_trainer.py:74-76``).  No effect for feed-forward models."""
+        self._hidden = None
+        if self._static_hidden is not None:
+            for h in self._static_hidden:
+                h.zero_()
+
     def drain(self) -> None:
         """Wait for every outstanding loss read."""
         self._collect(len(self._pending))

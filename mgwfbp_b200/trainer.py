@@ -634,7 +634,7 @@ class DLTrainer:
 
 
 def train_with_single(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, max_epochs, num_steps=1,
-                      max_iters: Optional[int] = None):
+                      max_iters: Optional[int] = None, use_graph: bool = True):
     """Single-GPU training loop (reference ``dl_trainer.py:956-984``): profiles the backward pass
     once, then trains, logging time per iteration and images/s."""
     from .parallel.optimizer import DistributedOptimizer
@@ -648,27 +648,41 @@ def train_with_single(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_u
     logger.info('Bencharmked backward time: %f', np.sum(layerwise_times))
     logger.info('Model size: %d', np.sum(layerwise_sizes))
     trainer.update_optimizer(DistributedOptimizer(trainer.optimizer, named_parameters=trainer.net.named_parameters()))
-    times, done = [], 0
+    # one micro-step per update: the graph-captured step with input prefetch; otherwise the accumulation loop
+    from .engine import TrainStep
+    step = TrainStep(trainer, use_graph=use_graph) if nsteps_update == 1 else None
+    upcoming = trainer.data_iter() if step is not None else None
     display = 40 if iters_per_epoch > 40 else max(iters_per_epoch - 1, 1)
+    done, counted, since = 0, 0, time.time()
     for epoch in range(max_epochs):
-        hidden = trainer.net.init_hidden() if dnn == 'lstm' else None
+        hidden = trainer.net.init_hidden() if (dnn == 'lstm' and step is None) else None
+        if step is not None:
+            step.reset_state()
         for i in range(iters_per_epoch):
-            s = time.time()
-            trainer.optimizer.zero_grad()
-            for j in range(nsteps_update):
-                if dnn == 'lstm':
-                    _, hidden = trainer.train(1, hidden=hidden)
-                else:
-                    trainer.train(1)
-            trainer.update_model()
-            times.append(time.time() - s)
+            if step is not None:
+                current, upcoming = upcoming, trainer.data_iter()
+                step.run(current, next_host_batch=upcoming)
+            else:
+                trainer.optimizer.zero_grad()
+                for j in range(nsteps_update):
+                    if dnn == 'lstm':
+                        _, hidden = trainer.train(1, hidden=hidden)
+                    else:
+                        trainer.train(1)
+                trainer.update_model()
             done += 1
+            counted += 1
             if i % display == 0 and i > 0:
                 if trainer.is_cuda:
-                    torch.cuda.synchronize()
-                t = float(np.mean(times))
+                    torch.cuda.synchronize()          # the host runs ahead of the device: close the interval first
+                now = time.time()
+                t = (now - since) / counted
                 logger.info('Time per iteration including communication: %f. Speed: %f images/s', t, batch_size * nsteps_update / t)
-                times = []
+                counted, since = 0, now
             if max_iters is not None and done >= max_iters:
+                if step is not None:
+                    step.drain()
                 return trainer
+    if step is not None:
+        step.drain()
     return trainer

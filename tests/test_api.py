@@ -226,6 +226,21 @@ def test_train_step_driver_on_cpu():
     assert t.get_train_iter() == 3
 
 
+def test_train_step_carries_and_resets_lstm_state():
+    """The PTB model's hidden state is carried from step to step and forgotten by ``reset_state`` (epoch start)."""
+    from mgwfbp_b200.engine import TrainStep
+    t = _trainer('lstm', 'ptb', batch_size=4)
+    t.update_optimizer(hvd.DistributedOptimizer(t.optimizer, named_parameters=t.net.named_parameters(), norm_clip=0.25))
+    step = TrainStep(t, use_graph=False)
+    step.run(t.data_iter())
+    assert step._hidden is not None and all(not h.requires_grad for h in step._hidden)
+    assert any(float(h.abs().sum()) > 0 for h in step._hidden)
+    step.reset_state()
+    assert step._hidden is None
+    step.run(t.data_iter())
+    assert step._hidden is not None and len(step.losses) == 2
+
+
 def test_extra_models_build():
     from mgwfbp_b200 import models
     for ctor in (models.preresnet20, models.resnet_mod20, models.resnext29_8_64, models.caffe_cifar, models.densenet100_12,

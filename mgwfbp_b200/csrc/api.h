@@ -12,7 +12,20 @@ extern "C" {
 const char* mgw_last_error(void);
 int mgw_version(void);
 
-// ---- symmetric heap (symm_heap.cu): one cudaMalloc region per rank, mapped into every peer --------
+void mgw_set_last_error_text(const char* text);
+
+// ---- symmetric heap (symm_heap.cu): one region per rank, mapped into every peer ---------------------
+// VMM flavour: cuMemCreate memory shared as POSIX file descriptors, optionally bound to an NVSwitch multicast object.
+int mgw_vmm_supported(int* out2);                                    // {vmm + fd handles, multicast}
+int mgw_vmm_create(size_t bytes, int world, int want_multicast, void** heap_out, void** base_out, size_t* bytes_out);
+int mgw_vmm_export_fd(void* heap, int* fd_out);
+int mgw_vmm_import_peer(void* heap, int peer, int fd, void** peer_base_out);
+int mgw_vmm_mc_create(void* heap, int world, int* fd_out);
+int mgw_vmm_mc_import(void* heap, int fd);
+int mgw_vmm_mc_add_device(void* heap);
+int mgw_vmm_mc_bind(void* heap, void** mc_base_out);
+int mgw_vmm_destroy(void* heap, int what);                           // what: 0 everything, 1 the multicast part only
+// IPC flavour: cudaMalloc + cudaIpc handles.
 int mgw_heap_create(size_t bytes, void** base_out);
 int mgw_heap_export(void* base, void* handle64_out);                 // 64-byte IPC handle
 int mgw_heap_open(const void* handle64, void** peer_base_out);      // enables peer access lazily

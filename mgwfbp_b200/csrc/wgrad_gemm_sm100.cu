@@ -142,7 +142,7 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, float (&v)[32]) {
 }
 
 __device__ __forceinline__ void report(int* status, int code) {
-    if (status) atomicCAS(status, 0, code);
+    if (status) atomicCAS_system(status, 0, code);      // the word may live in pinned host memory
 }
 
 __global__ void __launch_bounds__(kThreadsPerCta, 3)

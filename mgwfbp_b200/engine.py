@@ -30,8 +30,11 @@ from .settings import logger
 class TrainStep:
     WARMUP_EAGER_STEPS = 3
 
-    def __init__(self, trainer, use_graph: bool = True, loss_ring: int = 4):
+    def __init__(self, trainer, use_graph: bool = True, loss_ring: int = 4, track_accuracy: bool = False):
         self.trainer = trainer
+        self.track_accuracy = bool(track_accuracy)
+        self.eager_after_capture = 0     # steps that ran eagerly after the capture because their batch had another shape
+        self._replayed_last = False
         self.optimizer = trainer.optimizer
         self.cuda = trainer.is_cuda
         self.want_graph = bool(use_graph and self.cuda and trainer.dnn != 'lstman4' and settings.SHADOW_EVERY <= 0)
@@ -40,6 +43,8 @@ class TrainStep:
         self._graph: Optional[torch.cuda.CUDAGraph] = None
         self._static_batch: Optional[Tuple[torch.Tensor, ...]] = None
         self._static_loss: Optional[torch.Tensor] = None
+        self._static_outputs = None
+        self._static_labels = None
         self._eager_steps = 0
         self._launches_per_replay = {}
         self._hidden = None
@@ -61,18 +66,59 @@ class TrainStep:
             t._on_epoch_boundary()
         t.train_iter += 1
 
+    def _track(self, loss: torch.Tensor, outputs, labels) -> None:
+        """Epoch statistics on the device (no host read): the summed loss and, when asked for, the summed top-1
+        accuracy, which ``DLTrainer._on_epoch_boundary`` averages and logs (reference ``dl_trainer.py:752-771``)."""
+        t = self.trainer
+        ld = loss.detach()
+        if t._epoch_loss_t is None:
+            t._epoch_loss_t = ld.clone()
+        else:
+            t._epoch_loss_t.add_(ld)
+        if self.track_accuracy and outputs is not None and t.dnn not in ('lstm', 'lstman4'):
+            with torch.no_grad():
+                acc = (outputs.detach().argmax(1) == labels).float().mean().mul_(100.0)
+            if t._acc_sum_t is None:
+                t._acc_sum_t, t._acc_steps = acc.clone(), 1
+            else:
+                t._acc_sum_t.add_(acc)
+                t._acc_steps += 1
+
     def _eager(self, batch) -> torch.Tensor:
         t = self.trainer
         t.optimizer.zero_grad()
-        loss, outputs, labels, hidden = t.forward_loss(batch, self._hidden, on_device=True)
+        hidden_in = self._hidden
+        if t.dnn == 'lstm' and self._static_hidden is not None:
+            # after the capture the recurrent state lives in the static buffers; an eager step reads and refreshes them
+            hidden_in = tuple(h.clone() for h in self._static_hidden) if self._shapes_match_hidden(batch) else None
+        loss, outputs, labels, hidden = t.forward_loss(batch, hidden_in, on_device=True)
         if t.dnn == 'lstm':
             # keep only the values: a live reference into this step's autograd graph would keep its
             # gradient-accumulator nodes (and their stream) alive into the next step / a later capture
             from .models.lstm import repackage_hidden
             self._hidden = repackage_hidden(hidden)
+            if self._static_hidden is not None and self._shapes_match_hidden(batch):
+                for dst, src in zip(self._static_hidden, self._hidden):
+                    dst.copy_(src)
         t.backward(loss)
         t.optimizer.step()
+        self._track(loss, outputs, labels)
         return loss.detach()
+
+    def _shapes_match_hidden(self, batch) -> bool:
+        sb = self._static_batch
+        return sb is not None and torch.is_tensor(batch[0]) and batch[0].shape == sb[0].shape
+
+    def _same_shapes(self, batch) -> bool:
+        sb = self._static_batch
+        if sb is None or len(batch) != len(sb):
+            return False
+        for a, b in zip(sb, batch):
+            if torch.is_tensor(a) != torch.is_tensor(b):
+                return False
+            if torch.is_tensor(a) and (a.shape != b.shape or a.dtype != b.dtype):
+                return False
+        return True
 
     def _capture(self, batch) -> None:
         t = self.trainer
@@ -87,10 +133,12 @@ class TrainStep:
             self._static_hidden = tuple(h.detach().clone() for h in start)
             self._hidden = None
         with torch.cuda.graph(g):
-            loss, _o, _l, hid = t.forward_loss(self._static_batch, self._static_hidden, on_device=True)
+            loss, out, lab, hid = t.forward_loss(self._static_batch, self._static_hidden, on_device=True)
             t.backward(loss)
             t.optimizer.step()
             self._static_loss = loss.detach()
+            self._static_outputs = out.detach() if (self.track_accuracy and torch.is_tensor(out)) else None
+            self._static_labels = lab if torch.is_tensor(lab) else None
             if self._static_hidden is not None:
                 for dst, src in zip(self._static_hidden, hid):
                     dst.copy_(src.detach())
@@ -111,17 +159,28 @@ class TrainStep:
                 self.trainer.optimizer.zero_grad(set_to_none=True)
                 for tbl in _tables_of(self.trainer.optimizer):
                     tbl.invalidate()
-        if self.graphed:
+        if self.graphed and (batch is self._static_batch or self._same_shapes(batch)):
             if batch is not self._static_batch:
                 for dst, src in zip(self._static_batch, batch):
                     if torch.is_tensor(dst):
                         dst.copy_(src, non_blocking=True)
             sync = getattr(self.trainer.optimizer, 'sync_hyper', None)
             if sync is not None:
-                sync()
+                sync()                         # on the replaying stream: ordered after the previous replay, before this one
             self._graph.replay()
+            self._replayed_last = True
             counters.bump_many(self._launches_per_replay)
+            self._track(self._static_loss, self._static_outputs, self._static_labels)
             return self._static_loss
+        if self.graphed:
+            # A batch of another shape (the short last batch of an epoch): this one step runs eagerly.  The graph
+            # re-uploads its own gradient-pointer slots on every replay, so the tables only have to forget what
+            # they believe the device holds.
+            self.eager_after_capture += 1
+        if self._replayed_last:
+            for tbl in _tables_of(self.trainer.optimizer):
+                tbl.invalidate()
+            self._replayed_last = False
         self._eager_steps += 1
         return self._eager(batch)
 
@@ -179,7 +238,20 @@ class TrainStep:
             self.losses.append(float(loss))
         return self.losses[-1] if self.losses else None
 
+    def check_status(self) -> None:
+        """Raise :class:`CommTimeoutError` when a communication kernel of an earlier step gave up waiting for a peer
+        (the kernels record that in host-mapped memory; reading it costs no synchronisation, so this runs every step,
+        graph replay included), or when the weight-gradient GEMM reported a failed wait."""
+        comm = getattr(self.optimizer, '_comm', None)
+        check = getattr(comm, 'check_status', None)
+        if check is not None:
+            check()
+        from .ops import wgrad
+        wgrad.check_status_nosync()
+
     def _collect(self, force: int) -> None:
+        if self.cuda:
+            self.check_status()
         while self._pending:
             ev, slot = self._pending[0]
             if force > 0:
@@ -199,8 +271,10 @@ class TrainStep:
                 h.zero_()
 
     def drain(self) -> None:
-        """Wait for every outstanding loss read."""
+        """Wait for every outstanding loss read (and look at the kernels' status words once more afterwards)."""
         self._collect(len(self._pending))
+        if self.cuda:
+            self.check_status()
 
     def last_loss(self) -> Optional[float]:
         self.drain()
@@ -220,29 +294,195 @@ def _tables_of(optimizer):
     return out
 
 
-def fit_comm_model(comm=None, iters: int = 20) -> PiecewiseAlphaBeta:
+def fit_comm_model(comm=None, iters: int = 20, n_ctas: Optional[int] = None) -> PiecewiseAlphaBeta:
     """Measure the fused all-reduce kernels of this box and fit one alpha-beta line per algorithm.
 
     The sweep covers the reference's 32 KB - 2 MB grid (``profiling.py:158``) in coarser steps
-    and extends it to 64 MB so that the bandwidth term is resolved.  Rank 0's fit is broadcast;
+    and extends it to 64 MB so that the bandwidth term is resolved.  ``n_ctas`` caps the CTA count of
+    the large-message algorithm (pass ``comm.overlap_ctas`` for the model of a message that runs beside
+    backward; ``None`` for one that has the GPU to itself).  Rank 0's fit is broadcast;
     the returned piecewise model feeds ``DistributedOptimizer(cost_model=...)``."""
     from .parallel.comm.nvl import NvlComm
+    from .ops import _lib
     from .utils.profiling import CommunicationProfiler
     comm = comm or NvlComm.shared()
     one_max = comm.oneshot_max_bytes // 4
+    big = {v: k for k, v in _lib.ALGO_NAMES.items()}[comm.big_algo()]
     plans = {
         'oneshot': [n for n in (1024, 4096, 16384, 65536, 131072) if n <= one_max],
-        'nvls' if comm.nvls_available else 'twoshot': [1 << k for k in range(15, 25)],
+        big: [1 << k for k in range(15, 25)],
     }
     samples, ranges = {}, {}
     for algo, sizes in plans.items():
-        op = (lambda t, average=True, name=None, _a=algo: comm.allreduce_async_(t, average, name, algo=_a))
+        cap = n_ctas if algo != 'oneshot' else None
+
+        def op(t, average=True, name=None, _a=algo, _c=cap):
+            want = None if _c is None else min(_c, comm.choose((t.numel() + 3) // 4)[1])
+            return comm.allreduce_async_(t, average, name, algo=_a, n_ctas=want)
         prof = CommunicationProfiler(op, comm.synchronize, sizes, device=comm.device)
         samples[algo] = prof.benchmark(num_iters=iters)
         ranges[algo] = (0.0, float(comm.oneshot_max_bytes) + 1) if algo == 'oneshot' else (0.0, float('inf'))
     samples = runtime.broadcast_object(samples, 0)
     model = fit_piecewise(samples, ranges)
     for lo, hi, ab in model.pieces:
-        logger.info('comm model %-8s alpha = %.2f us, beta = %.3e s/B (%.0f GB/s algorithm bandwidth)',
-                    ab.name, ab.alpha * 1e6, ab.beta, 1e-9 / ab.beta if ab.beta > 0 else float('inf'))
+        logger.info('comm model %-8s%s alpha = %.2f us, beta = %.3e s/B (%.0f GB/s algorithm bandwidth)',
+                    ab.name, '' if n_ctas is None else ' (<= %d CTAs)' % n_ctas, ab.alpha * 1e6, ab.beta,
+                    1e-9 / ab.beta if ab.beta > 0 else float('inf'))
     return model
+
+
+def fit_interference(trainer, comm=None, n_ctas: Optional[int] = None, message_bytes: int = 8 << 20,
+                     reps: int = 4, cost_model=None) -> dict:
+    """How much does a communication kernel that runs beside backward slow backward down?
+
+    The MG-WFBP recurrences (reference ``distributed_optimizer.py:164-261``) assume the answer is "not at all".
+    On an NVSwitch box the kernel that moves a message shares SMs and memory bandwidth with the backward kernels, so
+    this measures it on the running box: forward + backward of ``trainer``'s model is timed alone and then beside a
+    side stream that runs all-reduce kernels of ``message_bytes`` with ``n_ctas`` CTAs back to back (the planned
+    algorithm and CTA count of overlapped groups).  With ``t0`` / ``t1`` the two times and ``c`` the time the side
+    stream was busy, ``rho = (t1 - t0) / min(c, t1)``: seconds of backward lost per second of overlapped
+    communication.  Rank 0's value (from max-over-ranks times) is broadcast.  Collective; takes a few hundred ms.
+    Returns ``{'rho', 't_alone_ms', 't_beside_ms', 'comm_busy_ms', 'n_ctas', 'messages'}``."""
+    from .ops import _lib
+    from .parallel.comm.nvl import NvlComm
+    comm = comm or NvlComm.shared()
+    if n_ctas is None:
+        n_ctas = comm.overlap_ctas
+    batch = trainer.to_device(trainer.data_iter())
+    net = trainer.net
+
+    def fwd_bwd():
+        for p in net.parameters():
+            p.grad = None
+        loss, _o, _l, _h = trainer.forward_loss(batch, None, on_device=True)
+        trainer.backward(loss)
+
+    def timed(fn) -> float:
+        torch.cuda.synchronize()
+        runtime.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return runtime.max_over_ranks(e0.elapsed_time(e1) / reps)
+
+    opt = trainer.optimizer
+    was_local = getattr(opt, 'local', None)
+    if was_local is not None:
+        opt.local = True                       # hooks of an already wrapped optimizer stay quiet
+    try:
+        for _ in range(2):
+            fwd_bwd()
+        run = fwd_bwd
+        graph = None
+        if trainer.dnn != 'lstman4':
+            try:                               # replay removes the launch gaps that would soak up the slow-down
+                for p in net.parameters():
+                    p.grad = None
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    loss, _o, _l, _h = trainer.forward_loss(batch, None, on_device=True)
+                    trainer.backward(loss)
+                run = graph.replay
+            except Exception as e:
+                logger.warning('interference fit: graph capture failed (%s); timing eager passes', e)
+                torch.cuda.synchronize()
+                graph, run = None, fwd_bwd
+        run()
+        t0 = timed(run)
+        buf = torch.zeros(message_bytes // 4, device=comm.device)
+        algo = {v: k for k, v in _lib.ALGO_NAMES.items()}[comm.big_algo()]
+        want = min(n_ctas, comm.choose(buf.numel() // 4)[1])
+        comm.synchronize(comm.allreduce_async_(buf, True, None, algo=algo, n_ctas=want))       # scratch + geometry settle here
+        per_msg = float(cost_model(message_bytes)) * 1e3 if cost_model is not None else 0.1
+        messages = int(runtime.broadcast_object(max(4, min(4000, int(1.5 * reps * t0 / max(per_msg, 1e-3)))), 0))
+        torch.cuda.synchronize()
+        runtime.barrier()
+        side = comm.stream
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record(side)
+        for _ in range(messages):
+            comm.allreduce_async_(buf, True, None, algo=algo, n_ctas=want)
+        s1.record(side)
+        e0.record()
+        for _ in range(reps):
+            run()
+        e1.record()
+        torch.cuda.synchronize()
+        comm.check_status()
+        t1 = runtime.max_over_ranks(e0.elapsed_time(e1) / reps)
+        busy = runtime.max_over_ranks(s0.elapsed_time(s1) / reps)
+        del graph
+    finally:
+        if was_local is not None:
+            opt.local = was_local
+        for p in net.parameters():
+            p.grad = None
+    overlap = max(min(busy, t1), 1e-6)
+    rho = min(max((t1 - t0) / overlap, 0.0), 1.0)
+    rho = float(runtime.broadcast_object(rho, 0))
+    out = {'rho': rho, 't_alone_ms': t0, 't_beside_ms': t1, 'comm_busy_ms': busy, 'n_ctas': int(want), 'messages': messages,
+           'message_bytes': int(message_bytes)}
+    logger.info('interference of a %d-CTA %s all-reduce beside forward+backward: rho = %.3f (%.3f ms alone, %.3f ms beside, '
+                'side stream busy %.3f ms per pass)', want, algo, rho, t0, t1, busy)
+    return out
+
+
+def tune_schedule(trainer, build_optimizer, interferences: Sequence[float], steps: int = 8, use_graph: bool = True):
+    """Pick the merge schedule by running it.
+
+    ``build_optimizer(rho)`` must return a ``DistributedOptimizer`` around the SAME base optimizer, scheduled with
+    interference ``rho`` (0 reproduces the reference's MG-WFBP schedule, 1 collapses to one message).  Every distinct
+    schedule that results is trained for a few steps through :class:`TrainStep` (eager warm-up, graph capture,
+    ``steps`` timed replays on one device-resident batch; device time, max over ranks), and the fastest is rebuilt
+    and installed with ``trainer.update_optimizer``.  Collective.  Returns ``(optimizer, report)`` where ``report``
+    lists ``{'rho', 'groups', 'ms_per_step'}`` per candidate.  These are real training steps on real batches."""
+    batch = trainer.to_device(trainer.data_iter()) if trainer.is_cuda else trainer.data_iter()
+    seen, report = {}, []
+    for rho in interferences:
+        opt = build_optimizer(rho)
+        digest = opt.merge_schedule.digest()
+        if digest in seen:
+            opt.close()
+            report.append({'rho': float(rho), 'groups': len(opt.merge_schedule.groups), 'ms_per_step': seen[digest], 'same_as_earlier': True})
+            continue
+        trainer.update_optimizer(opt)
+        step = TrainStep(trainer, use_graph=use_graph)
+        for _ in range(TrainStep.WARMUP_EAGER_STEPS + 2):
+            step.run_on_device(batch)
+        ms = _time_replays(step, batch, steps)
+        seen[digest] = ms
+        report.append({'rho': float(rho), 'groups': len(opt.merge_schedule.groups), 'ms_per_step': ms})
+        step.drain()
+        del step
+        opt.close()
+    best = min((r for r in report if not r.get('same_as_earlier')), key=lambda r: (r['ms_per_step'], r['groups']))
+    best_rho = runtime.broadcast_object(best['rho'], 0)
+    opt = build_optimizer(best_rho)
+    trainer.update_optimizer(opt)
+    if runtime.rank() == 0:
+        logger.info('schedule trial: %s -> rho %.3f (%d groups)', [(r['rho'], r['groups'], round(r['ms_per_step'], 3)) for r in report],
+                    best_rho, len(opt.merge_schedule.groups))
+    return opt, report
+
+
+def _time_replays(step: 'TrainStep', batch, steps: int) -> float:
+    if not step.cuda:
+        import time
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            step.run_on_device(batch)
+        return runtime.max_over_ranks((time.perf_counter() - t0) * 1e3 / steps)
+    torch.cuda.synchronize()
+    runtime.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step.run_on_device(batch)
+    e1.record()
+    torch.cuda.synchronize()
+    return runtime.max_over_ranks(e0.elapsed_time(e1) / steps)

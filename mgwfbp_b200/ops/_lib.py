@@ -59,6 +59,15 @@ def _declare(lib: C.CDLL) -> None:
     lib.mgw_heap_open.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
     lib.mgw_heap_close.argtypes = [C.c_void_p]
     lib.mgw_heap_destroy.argtypes = [C.c_void_p]
+    lib.mgw_vmm_supported.argtypes = [C.POINTER(C.c_int)]
+    lib.mgw_vmm_create.argtypes = [C.c_size_t, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_size_t)]
+    lib.mgw_vmm_export_fd.argtypes = [C.c_void_p, C.POINTER(C.c_int)]
+    lib.mgw_vmm_import_peer.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p)]
+    lib.mgw_vmm_mc_create.argtypes = [C.c_void_p, C.c_int, C.POINTER(C.c_int)]
+    lib.mgw_vmm_mc_import.argtypes = [C.c_void_p, C.c_int]
+    lib.mgw_vmm_mc_add_device.argtypes = [C.c_void_p]
+    lib.mgw_vmm_mc_bind.argtypes = [C.c_void_p, C.POINTER(C.c_void_p)]
+    lib.mgw_vmm_destroy.argtypes = [C.c_void_p, C.c_int]
     lib.mgw_host_status_alloc.argtypes = [C.c_int, C.POINTER(C.POINTER(C.c_int))]
     lib.mgw_host_status_free.argtypes = [C.POINTER(C.c_int)]
     lib.mgw_allreduce_group.argtypes = [C.POINTER(MgwAllreduceArgs), C.c_void_p]

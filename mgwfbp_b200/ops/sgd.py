@@ -31,6 +31,7 @@ class FastSGD:
         self.norm_clip = norm_clip
         momenta, created = ensure_momentum_buffers(optimizer, params)
         self.first_step = created
+        self.fallback_steps = 0          # steps that went through torch.optim.SGD.step instead of the kernel
         self.table = GroupTable(params, param_group_index(optimizer, params), momenta, self.device)
         self.hyper = HyperTable(self.device)
         self.n_ctas = max(1, min(self.MAX_CTAS, (self.table.n_vec + 2047) // 2048))
@@ -53,7 +54,10 @@ class FastSGD:
     def step(self, optimizer, grad_scale: float = 1.0):
         grads = [p.grad for p in self.params]
         if any(g is None for g in grads) or any(g.stride() != p.stride() for g, p in zip(grads, self.params)):
-            # a parameter without gradient, or an unusual gradient layout: use the stock update
+            # a parameter without gradient, or an unusual gradient layout: use the stock update (which also creates
+            # and fills the momentum buffers, so the next fast step must not treat them as fresh)
+            self.first_step = False
+            self.fallback_steps += 1
             return optimizer._base_cls.step(optimizer)
         self.table.refresh_grads(grads)
         if not torch.cuda.is_current_stream_capturing():

@@ -38,9 +38,11 @@ _status_cache = {}
 
 
 def _status(device) -> torch.Tensor:
+    """One status word per device in pinned host memory (device-visible under unified addressing): the kernels
+    record a failed bounded wait there and the host can look at it without synchronising."""
     t = _status_cache.get(device)
     if t is None:
-        t = _status_cache[device] = torch.zeros(1, dtype=torch.int32, device=device)
+        t = _status_cache[device] = torch.zeros(8, dtype=torch.int32).pin_memory()
     return t
 
 
@@ -52,14 +54,21 @@ def supported(dy: torch.Tensor, x: torch.Tensor) -> bool:
     return bool(_lib_ready().mgw_wgrad_gemm_supported(dy.data_ptr(), x.data_ptr(), dy.shape[1], x.shape[1], dy.shape[0]))
 
 
-def check_status(device=None) -> None:
-    """Raise if a GEMM CTA gave up on one of its bounded waits (synchronises the device)."""
+def check_status_nosync(device=None) -> None:
+    """Raise if a GEMM CTA of a launch that has already finished gave up on one of its bounded waits."""
     for dev, t in _status_cache.items():
         if device is None or dev == device:
-            code = int(t.item())
+            code = int(t[0])
             if code != 0:
                 t.zero_()
                 raise RuntimeError('wgrad_gemm kernel reported wait failure code %d' % code)
+
+
+def check_status(device=None) -> None:
+    """As :func:`check_status_nosync`, after waiting for every launch issued so far."""
+    if _status_cache:
+        torch.cuda.synchronize()
+    check_status_nosync(device)
 
 
 def wgrad_gemm(dy: torch.Tensor, x: torch.Tensor, scale: float = 1.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -4,19 +4,19 @@
 Replaces what Horovod's C++ core does for the reference (coordinator thread, name negotiation,
 tensor queue, NCCL launch; see ``distributed_optimizer.py:21-26,339,375``) with:
 
-* a **symmetric heap**: one device allocation per rank, mapped into every peer with CUDA IPC
-  (``csrc/symm_heap.cu``); handles are exchanged once over the gloo control plane;
-* **flag rows** inside the heap for CTA-to-CTA barriers between ranks (bounded waits);
+* a **symmetric arena** (``heap.py``, ``csrc/symm_heap.cu``): ``cuMemCreate`` memory per rank, mapped into
+  every peer and -- behind an NVSwitch -- bound to a multicast object; file descriptors are exchanged
+  once over Unix sockets, everything else over the gloo control plane.  Flag rows, staging areas,
+  gathered activation rows and scratch space are blocks of that one arena;
+* **flag rows** for CTA-to-CTA barriers between ranks (bounded waits);
 * one **kernel launch per merged group** on a high-priority side stream
-  (``csrc/allreduce_fused.cu``): pack through a pointer table, reduce over peer memory, average,
-  and -- for plain SGD -- update the weights in the same pass;
+  (``csrc/allreduce_fused.cu``): pack through a pointer table, reduce over peer memory (one-shot,
+  two-shot, or NVLS ``multimem.ld_reduce`` / ``multimem.st`` through the switch), average, and -- for
+  plain SGD -- update the weights in the same pass.  Groups whose kernel runs beside backward get a
+  small number of CTAs (``MGWFBP_OVERLAP_CTAS``); only the schedule's last group, which nothing can
+  hide, uses the whole GPU;
 * no negotiation: every rank launches groups in the order their gradients complete, which is the
   same on every rank because the schedule digest was compared at construction.
-
-Optional NVLS path: when ``MGWFBP_HEAP=torch`` the heap comes from
-``torch.distributed._symmetric_memory`` (allocation and rendezvous only), which also provides an
-NVSwitch multicast address; the ``nvls`` algorithm then reduces with ``multimem.ld_reduce`` /
-``multimem.st``.
 """
 from __future__ import annotations
 
@@ -33,6 +33,7 @@ from ...ops.tables import GroupTable, HyperTable, ensure_momentum_buffers, param
 from ...settings import logger
 from .. import runtime
 from .base import CommTimeoutError, Communicator
+from .heap import Block, SymmArena
 
 _ALIGN = 256
 
@@ -44,76 +45,6 @@ def _env_int(name: str, default: int) -> int:
         return default
 
 
-class IpcHeap:
-    """One symmetric region: same size and layout on every rank, all peers mapped locally."""
-
-    def __init__(self, lib, nbytes: int):
-        self.lib = lib
-        self.nbytes = int((nbytes + _ALIGN - 1) // _ALIGN * _ALIGN)
-        self.rank, self.world = runtime.rank(), runtime.size()
-        base = C.c_void_p()
-        _lib.check(lib.mgw_heap_create(self.nbytes, C.byref(base)), 'heap_create')
-        self.base = int(base.value)
-        handle = C.create_string_buffer(64)
-        _lib.check(lib.mgw_heap_export(self.base, handle), 'heap_export')
-        handles = runtime.allgather_object(bytes(handle.raw))
-        self.peer_base: List[int] = []
-        for r, h in enumerate(handles):
-            if r == self.rank:
-                self.peer_base.append(self.base)
-                continue
-            p = C.c_void_p()
-            _lib.check(lib.mgw_heap_open(C.create_string_buffer(h, 64), C.byref(p)), 'heap_open(rank %d)' % r)
-            self.peer_base.append(int(p.value))
-        self.mc_base = 0
-        self._top = 0
-        runtime.barrier()
-
-    def alloc(self, nbytes: int) -> int:
-        off = self._top
-        self._top = (off + int(nbytes) + _ALIGN - 1) // _ALIGN * _ALIGN
-        if self._top > self.nbytes:
-            raise MemoryError('symmetric heap exhausted')
-        return off
-
-    def close(self) -> None:
-        if self.base:
-            runtime.barrier()
-            for r, p in enumerate(self.peer_base):
-                if r != self.rank:
-                    self.lib.mgw_heap_close(p)
-            self.lib.mgw_heap_destroy(self.base)
-            self.base = 0
-
-
-class TorchSymmHeap:
-    """Same interface on top of ``torch.distributed._symmetric_memory`` (adds a multicast address)."""
-
-    def __init__(self, lib, nbytes: int):
-        import torch.distributed as dist
-        import torch.distributed._symmetric_memory as symm
-        self.lib = lib
-        self.nbytes = int((nbytes + _ALIGN - 1) // _ALIGN * _ALIGN)
-        self.rank, self.world = runtime.rank(), runtime.size()
-        dev = torch.device('cuda', torch.cuda.current_device())
-        self._tensor = symm.empty(self.nbytes, dtype=torch.uint8, device=dev)
-        self._handle = symm.rendezvous(self._tensor, dist.group.WORLD.group_name)
-        self._tensor.zero_()
-        torch.cuda.synchronize()
-        self.peer_base = [int(p) for p in self._handle.buffer_ptrs]
-        self.base = self.peer_base[self.rank]
-        self.mc_base = int(getattr(self._handle, 'multicast_ptr', 0) or 0)
-        self._top = 0
-        runtime.barrier()
-
-    alloc = IpcHeap.alloc
-
-    def close(self) -> None:
-        self._tensor = None
-        self._handle = None
-        self.base = 0
-
-
 def _wrap_device_memory(ptr: int, n_floats: int, device: torch.device) -> torch.Tensor:
     """A float32 tensor view of raw device memory that this module owns (symmetric heap)."""
     class _Mem:
@@ -123,15 +54,8 @@ def _wrap_device_memory(ptr: int, n_floats: int, device: torch.device) -> torch.
     return torch.as_tensor(holder, device=device)
 
 
-def make_heap(lib, nbytes: int):
-    kind = os.environ.get('MGWFBP_HEAP', 'ipc').lower()
-    if kind == 'torch':
-        return TorchSymmHeap(lib, nbytes)
-    return IpcHeap(lib, nbytes)
-
-
 class _GroupPlan:
-    __slots__ = ('table', 'params', 'algo', 'n_ctas', 'stage_off', 'args', 'partials_off', 'heap')
+    __slots__ = ('table', 'params', 'algo', 'n_ctas', 'stage_off', 'args', 'partials_off', 'block', 'overlapped')
 
 
 
@@ -151,6 +75,11 @@ class NvlComm(Communicator):
         self.oneshot_max_bytes = _env_int('MGWFBP_ONESHOT_MAX_BYTES', 512 * 1024)
         self.max_ctas_oneshot = min(_env_int('MGWFBP_ONESHOT_CTAS', 8), _lib.MAX_CTAS)
         self.max_ctas_twoshot = min(_env_int('MGWFBP_TWOSHOT_CTAS', 128), _lib.MAX_CTAS)
+        # groups whose kernel runs beside backward get few CTAs: what such a kernel costs is the SM time it holds
+        # (including the time its CTAs spin while a peer is late), not its latency
+        self.overlap_ctas = max(1, min(_env_int('MGWFBP_OVERLAP_CTAS', 16), _lib.MAX_CTAS))
+        # the switch-side reduction pays from this many ranks on (with two ranks a pull is as cheap as a multimem load)
+        self.nvls_min_world = _env_int('MGWFBP_NVLS_MIN_WORLD', 4)
         self.n_threads = _env_int('MGWFBP_COMM_THREADS', 512)
         # two-shot / NVLS kernels work through a CTA's chunk in pieces (pack, reduce and update of successive pieces
         # of different CTAs overlap); large messages use narrower CTAs, two of which fit on an SM
@@ -160,25 +89,38 @@ class NvlComm(Communicator):
         self.big_bytes = _env_int('MGWFBP_BIG_BYTES', 8 << 20)
         # control block: flag rows + per-CTA launch counters, in a heap of its own
         self._flag_bytes = int(self.lib.mgw_flag_block_bytes())
-        self._ctl = make_heap(self.lib, 2 * (self._flag_bytes + 4 * _lib.MAX_CTAS + _ALIGN))
-        self._flag_off = self._ctl.alloc(self._flag_bytes)
-        self._epoch_off = self._ctl.alloc(4 * _lib.MAX_CTAS)
-        self._gflag_off = self._ctl.alloc(self._flag_bytes)          # flag rows / counters of the row all-gather
-        self._gepoch_off = self._ctl.alloc(4 * _lib.MAX_CTAS)
+        self.arena = SymmArena(self.lib)
+        ctl_bytes = 2 * (self._flag_bytes + 4 * _lib.MAX_CTAS + 2 * _ALIGN)
+        self._ctl: Block = self.arena.alloc(ctl_bytes)               # first block of a fresh (zeroed) heap
+        top = [0]
+
+        def carve(n):
+            off = top[0]
+            top[0] = (off + n + _ALIGN - 1) // _ALIGN * _ALIGN
+            return off
+        self._flag_off = carve(self._flag_bytes)
+        self._epoch_off = carve(4 * _lib.MAX_CTAS)
+        self._gflag_off = carve(self._flag_bytes)          # flag rows / counters of the row all-gather
+        self._gepoch_off = carve(4 * _lib.MAX_CTAS)
+        assert top[0] <= ctl_bytes
         self._gather_tables = None
         status = C.POINTER(C.c_int)()
         _lib.check(self.lib.mgw_host_status_alloc(8, C.byref(status)), 'status_alloc')
         self._status = status
-        self._heaps: List[object] = []
-        self._scratch = None            # (heap, stage_off, capacity_vec) for allreduce_async_
+        self._blocks: Dict[int, List[Block]] = {}      # id(optimizer) -> blocks to give back on detach
+        self._scratch = None            # block + capacities for allreduce_async_
         self._scratch_tables: Dict[Tuple[int, int], GroupTable] = {}
         self._scratch_geometry = None
         self._done_event = torch.cuda.Event()
         self._plans: Dict[int, List[_GroupPlan]] = {}
         self._hyper: Dict[int, HyperTable] = {}
         self._keepalive: List[object] = []
-        self.nvls_available = bool(self._ctl.mc_base)
         self.launches = 0
+
+    @property
+    def nvls_available(self) -> bool:
+        """True when the symmetric heap is bound to an NVSwitch multicast object (``multimem`` instructions work)."""
+        return self.arena.has_multicast
 
     @classmethod
     def shared(cls) -> 'NvlComm':
@@ -194,9 +136,8 @@ class NvlComm(Communicator):
 
     def close(self) -> None:
         torch.cuda.synchronize()
-        for h in self._heaps + [self._ctl]:
-            h.close()
-        self._heaps = []
+        self.arena.close()
+        self._blocks, self._plans, self._hyper, self._scratch = {}, {}, {}, None
         if self._status:
             self.lib.mgw_host_status_free(self._status)
             self._status = None
@@ -222,8 +163,15 @@ class NvlComm(Communicator):
             self._status[i] = 0
 
     # ------------------------------------------------------------------ planning
-    def choose(self, n_vec: int) -> Tuple[int, int]:
-        """Algorithm and CTA count for a message of ``n_vec`` float4 slots (same answer on every rank)."""
+    def big_algo(self) -> int:
+        """The algorithm for messages beyond the one-shot range."""
+        if self.nvls_available and self._world >= self.nvls_min_world:
+            return _lib.ALGO_NVLS
+        return _lib.ALGO_TWOSHOT
+
+    def choose(self, n_vec: int, overlapped: bool = False) -> Tuple[int, int]:
+        """Algorithm and CTA count for a message of ``n_vec`` float4 slots (same answer on every rank).
+        ``overlapped``: the kernel will run beside backward, so it is given at most ``overlap_ctas`` CTAs."""
         nbytes = n_vec * 16
         forced = settings.COMM_ALGO.lower()
         if forced in _lib.ALGO_NAMES and not (forced == 'nvls' and not self.nvls_available):
@@ -231,14 +179,15 @@ class NvlComm(Communicator):
         elif nbytes <= self.oneshot_max_bytes:
             algo = _lib.ALGO_ONESHOT
         else:
-            algo = _lib.ALGO_NVLS if self.nvls_available else _lib.ALGO_TWOSHOT
+            algo = self.big_algo()
         # a CTA is worth launching for two (one-shot) / eight (two-shot) float4 slots per thread
         if algo == _lib.ALGO_ONESHOT:
             per_cta = 2 * self.n_threads
             n_ctas = max(1, min(self.max_ctas_oneshot, (n_vec + per_cta - 1) // per_cta))
         else:
             per_cta = 8 * self._threads_for(algo, n_vec)
-            n_ctas = max(1, min(self.max_ctas_twoshot, (n_vec + per_cta - 1) // per_cta))
+            cap = min(self.max_ctas_twoshot, self.overlap_ctas) if overlapped else self.max_ctas_twoshot
+            n_ctas = max(1, min(cap, (n_vec + per_cta - 1) // per_cta))
         return algo, n_ctas
 
     def _threads_for(self, algo: int, n_vec: int) -> int:
@@ -246,15 +195,15 @@ class NvlComm(Communicator):
             return self.big_threads
         return self.n_threads
 
-    def _fill_args(self, plan: _GroupPlan, heap, hyper_ptr: int, partials_ptr: int,
+    def _fill_args(self, plan: _GroupPlan, block: Block, hyper_ptr: int, partials_ptr: int,
                    inbox_stride: Optional[int] = None, stage_slots: Optional[int] = None) -> None:
         a = _lib.MgwAllreduceArgs()
         a.group = plan.table.struct
         for r in range(self._world):
-            a.stage[r] = heap.peer_base[r] + plan.stage_off
-            a.flags[r] = self._ctl.peer_base[r] + self._flag_off
+            a.stage[r] = block.peer(r) + plan.stage_off
+            a.flags[r] = self._ctl.peer(r) + self._flag_off
         a.epoch = self._ctl.base + self._epoch_off
-        a.mc_stage = (heap.mc_base + plan.stage_off) if heap.mc_base else None
+        a.mc_stage = (block.mc + plan.stage_off) if block.mc else None
         a.hyper = hyper_ptr or None
         a.sumsq_partials = partials_ptr or None
         a.status = C.cast(self._status, C.c_void_p).value
@@ -276,17 +225,18 @@ class NvlComm(Communicator):
         plans: List[_GroupPlan] = []
         total = 0
         sizes = []
-        for names in opt._groups:
+        n_groups = len(opt._groups)
+        for gi, names in enumerate(opt._groups):
             params = [named[n] for n in names]
             n_vec = sum((p.numel() + 3) // 4 for p in params)
-            algo, n_ctas = self.choose(n_vec)
+            # every group but the last one of the schedule is launched while backward still runs
+            algo, n_ctas = self.choose(n_vec, overlapped=gi < n_groups - 1)
             nbytes = int(self.lib.mgw_stage_bytes(algo, n_vec, self._world))
             sizes.append((algo, n_ctas, nbytes))
             total += (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
-        heap = make_heap(self.lib, total + _ALIGN)
-        self._heaps.append(heap)
-        if heap.mc_base:
-            self.nvls_available = True
+        block = self.arena.alloc(total + _ALIGN)
+        self._blocks.setdefault(key, []).append(block)
+        stage_top = 0
         hyper = HyperTable(self.device)
         self._hyper[key] = hyper
         n_partials = sum(s[1] for s in sizes)
@@ -306,10 +256,11 @@ class NvlComm(Communicator):
             plan.params = params
             plan.table = GroupTable(params, pgi, momenta, self.device)
             plan.algo, plan.n_ctas = algo, n_ctas
-            plan.stage_off = heap.alloc(nbytes)
+            plan.stage_off = stage_top
+            stage_top += (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
             plan.partials_off = p_off
-            plan.heap = heap
-            self._fill_args(plan, heap, hyper.data_ptr(), partials.data_ptr() + 4 * p_off)
+            plan.block = block
+            self._fill_args(plan, block, hyper.data_ptr(), partials.data_ptr() + 4 * p_off)
             p_off += n_ctas
             plans.append(plan)
         self._plans[key] = plans
@@ -322,7 +273,7 @@ class NvlComm(Communicator):
         mode = 0
         if opt._fused_update:
             mode |= _lib.MODE_UPDATE
-            if settings.WRITE_BACK_GRADS:
+            if settings.WRITE_BACK_GRADS:          # off by default: the update consumed the gradient, nobody reads it again
                 mode |= _lib.MODE_WRITEBACK
         else:
             mode |= _lib.MODE_WRITEBACK
@@ -337,6 +288,20 @@ class NvlComm(Communicator):
             algos[pl.algo] += 1
         logger.info('NvlComm: %d groups (%d one-shot, %d two-shot, %d nvls), %.1f MB staging, fused update: %s',
                     len(plans), algos[0], algos[1], algos[2], total / 1e6, opt._fused_update)
+
+    def detach(self, opt) -> None:
+        """Forget ``opt`` (collective): its staging blocks go back to the arena once no rank uses them any more."""
+        key = id(opt)
+        if key not in self._plans and key not in self._blocks:
+            return
+        torch.cuda.synchronize()
+        runtime.barrier()
+        for block in self._blocks.pop(key, []):
+            self.arena.free(block)
+        self._plans.pop(key, None)
+        self._hyper.pop(key, None)
+        for st in getattr(opt, '_ext_state', {}).values():
+            st['bufs'] = None
 
     # ------------------------------------------------------------------ hot path
     def launch_group(self, opt, gi: int) -> None:
@@ -410,7 +375,7 @@ class NvlComm(Communicator):
         for name, p, module in opt._external:
             mom, created = ensure_momentum_buffers(opt, [p])
             opt._ext_state[id(module)] = dict(name=name, param=p, mom=mom[0], pg=param_group_index(opt, [p])[0],
-                                              first=created, bufs=None)
+                                              first=created, bufs=None, opt_key=id(opt))
             module._exchange = (lambda m, dy, x, _o=opt: self.exchange_external(_o, m, dy, x))
 
     def _gather_buffers(self, st, rows: int, m: int, n: int):
@@ -421,15 +386,16 @@ class NvlComm(Communicator):
             raise RuntimeError('gathered weight-gradient buffers must exist before CUDA graph capture (run eager steps first)')
         w = self._world
         nbytes = 4 * w * rows * (m + n)
-        heap = make_heap(self.lib, nbytes + 2 * _ALIGN)
-        self._heaps.append(heap)
-        off_dy, off_x = heap.alloc(4 * w * rows * m), heap.alloc(4 * w * rows * n)
+        block = self.arena.alloc(nbytes + 2 * _ALIGN)
+        self._blocks.setdefault(st['opt_key'], []).append(block)
+        off_dy = 0
+        off_x = (4 * w * rows * m + _ALIGN - 1) // _ALIGN * _ALIGN
 
         def ptr_table(off):
-            return torch.tensor([heap.peer_base[r] + off for r in range(w)], dtype=torch.int64, device=self.device)
-        flags = torch.tensor([self._ctl.peer_base[r] + self._gflag_off for r in range(w)], dtype=torch.int64, device=self.device)
-        st['bufs'] = dict(rows=rows, heap=heap, off_dy=off_dy, off_x=off_x, tab_dy=ptr_table(off_dy), tab_x=ptr_table(off_x),
-                          flags=flags, dy_all=heap.base + off_dy, x_all=heap.base + off_x)
+            return torch.tensor([block.peer(r) + off for r in range(w)], dtype=torch.int64, device=self.device)
+        flags = torch.tensor([self._ctl.peer(r) + self._gflag_off for r in range(w)], dtype=torch.int64, device=self.device)
+        st['bufs'] = dict(rows=rows, block=block, off_dy=off_dy, off_x=off_x, tab_dy=ptr_table(off_dy), tab_x=ptr_table(off_x),
+                          flags=flags, dy_all=block.base + off_dy, x_all=block.base + off_x)
         return st['bufs']
 
     def exchange_external(self, opt, module, dy: torch.Tensor, x: torch.Tensor) -> None:
@@ -477,7 +443,10 @@ class NvlComm(Communicator):
 
     def sync_hyper(self, opt) -> None:
         """Upload ``opt``'s current learning rates etc. (call before replaying a captured step)."""
-        self._hyper[id(opt)].sync(opt.param_groups, self.stream)
+        # On the CURRENT stream, the one that replays the captured step: the upload is then ordered after every
+        # kernel of the previous replay (which still reads the table) and before every kernel of the next one.
+        # The side stream is idle between replays, so an upload there could land in the middle of a replay.
+        self._hyper[id(opt)].sync(opt.param_groups)
 
     # ------------------------------------------------------------------ generic tensor all-reduce
     def _ensure_scratch(self, n_vec: int) -> None:
@@ -491,11 +460,17 @@ class NvlComm(Communicator):
         os_cap = self.oneshot_max_bytes // 16 + 1
         os_bytes = int(self.lib.mgw_stage_bytes(_lib.ALGO_ONESHOT, os_cap, self._world))
         ts_bytes = int(self.lib.mgw_stage_bytes(_lib.ALGO_TWOSHOT, ts_cap, self._world))
-        heap = make_heap(self.lib, os_bytes + ts_bytes + 2 * _ALIGN)
-        self._heaps.append(heap)
-        if heap.mc_base:
-            self.nvls_available = True
-        self._scratch = dict(heap=heap, os_off=heap.alloc(os_bytes), os_cap=os_cap, ts_off=heap.alloc(ts_bytes), ts_cap=ts_cap)
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError('the all-reduce scratch area must exist before CUDA graph capture (call once eagerly first)')
+        if sc is not None:
+            # every rank grows at the same call: drain, meet, and give the old block back before taking a larger one
+            torch.cuda.synchronize()
+            runtime.barrier()
+            self.arena.free(sc['block'])
+            self._scratch_geometry = None
+        os_al = (os_bytes + _ALIGN - 1) // _ALIGN * _ALIGN
+        block = self.arena.alloc(os_al + ts_bytes + _ALIGN)
+        self._scratch = dict(block=block, os_off=0, os_cap=os_cap, ts_off=os_al, ts_cap=ts_cap)
 
     def allreduce_async_(self, tensor: torch.Tensor, average: bool = True, name: Optional[str] = None,
                          algo: Optional[str] = None, n_ctas: Optional[int] = None):
@@ -515,7 +490,7 @@ class NvlComm(Communicator):
             table = GroupTable([flat], [0], [None], self.device)
             self._scratch_tables[key] = table
         plan = _GroupPlan()
-        plan.table, plan.params, plan.heap = table, [flat], sc['heap']
+        plan.table, plan.params, plan.block = table, [flat], sc['block']
         plan.algo, plan.n_ctas = self.choose(n_vec)
         if algo is not None:
             plan.algo = _lib.ALGO_NAMES[algo]
@@ -534,7 +509,7 @@ class NvlComm(Communicator):
                 torch.cuda.synchronize()
                 runtime.barrier()
             self._scratch_geometry = geometry
-        self._fill_args(plan, sc['heap'], 0, 0, inbox_stride=sc['os_cap'], stage_slots=sc['ts_cap'])
+        self._fill_args(plan, sc['block'], 0, 0, inbox_stride=sc['os_cap'], stage_slots=sc['ts_cap'])
         compute = torch.cuda.current_stream()
         ready = torch.cuda.Event()
         ready.record(compute)

@@ -54,7 +54,11 @@ class _DistributedMixin:
 
     # ------------------------------------------------------------------ construction
     def _dist_init(self, base_optimizer, named_parameters, compression, seq_layernames, layerwise_times,
-                   norm_clip, threshold, writer, gradient_path, comm, cost_model, fused_update):
+                   norm_clip, threshold, writer, gradient_path, comm, cost_model, fused_update, interference=None,
+                   cost_model_last=None):
+        self._wrapped = base_optimizer
+        self._interference = interference
+        self._cost_model_last = cost_model_last
         self._compression = compression
         self._density = 1
         self._profiling = False
@@ -184,9 +188,12 @@ class _DistributedMixin:
             cost = self._resolve_cost_model()
             # kernels of the fused data plane compete with backward for SMs and bandwidth; other backends
             # (NCCL / gloo behind torch.distributed) are scheduled by the reference's recurrences unchanged
-            rho = settings.INTERFERENCE if self._fused_comm else 0.0
+            rho = 0.0
+            if self._fused_comm:
+                rho = settings.INTERFERENCE if self._interference is None else float(self._interference)
             if rho > 0.0:
-                sched = groups_mgwfbp_contended(names, sizes, self._layerwise_times, cost, rho, nbytes)
+                sched = groups_mgwfbp_contended(names, sizes, self._layerwise_times, cost, rho, nbytes,
+                                                cost_last=self._cost_model_last)
             else:
                 sched = groups_mgwfbp(names, sizes, self._layerwise_times, cost, nbytes)
             if runtime.rank() == 0:
@@ -262,6 +269,18 @@ class _DistributedMixin:
         for h in self._hook_handles:
             h.remove()
         self._hook_handles = []
+
+    def close(self) -> None:
+        """Retire this wrapper (collective when a fused communicator is attached): hooks are removed, staging memory
+        goes back to the communicator, and the optimizer state (momentum buffers created meanwhile) is handed to the
+        optimizer it was built from, so that a new wrapper around that optimizer continues where this one stopped."""
+        self.remove_hooks()
+        if self._active and self._fused_comm and hasattr(self._comm, 'detach'):
+            self._comm.detach(self)
+        wrapped = getattr(self, '_wrapped', None)
+        if wrapped is not None:
+            wrapped.state.update(self.state)
+        self._active = False
 
     def check_hooked_tensor_sequence(self, name: str) -> None:
         """With a profiled layer sequence, gradients must arrive last layer first
@@ -487,7 +506,8 @@ class _DistributedMixin:
 
 def DistributedOptimizer(optimizer, named_parameters=None, compression=None, density=0.001, seq_layernames=None,
                          layerwise_times=None, norm_clip=None, threshold=0, writer=None, gradient_path=None,
-                         comm: Optional[Communicator] = None, cost_model=None, fused_update: Optional[bool] = None):
+                         comm: Optional[Communicator] = None, cost_model=None, fused_update: Optional[bool] = None,
+                         interference: Optional[float] = None, cost_model_last=None):
     """Wrap ``optimizer`` so that gradients are averaged across workers before each update.
 
     Signature and merge policies follow reference ``distributed_optimizer.py:435-471``:
@@ -501,7 +521,10 @@ def DistributedOptimizer(optimizer, named_parameters=None, compression=None, den
 
     Extra keyword arguments select the data plane (``comm``), the all-reduce cost model
     (``cost_model``; default: measured alpha/beta if available, else the table for
-    ``settings.CONNECTION``) and whether the update is fused into the all-reduce kernels.
+    ``settings.CONNECTION``), whether the update is fused into the all-reduce kernels, and -- for the
+    fused NVLink data plane -- how much a second of communication kernel running beside backward slows
+    backward down (``interference``, see ``engine.fit_interference``; default ``settings.INTERFERENCE``)
+    and the cost model of the schedule's last message, which runs with the whole GPU (``cost_model_last``).
 
     Example of gradient clipping::
 
@@ -519,7 +542,7 @@ def DistributedOptimizer(optimizer, named_parameters=None, compression=None, den
     obj.defaults = dict(optimizer.defaults)
     obj.state.update(optimizer.state)
     obj._dist_init(optimizer, named_parameters, compression, seq_layernames, layerwise_times, norm_clip,
-                   threshold, writer, gradient_path, comm, cost_model, fused_update)
+                   threshold, writer, gradient_path, comm, cost_model, fused_update, interference, cost_model_last)
     if not obj._active and obj._base_is_sgd:
         first = next(iter(obj._named_parameters.values()), None)
         if first is not None and first.is_cuda:

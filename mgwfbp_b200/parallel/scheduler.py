@@ -211,12 +211,15 @@ def simulate_schedule(schedule: MergeSchedule, names: Sequence[str], sizes: Sequ
 # through the interference-aware timeline with the TRUE cost model, and the earliest finish wins.
 
 def simulate_contended(schedule: MergeSchedule, names: Sequence[str], sizes: Sequence[int], tb: Sequence[float],
-                       cost: Callable[[float], float], interference: float, bytes_per_elem: int = 4) -> Dict[str, float]:
+                       cost: Callable[[float], float], interference: float, bytes_per_elem: int = 4,
+                       cost_last: Optional[Callable[[float], float]] = None) -> Dict[str, float]:
     """Timeline of ``schedule`` when backward runs at rate ``1 - interference`` while a message is in flight.
 
     Messages are sent in group order, one at a time, each as soon as its last gradient exists and the
     previous message is done.  Returns the finish time of the iteration's backward + communication
     (``finish``), when backward itself ended (``backward_end``), the summed message time and the number of groups.
+    ``cost_last`` (optional) prices the schedule's last message, which is launched when backward is over and may
+    therefore use the whole GPU instead of the few CTAs an overlapped message gets.
     """
     rho = min(max(float(interference), 0.0), 1.0)
     names = list(names)
@@ -231,6 +234,8 @@ def simulate_contended(schedule: MergeSchedule, names: Sequence[str], sizes: Seq
     total_work = run
     need = [max(done_at[idx[n]] for n in g) for g in schedule.groups]
     tcs = [float(cost(n_el * bytes_per_elem)) for n_el in schedule.group_sizes]
+    if cost_last is not None and tcs:
+        tcs[-1] = float(cost_last(schedule.group_sizes[-1] * bytes_per_elem))
     t = w = 0.0
     qi, G = 0, len(need)
     backward_end = 0.0 if total_work <= 0.0 else None
@@ -261,8 +266,8 @@ def groups_mgwfbp_contended(names: Sequence[str], sizes: Sequence[int], tb: Sequ
                             cost: Callable[[float], float], interference: float, bytes_per_elem: int = 4,
                             startup: Optional[Callable[[float], float]] = None,
                             inflations: Sequence[float] = (1, 1.5, 2, 2.5, 3, 3.5, 4, 6, 8, 16, 32, 64, 256, 1024),
-                            buckets: Sequence[int] = (1 << 18, 1 << 19, 1 << 20, 1 << 21, 1 << 22, 1 << 23, 1 << 24, 1 << 25)
-                            ) -> MergeSchedule:
+                            buckets: Sequence[int] = (1 << 18, 1 << 19, 1 << 20, 1 << 21, 1 << 22, 1 << 23, 1 << 24, 1 << 25),
+                            cost_last: Optional[Callable[[float], float]] = None) -> MergeSchedule:
     """The MG-WFBP schedule that finishes first when overlapped communication slows backward down.
 
     ``interference`` = 0 returns exactly :func:`groups_mgwfbp`.  Otherwise the candidates described above are
@@ -291,7 +296,7 @@ def groups_mgwfbp_contended(names: Sequence[str], sizes: Sequence[int], tb: Sequ
         if sig in seen:
             continue
         seen[sig] = cand
-        sim = simulate_contended(cand, names, sizes, tb, cost, interference, bytes_per_elem)
+        sim = simulate_contended(cand, names, sizes, tb, cost, interference, bytes_per_elem, cost_last)
         table.append((float(k), len(cand.groups), sim['finish']))
         key = (sim['finish'], len(cand.groups))
         if best is None or key < best[0]:
@@ -303,7 +308,7 @@ def groups_mgwfbp_contended(names: Sequence[str], sizes: Sequence[int], tb: Sequ
         if sig in seen:
             continue
         seen[sig] = cand
-        sim = simulate_contended(cand, names, sizes, tb, cost, interference, bytes_per_elem)
+        sim = simulate_contended(cand, names, sizes, tb, cost, interference, bytes_per_elem, cost_last)
         table.append((-float(thr), len(cand.groups), sim['finish']))
         key = (sim['finish'], len(cand.groups))
         if key < best[0]:

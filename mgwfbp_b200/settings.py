@@ -73,8 +73,10 @@ CHANNELS_LAST = _env_flag('CHANNELS_LAST', True)
 # tensor-core weight-gradient GEMM with the SGD epilogue instead of all-reducing the weight gradient.
 GATHERED_WGRAD = _env_flag('GATHERED_WGRAD', True)
 
-# After the fused kernels ran, leave the averaged gradient readable in ``p.grad``.
-WRITE_BACK_GRADS = _env_flag('WRITE_BACK_GRADS', True)
+# After the fused all-reduce + update kernels ran, also store the averaged gradient back into ``p.grad``.  Off by
+# default: with the update fused nobody reads the gradient again and the store is one more pass over the model
+# (``optimizer.synchronize()`` + clipping paths do not fuse the update and always get the averaged gradient).
+WRITE_BACK_GRADS = _env_flag('WRITE_BACK_GRADS', False)
 
 # Every SHADOW_EVERY-th iteration the fused data plane is checked against a slow path: local gradients, parameters
 # and momenta are snapshotted before each group is launched, averaged over the CPU control plane and the update is

@@ -141,6 +141,7 @@ class DLTrainer:
         self.timer = self.forwardtime = self.backwardtime = self.iotime = 0.0
         self.epochs_info: List[float] = []
         self.train_acc_top1: List[Any] = []
+        self._acc_sum_t, self._acc_steps = None, 0
         self.num_of_updates_during_comm = 0
         self._loss_t: Optional[torch.Tensor] = None       # loss of the last train() call, on device
         self._epoch_loss_t: Optional[torch.Tensor] = None
@@ -543,13 +544,17 @@ class DLTrainer:
         self.train_epoch += 1
         npe = self.num_batches_per_epoch
         logger.info('train iter: %d, num_batches_per_epoch: %d', self.train_iter, npe)
-        acc = float(torch.stack([a.reshape(()) for a in self.train_acc_top1]).mean()) if self.train_acc_top1 else float('nan')
+        if self._acc_sum_t is not None:           # accumulated on the device by engine.TrainStep
+            acc = float(self._acc_sum_t) / max(self._acc_steps, 1)
+        else:
+            acc = float(torch.stack([a.reshape(()) for a in self.train_acc_top1]).mean()) if self.train_acc_top1 else float('nan')
         epoch_loss = float(self._epoch_loss_t) if self._epoch_loss_t is not None else self.avg_loss_per_epoch
         logger.info('Epoch %d, avg train acc: %f, lr: %f, avg loss: %f' % (self.train_iter // npe, acc, self.lr, epoch_loss / npe))
         if self.rank == 0 and self.writer is not None:
             self.writer.add_scalar('cross_entropy', epoch_loss / npe, self.train_epoch)
             self.writer.add_scalar('top-1_acc', acc, self.train_epoch)
         self.train_acc_top1 = []
+        self._acc_sum_t, self._acc_steps = None, 0
         self.epochs_info.append(epoch_loss / npe)
         self.avg_loss_per_epoch, self._epoch_loss_t = 0.0, None
         if self.train_iter > 0 and self.rank == 0:

@@ -20,7 +20,11 @@ def main():
     reqs = json.load(sys.stdin)
     ref = reqs[0]['reference_dir']
     state = {'world': reqs[0]['world']}
-    sys.path[:] = [ref] + [p for p in sys.path if p not in ('', ref) and 'repo' not in p.split('/')[-1:]]
+    # the reference is a flat directory of modules (settings, utils, profiling, ...): the repository under test has
+    # modules of the same names at its root, so its directory (passed in the request) must not be importable here
+    import os
+    repo = os.path.abspath(reqs[0].get('repo_root') or os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    sys.path[:] = [ref] + [p for p in sys.path if p not in ('', ref) and os.path.abspath(p) != repo]
     collections.Iterable = collections.abc.Iterable
     calls = []
     ops = types.ModuleType('horovod.torch.mpi_ops')

@@ -155,7 +155,9 @@ def _gathered_wgrad(rank, world):
     """A large linear layer fed by a small batch: its weight is updated from gathered activations by
     the tensor-core GEMM with the SGD epilogue and never enters the gradient all-reduce."""
     import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
     from mgwfbp_b200.ops.wgrad import convert_large_linears, GatheredWgradLinear
+    settings.WRITE_BACK_GRADS = True        # this test also looks at the gradient the GEMM formed
     torch.manual_seed(0)
     torch.backends.cuda.matmul.allow_tf32 = False
     mk_net = lambda: torch.nn.Sequential(torch.nn.Linear(64, 2048), torch.nn.ReLU(), torch.nn.Linear(2048, 4096),

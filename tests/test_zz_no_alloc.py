@@ -14,6 +14,14 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+def _loaded_path():
+    """The image that ``_lib.load()`` mapped (the index-checking build when ``MGWFBP_CHECKED=1``): opening the same
+    file again yields the same image, so the error text read through one handle belongs to the call made through the other."""
+    from mgwfbp_b200.ops import _lib
+    from mgwfbp_b200.ops.build import CHECKED_LIB_PATH, LIB_PATH
+    return CHECKED_LIB_PATH if _lib.is_checked() else LIB_PATH
+
+
 def _norm_both_ways(lib, clib, table, grads, n_ctas, max_norm):
     from mgwfbp_b200.ops import _lib
     dev = grads[0].device
@@ -33,10 +41,9 @@ def _norm_both_ways(lib, clib, table, grads, n_ctas, max_norm):
 
 def test_static_scratch_variant_matches_regular_entry_points():
     from mgwfbp_b200.ops import _lib
-    from mgwfbp_b200.ops.build import LIB_PATH
     from mgwfbp_b200.ops.tables import GroupTable
     lib = _lib.load(allow_build=False)
-    clib = C.CDLL(LIB_PATH)                               # the plain exported symbol, no Python wrapper in between
+    clib = C.CDLL(_loaded_path())                         # the plain exported symbol, no Python wrapper in between
     clib.mgw_grad_clip_coef_static.restype = C.c_int
     dev = torch.device('cuda')
     torch.manual_seed(0)
@@ -55,10 +62,9 @@ def test_static_scratch_variant_matches_regular_entry_points():
 
 def test_static_scratch_variant_rejects_oversized_requests():
     from mgwfbp_b200.ops import _lib
-    from mgwfbp_b200.ops.build import LIB_PATH
     from mgwfbp_b200.ops.tables import GroupTable
     lib = _lib.load(allow_build=False)
-    clib = C.CDLL(LIB_PATH)
+    clib = C.CDLL(_loaded_path())
     clib.mgw_grad_clip_coef_static.restype = C.c_int
     dev = torch.device('cuda')
     x = torch.ones(64, device=dev)

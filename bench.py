@@ -96,6 +96,21 @@ def _dist_env(args):
     return int(os.environ.get('RANK', '0')), int(os.environ.get('LOCAL_RANK', '0')), world
 
 
+def _config(args, world, bs, dataset, groups, graphed, comm):
+    """The ``config`` object of the JSON line; both arms print the same keys."""
+    return {'model': args.dnn, 'global_batch': world * bs, 'per_gpu_batch': bs,
+            'seq_len': 35 if args.dnn == 'lstm' else None, 'parallelism': 'dp%d' % world,
+            'policy': args.policy + ('(%d)' % args.threshold if args.policy == 'bucket' else ''), 'cuda_graph': bool(graphed),
+            'optimizer': 'sgd momentum 0.9 wd 1e-4' if dataset != 'ptb' else 'sgd lr 22 clip 0.25',
+            'groups': groups, 'comm': comm,
+            'matmul': 'fp32' if args.fp32_matmul else 'tf32',
+            'l2': 'per-step working set (activations + weights, > 1 GB) exceeds the 126 MB L2; no explicit flush'}
+
+
+def _dtype(args):
+    return 'tf32 convolutions, %s matmul (fp32 storage)' % ('fp32' if args.fp32_matmul else 'tf32')
+
+
 def _time_steps(torch, dist_ok, step_fn, steps, barrier):
     """Time exactly `steps` calls of step_fn on the device; returns ms per step (this rank)."""
     barrier()
@@ -118,7 +133,7 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     torch.backends.cudnn.benchmark = True
     torch.backends.cudnn.allow_tf32 = True
-    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.backends.cuda.matmul.allow_tf32 = not args.fp32_matmul          # the same setting in both arms
     sys.path.insert(0, ROOT)
     import mgwfbp_b200 as hvd
     from mgwfbp_b200 import settings
@@ -131,6 +146,7 @@ def run_ours(args):
     hvd.init()
     settings.logger.setLevel('WARNING')
     settings.ADAPTIVE_MERGE = args.policy == 'mgwfbp'
+    settings.ORIGINAL_HOROVOD = args.policy == 'nccl'        # the in-repo stock arm: NCCL buckets + torch's SGD.step
     trainer = DLTrainer(rank, world, dist=False, batch_size=bs, ngpus=1, data_dir='synthetic', dataset=dataset,
                         dnn=args.dnn, lr=lr, nworkers=world, prefix='allreduce', seed=0,
                         momentum=0.9 if dataset != 'ptb' else None, weight_decay=1e-4 if dataset != 'ptb' else None)
@@ -139,18 +155,18 @@ def run_ours(args):
     if world > 1 and args.policy == 'mgwfbp':
         seq, times, _sizes = profile_backward(trainer, warmup=3, iteration=10)
         times = hvd.broadcast_object(list(times), 0)
-    threshold = {'mgwfbp': 0, 'wfbp': 0, 'single': 524288000, 'bucket': args.threshold}[args.policy]
+    threshold = {'mgwfbp': 0, 'wfbp': 0, 'single': 524288000, 'bucket': args.threshold, 'nccl': 0}[args.policy]
     norm_clip = 0.25 if args.dnn == 'lstm' else None
-    cost_model = None
-    if world > 1 and args.policy == 'mgwfbp' and not args.no_comm_fit:
-        # alpha/beta of the fused kernels measured on this box feed the merge scheduler
-        from mgwfbp_b200.engine import fit_comm_model
-        cost_model = fit_comm_model()
-    optimizer = hvd.DistributedOptimizer(trainer.optimizer, named_parameters=trainer.net.named_parameters(),
-                                         seq_layernames=seq, layerwise_times=times, threshold=threshold,
-                                         norm_clip=norm_clip, cost_model=cost_model)
-    hvd.broadcast_parameters(trainer.net.state_dict(), root_rank=0)
-    trainer.update_optimizer(optimizer)
+    # start-up self-check of the communication kernels (outside every timed region)
+    selfcheck = None
+    if world > 1 and args.policy != 'nccl' and not args.no_selfcheck:
+        from mgwfbp_b200.parallel.comm.selfcheck import selfcheck as run_selfcheck
+        selfcheck = run_selfcheck()
+    # cost model + interference measured on this box, schedule confirmed by timing it (engine.build_distributed_optimizer)
+    from mgwfbp_b200.engine import build_distributed_optimizer
+    optimizer, tuning = build_distributed_optimizer(trainer, seq_layernames=seq, layerwise_times=times, threshold=threshold,
+                                                    norm_clip=norm_clip, tune=not args.no_tune, fit_comm=not args.no_comm_fit,
+                                                    use_graph=not args.no_graph)
 
     from mgwfbp_b200.engine import TrainStep
     step = TrainStep(trainer, use_graph=not args.no_graph)
@@ -237,6 +253,16 @@ def run_ours(args):
             exposed = hvd.parallel.runtime.max_over_ranks(sum(vals) / len(vals))
             comm_ms = hvd.parallel.runtime.max_over_ranks(sum(totals) / len(totals))
 
+    comm = getattr(optimizer, '_comm', None)
+    if world == 1:
+        comm_name = 'none (one GPU)'
+    elif getattr(comm, 'fused', False):
+        algos = sorted({p.algo for p in comm._plans.get(id(optimizer), [])})
+        comm_name = 'own NVLink kernels (%s; %s heap%s)' % (
+            '+'.join({0: 'one-shot', 1: 'two-shot', 2: 'NVLS multimem'}[a] for a in algos), comm.arena.heaps[0].kind,
+            ', NVSwitch multicast' if comm.nvls_available else '')
+    else:
+        comm_name = 'NCCL via torch.distributed (stock arm)'
     if rank == 0:
         value = world * bs * per_sample / (ms_dev * 1e-3)
         e2e = world * bs * per_sample / (ms_e2e * 1e-3)
@@ -244,18 +270,16 @@ def run_ours(args):
         out = {
             'metric': '%s training throughput (%s, aggregate over all GPUs)' % (args.dnn, unit), 'value': value, 'unit': unit,
             'n_gpus': world, 'steps': args.steps, 'warmup': max(args.warmup, 3), 'ms_per_step': ms_dev,
-            'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': 'tf32 (fp32 storage)',
+            'higher_is_better': True, 'scaling': 'weak', 'vs_baseline': None, 'dtype': _dtype(args),
             'data': 'synthetic', 'impl': 'ours',
-            'config': {'model': args.dnn, 'global_batch': world * bs, 'per_gpu_batch': bs,
-                       'seq_len': 35 if args.dnn == 'lstm' else None, 'parallelism': 'dp%d' % world,
-                       'policy': args.policy + ('(%d)' % args.threshold if args.policy == 'bucket' else ''), 'cuda_graph': step.graphed,
-                       'optimizer': 'sgd momentum 0.9 wd 1e-4' if dataset != 'ptb' else 'sgd lr 22 clip 0.25',
-                       'groups': len(optimizer.merge_schedule.groups),
-                       'l2': 'per-step working set (activations + weights, > 1 GB) exceeds the 126 MB L2; no explicit flush'},
+            'config': _config(args, world, bs, dataset, len(optimizer.merge_schedule.groups), step.graphed, comm_name),
             'clocks': clocks,
             'e2e': {'value': e2e, 'unit': unit, 'ms_per_step': ms_e2e, 'h2d_bytes_per_step': h2d, 'd2h_bytes_per_step': 4},
             'gpu_launches': launches, 'final_loss': final_loss,
             'exposed_comm_ms': exposed, 'comm_kernel_ms': comm_ms,
+            'selfcheck': selfcheck, 'schedule_tuning': tuning,
+            'sgd_stock_fallback_steps': getattr(getattr(optimizer, '_fast_sgd', None), 'fallback_steps', 0),
+            'eager_steps_after_capture': step.eager_after_capture,
         }
         print(json.dumps(out))
     hvd.shutdown()
@@ -279,6 +303,8 @@ def run_reference(args):
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device')
     torch.cuda.set_device(local_rank)
+    torch.backends.cudnn.allow_tf32 = True                                   # torch's default, stated
+    torch.backends.cuda.matmul.allow_tf32 = not args.fp32_matmul             # the same setting in both arms
     import logging
     import numpy as np
     import settings
@@ -339,7 +365,7 @@ def run_reference(args):
         box = [list(times)]
         torch.distributed.broadcast_object_list(box, src=0)
         times = box[0]
-    threshold = {'mgwfbp': 0, 'wfbp': 0, 'single': 524288000, 'bucket': args.threshold}[args.policy]
+    threshold = {'mgwfbp': 0, 'wfbp': 0, 'single': 524288000, 'bucket': args.threshold, 'nccl': 0}[args.policy]
     from compression import compressors
     optimizer = hvd.DistributedOptimizer(trainer.optimizer, named_parameters=trainer.net.named_parameters(),
                                          compression=compressors[None], seq_layernames=seq, layerwise_times=times,
@@ -385,10 +411,9 @@ def run_reference(args):
             'metric': '%s training throughput (%s, aggregate over all GPUs)' % (args.dnn, unit),
             'value': world * bs * per_sample / (ms_dev * 1e-3), 'unit': unit, 'n_gpus': world, 'steps': args.steps,
             'warmup': max(args.warmup, 3), 'ms_per_step': ms_dev, 'higher_is_better': True, 'scaling': 'weak',
-            'vs_baseline': None, 'dtype': 'tf32 convolutions (fp32 storage, torch defaults)', 'data': 'synthetic',
-            'config': {'model': args.dnn, 'global_batch': world * bs, 'per_gpu_batch': bs, 'parallelism': 'dp%d' % world,
-                       'policy': args.policy, 'comm': 'NCCL via torch.distributed behind a horovod.torch.mpi_ops shim',
-                       'groups': len(optimizer._groups)},
+            'vs_baseline': None, 'dtype': _dtype(args), 'data': 'synthetic',
+            'config': _config(args, world, bs, dataset, len(optimizer._groups), False,
+                              'none (one GPU)' if world == 1 else 'NCCL via torch.distributed behind a horovod.torch.mpi_ops shim'),
             'clocks': clocks,
             'e2e': {'value': world * bs * per_sample / (ms_e2e * 1e-3), 'unit': unit, 'ms_per_step': ms_e2e,
                     'h2d_bytes_per_step': sum(t.numel() * t.element_size() for t in ring[0]), 'd2h_bytes_per_step': 4},
@@ -407,8 +432,12 @@ def main():
     ap.add_argument('--impl', choices=['ours', 'reference'], default='ours')
     ap.add_argument('--dnn', choices=sorted(WORKLOADS), default='resnet50')
     ap.add_argument('--batch-size', type=int, default=None, help='per-GPU batch (default: the workload\'s)')
-    ap.add_argument('--policy', choices=['mgwfbp', 'wfbp', 'single', 'bucket'], default='mgwfbp',
-                    help="merge policy: MG-WFBP schedule, one message per tensor, one message in all, or fixed-size buckets")
+    ap.add_argument('--policy', choices=['mgwfbp', 'wfbp', 'single', 'bucket', 'nccl'], default='mgwfbp',
+                    help="merge policy: MG-WFBP schedule, one message per tensor, one message in all, fixed-size buckets, or "
+                         "the stock arm (NCCL through torch.distributed in 64 MB fusion buckets + torch's SGD.step)")
+    ap.add_argument('--fp32-matmul', action='store_true', help='full-precision cuBLAS matmuls in both arms (default: TF32 in both)')
+    ap.add_argument('--no-tune', action='store_true', help='do not time candidate schedules; trust the interference model')
+    ap.add_argument('--no-selfcheck', action='store_true', help='skip the start-up self-check of the communication kernels')
     ap.add_argument('--threshold', type=int, default=8 * 1024 * 1024, help="bucket size in elements for --policy bucket")
     ap.add_argument('--no-graph', action='store_true', help='do not capture the training step in a CUDA graph')
     ap.add_argument('--timeline', default=None, metavar='PREFIX',

@@ -37,7 +37,12 @@ class TrainStep:
         self._replayed_last = False
         self.optimizer = trainer.optimizer
         self.cuda = trainer.is_cuda
-        self.want_graph = bool(use_graph and self.cuda and trainer.dnn != 'lstman4' and settings.SHADOW_EVERY <= 0)
+        comm = getattr(self.optimizer, '_comm', None)
+        library_comm = comm is not None and comm.size() > 1 and not getattr(comm, 'fused', False)
+        # not captured: CTC models (host-side label handling), the shadow checker (host round trips) and the stock arm
+        # (torch.distributed work handles)
+        self.want_graph = bool(use_graph and self.cuda and trainer.dnn != 'lstman4' and settings.SHADOW_EVERY <= 0
+                               and not library_comm)
         self._static_hidden = None
         self.graphed = False
         self._graph: Optional[torch.cuda.CUDAGraph] = None
@@ -486,3 +491,63 @@ def _time_replays(step: 'TrainStep', batch, steps: int) -> float:
     e1.record()
     torch.cuda.synchronize()
     return runtime.max_over_ranks(e0.elapsed_time(e1) / steps)
+
+
+def build_distributed_optimizer(trainer, seq_layernames=None, layerwise_times=None, threshold: int = 0, norm_clip=None,
+                                compression=None, writer=None, gradient_path=None, tune: bool = True,
+                                fit_comm: bool = True, trial_steps: int = 8, use_graph: bool = True):
+    """What the entry points do between profiling backward and the first training step (reference
+    ``dist_trainer.py:55-66``: build the wrapped optimizer, broadcast the parameters), plus the measurements the merge
+    scheduler needs on an NVSwitch box.
+
+    With the fused NVLink data plane and the adaptive policy this (1) fits the all-reduce cost model of this box for a
+    message that has the GPU to itself and for one that runs beside backward with ``comm.overlap_ctas`` CTAs
+    (:func:`fit_comm_model`), (2) measures how much such a message slows backward down (:func:`fit_interference`),
+    (3) builds the interference-aware MG-WFBP schedule for that value and a few neighbours and keeps the one that
+    trains fastest (:func:`tune_schedule`).  In every other configuration it just wraps the optimizer.  Parameters are
+    broadcast from rank 0 before the first step either way.  Returns ``(optimizer, info)``; ``info`` holds what was
+    measured (``None`` entries where nothing was)."""
+    from .parallel.broadcast import broadcast_parameters
+    from .parallel.optimizer import DistributedOptimizer
+    base = trainer.optimizer
+    named = list(trainer.net.named_parameters())
+    info = {'interference': None, 'trial': None, 'cost_model': None, 'cost_model_overlapped': None}
+
+    def build(rho=None, cost=None, cost_last=None):
+        return DistributedOptimizer(base, named_parameters=named, compression=compression, seq_layernames=seq_layernames,
+                                    layerwise_times=layerwise_times, norm_clip=norm_clip, threshold=threshold, writer=writer,
+                                    gradient_path=gradient_path, cost_model=cost, cost_model_last=cost_last, interference=rho)
+
+    adaptive_fused = (runtime.size() > 1 and trainer.is_cuda and not settings.ORIGINAL_HOROVOD and settings.ADAPTIVE_MERGE
+                      and layerwise_times is not None)
+    if not adaptive_fused:
+        opt = build()
+        broadcast_parameters(trainer.net.state_dict(), root_rank=0)
+        trainer.update_optimizer(opt)
+        return opt, info
+    from .parallel.comm.nvl import NvlComm
+    comm = NvlComm.shared()
+    cost_full = cost_ovl = None
+    if fit_comm:
+        cost_full = fit_comm_model(comm)
+        cost_ovl = fit_comm_model(comm, n_ctas=comm.overlap_ctas)
+        info['cost_model'] = [(ab.name, ab.alpha, ab.beta) for _lo, _hi, ab in cost_full.pieces]
+        info['cost_model_overlapped'] = [(ab.name, ab.alpha, ab.beta) for _lo, _hi, ab in cost_ovl.pieces]
+    broadcast_parameters(trainer.net.state_dict(), root_rank=0)
+    if settings.INTERFERENCE_PINNED:
+        rhos = [settings.INTERFERENCE]
+    else:
+        info['interference'] = fit_interference(trainer, comm, cost_model=cost_ovl)
+        rho = info['interference']['rho']
+        rhos = []
+        for r in (rho, 0.5 * rho, min(1.0, 2.0 * rho), min(1.0, 4.0 * rho), 1.0):
+            r = round(max(r, 1e-3), 4)
+            if r not in rhos:
+                rhos.append(r)
+    mk = lambda r: build(r, cost_ovl, cost_full)      # noqa: E731
+    if tune and len(rhos) > 1:
+        opt, info['trial'] = tune_schedule(trainer, mk, rhos, steps=trial_steps, use_graph=use_graph)
+    else:
+        opt = mk(rhos[0])
+        trainer.update_optimizer(opt)
+    return opt, info

@@ -11,7 +11,7 @@ import ctypes as C
 import os
 from typing import Optional
 
-from .build import CHECKED_LIB_PATH, LIB_PATH, build
+from .build import CHECKED_LIB_PATH, LIB_PATH, build  # noqa: F401  (re-exported)
 
 MAX_RANKS = 16
 MAX_CTAS = 296

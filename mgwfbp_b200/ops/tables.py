@@ -73,10 +73,11 @@ class GroupTable:
         self.tensors = _to_device_bytes(table, device)
         self.grad_ptrs = torch.zeros(max(n, 1), dtype=torch.int64, device=device)
         self._grad_ptr_cache: Optional[List[int]] = None
-        # two pinned staging slots, allocated once: no host allocation on the hot path, and a
-        # captured CUDA graph can keep reading the slot it was captured with
-        self._pinned = [_pinned_empty(max(n, 1), torch.int64) for _ in range(2)]
-        self._pinned_events: List[Optional[torch.cuda.Event]] = [None, None]
+        # pinned staging slots, allocated once (no host allocation on the hot path): eager refreshes alternate
+        # between slots 0 and 1; slot 2 belongs to CUDA graph capture -- a captured upload re-reads its slot on every
+        # replay, so eager steps that run between replays must never write there
+        self._pinned = [_pinned_empty(max(n, 1), torch.int64) for _ in range(3)]
+        self._pinned_events: List[Optional[torch.cuda.Event]] = [None, None, None]
         self._slot = 0
         self._struct = _lib.MgwGroup(self.tensors.data_ptr(), self.grad_ptrs.data_ptr(), self.voff.data_ptr(), n, self.n_vec)
 
@@ -89,19 +90,24 @@ class GroupTable:
         ptrs = [g.data_ptr() for g in grads]
         if ptrs == self._grad_ptr_cache:
             return False
-        self._slot ^= 1
-        ev = self._pinned_events[self._slot]
-        if ev is not None and not torch.cuda.is_current_stream_capturing():
-            ev.synchronize()                       # the previous copy out of this slot has finished
-        host = self._pinned[self._slot]
+        capturing = torch.cuda.is_current_stream_capturing()
+        if capturing:
+            slot = 2
+        else:
+            self._slot ^= 1
+            slot = self._slot
+            ev = self._pinned_events[slot]
+            if ev is not None:
+                ev.synchronize()                   # the previous copy out of this slot has finished
+        host = self._pinned[slot]
         host[:len(ptrs)] = torch.tensor(ptrs, dtype=torch.int64)
         with torch.cuda.stream(stream) if stream is not None else _nullcontext():
             self.grad_ptrs[:len(ptrs)].copy_(host[:len(ptrs)], non_blocking=True)
             ev = None
-            if not torch.cuda.is_current_stream_capturing():
+            if not capturing:
                 ev = torch.cuda.Event()
                 ev.record()
-        self._pinned_events[self._slot] = ev
+        self._pinned_events[slot] = ev
         self._grad_ptr_cache = ptrs
         return True
 

@@ -88,7 +88,8 @@ def make_communicator(device: Optional[torch.device] = None, prefer_fused: bool 
     """Pick the data plane for tensors living on ``device``."""
     if runtime.size() == 1:
         return LocalComm()
-    if device is not None and torch.device(device).type == 'cuda' and prefer_fused:
+    from ... import settings
+    if device is not None and torch.device(device).type == 'cuda' and prefer_fused and not settings.ORIGINAL_HOROVOD:
         from .nvl import NvlComm  # needs the native library
         return NvlComm.shared()
     return TorchDistComm()

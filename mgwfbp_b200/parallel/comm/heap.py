@@ -23,6 +23,7 @@ sequence of ``alloc`` / ``free`` calls, so offsets agree without communication; 
 """
 from __future__ import annotations
 
+import array
 import ctypes as C
 import os
 import socket
@@ -74,10 +75,18 @@ def exchange_fds(my_fd: Optional[int], senders: Sequence[int], timeout_s: float 
         if rank in senders:
             for r in range(world):
                 if r != rank:
-                    socket.send_fds(sock, [struct.pack('i', rank)], [int(my_fd)], 0, _socket_name(seq, r))
+                    sock.sendmsg([struct.pack('i', rank)],
+                                 [(socket.SOL_SOCKET, socket.SCM_RIGHTS, array.array('i', [int(my_fd)]))], 0,
+                                 _socket_name(seq, r))
         expect = [s for s in senders if s != rank]
         while len(got) < len(expect):
-            msg, fds, _flags, _addr = socket.recv_fds(sock, 16, 1)
+            fds = array.array('i')
+            msg, ancdata, _flags, _addr = sock.recvmsg(16, socket.CMSG_LEN(fds.itemsize))
+            for level, kind, data in ancdata:
+                if level == socket.SOL_SOCKET and kind == socket.SCM_RIGHTS:
+                    fds.frombytes(data[:len(data) - (len(data) % fds.itemsize)])
+            if len(fds) != 1:
+                raise OSError('message without a file descriptor')
             got[struct.unpack('i', msg[:4])[0]] = fds[0]
         runtime.barrier()
     finally:

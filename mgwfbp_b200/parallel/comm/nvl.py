@@ -147,6 +147,8 @@ class NvlComm(Communicator):
     # ------------------------------------------------------------------ status
     def status(self) -> Tuple[int, int, int, int, int]:
         s = self._status
+        if not s:                                   # closed
+            return (0, 0, 0, 0, 0)
         return (s[0], s[1], s[2], s[3], s[4])
 
     def check_status(self, synchronize: bool = False) -> None:
@@ -302,6 +304,8 @@ class NvlComm(Communicator):
         self._hyper.pop(key, None)
         for st in getattr(opt, '_ext_state', {}).values():
             st['bufs'] = None
+        for _name, _p, module in getattr(opt, '_external', []):
+            module._exchange = None                 # the layer behaves like nn.Linear again
 
     # ------------------------------------------------------------------ hot path
     def launch_group(self, opt, gi: int) -> None:

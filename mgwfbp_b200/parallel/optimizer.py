@@ -181,7 +181,10 @@ class _DistributedMixin:
         names = self._sequential_keys
         sizes = [self._named_parameters[k].numel() for k in names]
         self._sizes = sizes
-        if settings.ADAPTIVE_MERGE and self._layerwise_times is not None:
+        if settings.ORIGINAL_HOROVOD and not self._fused_comm:
+            # the stock arm: Horovod's tensor fusion is a fixed-size bucket, no profile involved
+            sched = groups_by_threshold(names, sizes, settings.HOROVOD_FUSION_ELEMENTS)
+        elif settings.ADAPTIVE_MERGE and self._layerwise_times is not None:
             if len(self._layerwise_times) != len(names):
                 raise ValueError('layerwise_times and seq_layernames differ in length')
             nbytes = 2 if settings.FP16 else 4

@@ -80,7 +80,16 @@ def init(backend: Optional[str] = None, timeout_s: Optional[float] = None, devic
 
 
 def shutdown() -> None:
-    """Leave the job; safe to call twice."""
+    """Leave the job; safe to call twice.  A live NVLink communicator is closed first (collective: its symmetric
+    memory is unmapped and, where bound, released from the NVSwitch multicast object while all ranks are still there)."""
+    try:
+        import sys
+        nvl = sys.modules.get(__package__ + '.comm.nvl')
+        comm = getattr(getattr(nvl, 'NvlComm', None), '_shared', None) if nvl is not None else None
+        if comm is not None:
+            comm.close()
+    except Exception as e:  # pragma: no cover - teardown is best effort (e.g. a peer is already gone)
+        logger.warning('closing the NVLink communicator failed: %s', e)
     if _state['initialized'] and _state['owns_pg'] and dist.is_initialized():
         try:
             dist.destroy_process_group()

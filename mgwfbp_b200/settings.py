@@ -84,13 +84,20 @@ WRITE_BACK_GRADS = _env_flag('WRITE_BACK_GRADS', False)
 # while this is on.
 SHADOW_EVERY = int(_env_str('SHADOW', '0') or 0)
 
-# Fraction of a second that backward loses per second of all-reduce kernel running beside it (0 = overlapped
-# communication is free, the assumption of the MG-WFBP recurrences; 1 = it costs as much as exposed communication).
-# Used only with the fused NVLink data plane, whose kernels share SMs and memory bandwidth with backward.
-# Measured on B200 (2 GPUs, batch 64/32 per GPU): ResNet-50 12.34 ms/step with the plain MG-WFBP schedule (95
-# messages), 12.02 with three 32 MB buckets, 12.00 with one message; DenseNet-201 27.5 (402 messages) vs 24.7 ms
-# (one); i.e. overlap buys nothing there and every extra message costs, which is what 1.0 expresses.
-INTERFERENCE = float(_env_str('INTERFERENCE', '1.0'))
+# Seconds of backward lost per second of all-reduce kernel running beside it (0 = overlapped communication is free,
+# the assumption of the MG-WFBP recurrences; 1 = it costs as much as exposed communication and the schedule collapses
+# to one message).  Only the fused NVLink data plane has such a cost: its kernels share SMs and memory bandwidth with
+# backward.  The entry points measure it on the running box for the planned CTA count (``engine.fit_interference``)
+# and then confirm the schedule by timing it (``engine.tune_schedule``); this value is what a bare
+# ``DistributedOptimizer(...)`` uses when nothing was measured, or what ``MGWFBP_INTERFERENCE`` pins.
+_interference_env = _env_str('INTERFERENCE', '')
+INTERFERENCE_PINNED = _interference_env != ''
+INTERFERENCE = float(_interference_env) if INTERFERENCE_PINNED else 0.25
+
+# The stock comparison arm (reference dist_trainer.py:12-15 imports horovod.torch itself when this is set): gradients
+# go through torch.distributed (NCCL on GPUs) in Horovod-style fusion buckets of 64 MB, the update is torch's own
+# SGD.step, none of this package's communication or update kernels run.
+HOROVOD_FUSION_ELEMENTS = 16 * 1024 * 1024
 
 # 'auto' | 'oneshot' | 'twoshot' | 'nvls'
 COMM_ALGO = _env_str('COMM_ALGO', 'auto')

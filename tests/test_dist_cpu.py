@@ -23,6 +23,9 @@ def _worker(rank, world, port, fn, args, out_dir, use_cuda=False):
     sys.path.insert(0, ROOT)
     torch.set_num_threads(1)
     os.environ.setdefault('NCCL_NVLS_ENABLE', '0')
+    # tests that exercise the NVSwitch multicast path ask for it themselves; everything else (failure tests above all)
+    # runs on peer loads and stores only
+    os.environ.setdefault('MGWFBP_NVLS', '0')
     import mgwfbp_b200 as hvd
     hvd.init(timeout_s=float(os.environ.get('MGWFBP_TEST_TIMEOUT_S', '120')), device='cuda' if use_cuda else 'cpu')
     try:

@@ -93,3 +93,62 @@ def test_fp16_mode_trains_and_tracks_fp32():
     num = sum(float((a - b).pow(2).sum()) for a, b in zip(p16, p32))
     den = sum(float(b.pow(2).sum()) for b in p32)
     assert (num / den) ** 0.5 < 2e-2, 'fp16 run drifted from the fp32 run: relative distance %.4f' % ((num / den) ** 0.5)
+
+
+def test_short_batch_after_capture_runs_eagerly_and_replay_resumes():
+    """The last batch of an epoch is shorter than the captured one (loaders do not drop it): that step runs eagerly,
+    the next full batch goes through the graph again, and the trajectory equals an all-eager run."""
+    from mgwfbp_b200.engine import TrainStep
+    torch.backends.cudnn.allow_tf32 = False
+    torch.backends.cudnn.deterministic = True
+    try:
+        g = torch.Generator().manual_seed(5)
+        sizes = [16, 16, 16, 16, 16, 7, 16, 16, 5, 16]
+        batches = [(torch.randn(n, 3, 32, 32, generator=g).pin_memory(), torch.randint(0, 10, (n,), generator=g).pin_memory())
+                   for n in sizes]
+        out = {}
+        for mode in (False, True):
+            t = _trainer('resnet20', 'cifar10', 16, lr=0.05)
+            step = TrainStep(t, use_graph=mode)
+            for b in batches:
+                step.run(b)
+            step.drain()
+            torch.cuda.synchronize()
+            out[mode] = (list(step.losses), [p.detach().clone() for p in t.net.parameters()], step.eager_after_capture)
+        assert out[True][2] == 2 and out[False][2] == 0
+        for a, b in zip(out[False][0], out[True][0]):
+            assert abs(a - b) < 2e-3 * max(1.0, abs(a)), (out[False][0], out[True][0])
+        for a, b in zip(out[False][1], out[True][1]):
+            torch.testing.assert_close(a, b, rtol=1e-3, atol=1e-4)
+    finally:
+        torch.backends.cudnn.allow_tf32 = True
+        torch.backends.cudnn.deterministic = False
+
+
+def test_status_word_is_read_during_graph_replay():
+    """A communication kernel that gave up waiting leaves a record in host-mapped memory.  TrainStep looks at it on
+    every step, also while it only replays a graph.  The record is written by the test itself (no kernel fails)."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200.engine import TrainStep
+    from mgwfbp_b200.parallel.comm.base import CommTimeoutError
+    from mgwfbp_b200.parallel.comm.nvl import NvlComm
+    from mgwfbp_b200.trainer import DLTrainer
+    t = DLTrainer(0, 1, dist=False, ngpus=1, batch_size=16, data_dir='synthetic', dataset='cifar10', dnn='resnet20', lr=0.05,
+                  nworkers=1, seed=0)
+    t.num_batches_per_epoch = 10 ** 9
+    comm = NvlComm.shared()
+    opt = hvd.DistributedOptimizer(t.optimizer, named_parameters=t.net.named_parameters(), threshold=100000, comm=comm)
+    t.update_optimizer(opt)
+    step = TrainStep(t, use_graph=True)
+    for _ in range(6):
+        step.run(t.data_iter())
+    step.drain()
+    assert step.graphed
+    comm._status[1], comm._status[2], comm._status[3], comm._status[4] = 3, 17, 16, 5
+    comm._status[0] = 1                                        # MGW_STATUS_TIMEOUT as a kernel would record it
+    with pytest.raises(CommTimeoutError, match='waited for rank 3'):
+        step.run(t.data_iter())
+    comm.clear_status()
+    step.run(t.data_iter())                                    # training continues once the record is cleared
+    step.drain()
+    opt.close()

@@ -235,10 +235,12 @@ def _missing_peer(rank, world):
     """Rank 1 never launches its group: rank 0's kernel must time out and report, not hang.
     The failure is injected on the host (a skipped launch); no GPU is faulted."""
     os.environ['MGWFBP_COMM_TIMEOUT_S'] = '0.2'
+    os.environ['MGWFBP_HEAP'] = 'ipc'                  # plain peer memory, nothing bound to the switch
     from mgwfbp_b200.parallel.comm.base import CommTimeoutError
     from mgwfbp_b200.parallel.comm.nvl import NvlComm
     import mgwfbp_b200 as hvd
     comm = NvlComm.shared()
+    assert not comm.nvls_available
     x = torch.ones(4096, device='cuda')
     comm.synchronize(comm.allreduce_async_(x.clone()))          # a healthy round first
     torch.cuda.synchronize()
@@ -262,15 +264,18 @@ def test_missing_peer_is_reported_not_hung():
 
 
 def _nvls_allreduce(rank, world):
-    """NVSwitch multicast path (multimem.ld_reduce / multimem.st) on a heap from torch's symmetric memory.
-    Every rank reaches the final barrier whatever happens, so no rank leaves while peers still use the heap."""
-    os.environ['MGWFBP_HEAP'] = 'torch'
+    """NVSwitch multicast path (multimem.ld_reduce / multimem.st) on the package's own heap (cuMemCreate memory bound
+    to a multicast object).  Every rank reaches the final barrier whatever happens, so no rank leaves while peers
+    still use the heap."""
+    os.environ['MGWFBP_HEAP'] = 'vmm'
+    os.environ['MGWFBP_NVLS'] = '1'
     import mgwfbp_b200 as hvd
     out = {'available': False, 'error': None, 'results': {}}
     try:
         from mgwfbp_b200.parallel.comm.nvl import NvlComm
         comm = NvlComm.shared()
         out['available'] = bool(comm.nvls_available)
+        out['heap'] = comm.arena.heaps[0].kind
         if comm.nvls_available:
             for numel in (4096, (1 << 20) + 4):
                 g = torch.Generator(device='cuda').manual_seed(77 * rank + 1)
@@ -297,3 +302,151 @@ def test_nvls_multimem_allreduce_when_available():
         for r in res:
             torch.testing.assert_close(r['results'][numel][1].double(), want, rtol=1e-5, atol=1e-5)
             assert torch.equal(r['results'][numel][1], res[0]['results'][numel][1])
+
+
+def _selfcheck_and_heap(rank, world, nvls):
+    os.environ['MGWFBP_NVLS'] = '1' if nvls else '0'
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200.parallel.comm.nvl import NvlComm
+    from mgwfbp_b200.parallel.comm.selfcheck import selfcheck
+    comm = NvlComm.shared()
+    out = selfcheck(comm)
+    out['heap'] = comm.arena.heaps[0].kind
+    # blocks come back to the arena and are handed out again at the same offsets on every rank
+    a = comm.arena.alloc(1 << 20)
+    b = comm.arena.alloc(3 << 20)
+    offs = (a.off, b.off)
+    comm.arena.free(a)
+    c = comm.arena.alloc(1 << 19)
+    out['offsets'] = (offs, c.off)
+    hvd.barrier()
+    return out
+
+
+@pytest.mark.parametrize('nvls', [False, True])
+def test_selfcheck_on_the_default_heap(nvls):
+    res = run_ranks(_selfcheck_and_heap, (nvls,), world=_world())
+    assert all(r['heap'] == 'vmm' for r in res), [r['heap'] for r in res]
+    assert all(r['ok'] and r['bitwise_equal'] for r in res), res[0]
+    assert len({str(r['offsets']) for r in res}) == 1
+    assert res[0]['offsets'][1] == res[0]['offsets'][0][0]          # the freed block was reused
+    if nvls and not res[0]['multicast_heap']:
+        pytest.skip('the devices offer no NVSwitch multicast; checked one-shot and two-shot only')
+    if nvls:
+        assert 'nvls' in res[0]['algorithms']
+
+
+def _graph_replay_with_moving_lr(rank, world):
+    """Learning rate changes before every replay of the captured step (what the warm-up schedule does); the
+    table upload must be ordered against the replays on every rank, or replicas drift apart."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
+    from mgwfbp_b200.engine import TrainStep
+    from mgwfbp_b200.trainer import DLTrainer
+    settings.ADAPTIVE_MERGE = False
+    t = DLTrainer(rank, world, dist=False, ngpus=1, batch_size=16, data_dir='synthetic', dataset='cifar10', dnn='resnet20',
+                  lr=0.1, nworkers=world, seed=0)
+    t.num_batches_per_epoch = 40            # warm-up over 5 "epochs" of 40 steps: lr differs at every step
+    opt = hvd.DistributedOptimizer(t.optimizer, named_parameters=t.net.named_parameters(), threshold=100000)
+    hvd.broadcast_parameters(t.net.state_dict(), 0)
+    t.update_optimizer(opt)
+    step = TrainStep(t, use_graph=True)
+    lrs = []
+    for _ in range(14):
+        step.run(t.data_iter())
+        lrs.append(t.lr)
+    step.drain()
+    torch.cuda.synchronize()
+    return {'graphed': step.graphed, 'lrs': lrs, 'params': [p.detach().cpu() for p in t.net.parameters()],
+            'losses': list(step.losses)}
+
+
+def test_replicas_stay_identical_while_lr_moves_under_graph_replay():
+    res = run_ranks(_graph_replay_with_moving_lr, (), world=2)
+    assert res[0]['graphed'] and len(set(res[0]['lrs'])) == len(res[0]['lrs'])
+    for a, b in zip(res[0]['params'], res[1]['params']):
+        assert torch.equal(a, b), 'replicas diverged'
+    assert all(l == l for l in res[0]['losses'])
+
+
+def _missing_peer_under_graph_replay(rank, world):
+    """Rank 1 skips one replay of its captured step on the host.  Rank 0's communication kernels run into their
+    bounded wait, record it, and the next look at the status word -- TrainStep does that every step -- raises.
+    Nothing faults: plain peer memory, short timeout, both ranks meet at the final barrier."""
+    os.environ['MGWFBP_COMM_TIMEOUT_S'] = '0.2'
+    os.environ['MGWFBP_HEAP'] = 'ipc'
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
+    from mgwfbp_b200.engine import TrainStep
+    from mgwfbp_b200.parallel.comm.base import CommTimeoutError
+    from mgwfbp_b200.trainer import DLTrainer
+    settings.ADAPTIVE_MERGE = False
+    settings.WARMUP = False
+    t = DLTrainer(rank, world, dist=False, ngpus=1, batch_size=16, data_dir='synthetic', dataset='cifar10', dnn='resnet20',
+                  lr=0.05, nworkers=world, seed=0)
+    t.num_batches_per_epoch = 10 ** 9
+    opt = hvd.DistributedOptimizer(t.optimizer, named_parameters=t.net.named_parameters(), threshold=100000)
+    hvd.broadcast_parameters(t.net.state_dict(), 0)
+    t.update_optimizer(opt)
+    step = TrainStep(t, use_graph=True)
+    for _ in range(6):
+        step.run(t.data_iter())
+    step.drain()
+    torch.cuda.synchronize()
+    assert step.graphed
+    hvd.barrier()
+    err, after = None, 0
+    if rank == 0:
+        try:
+            for after in range(1, 4):               # the step rank 1 skips, and at most two more looks
+                step.run(t.data_iter())
+                torch.cuda.synchronize()
+            step.drain()
+        except CommTimeoutError as e:
+            err = str(e)
+    hvd.barrier()
+    torch.cuda.synchronize()
+    alive = float((torch.ones(4, device='cuda') * 3).sum())
+    return {'err': err, 'steps_until_raise': after, 'alive': alive}
+
+
+def test_missing_peer_is_detected_under_graph_replay():
+    res = run_ranks(_missing_peer_under_graph_replay, (), world=2)
+    assert res[0]['err'] and 'gave up' in res[0]['err'], res[0]
+    assert res[0]['steps_until_raise'] <= 2
+    assert res[0]['alive'] == 12.0 and res[1]['alive'] == 12.0
+
+
+def _tuned_schedule(rank, world):
+    """engine.build_distributed_optimizer end to end on a small model: cost-model fit, interference fit, trial."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
+    from mgwfbp_b200.engine import TrainStep, build_distributed_optimizer
+    from mgwfbp_b200.trainer import DLTrainer
+    from mgwfbp_b200.utils.profiling import benchmark
+    settings.ADAPTIVE_MERGE = True
+    t = DLTrainer(rank, world, dist=False, ngpus=1, batch_size=32, data_dir='synthetic', dataset='cifar10', dnn='resnet20',
+                  lr=0.05, nworkers=world, seed=0)
+    t.num_batches_per_epoch = 10 ** 9
+    seq, times, _ = benchmark(t, warmup=2, iteration=4)
+    times = hvd.broadcast_object(list(times), 0)
+    opt, info = build_distributed_optimizer(t, seq_layernames=seq, layerwise_times=times, trial_steps=4)
+    step = TrainStep(t, use_graph=True)
+    for _ in range(6):
+        step.run(t.data_iter())
+    step.drain()
+    torch.cuda.synchronize()
+    opt.communicator.check_status()
+    return {'info': info, 'groups': len(opt.merge_schedule.groups), 'losses': list(step.losses),
+            'params': [p.detach().cpu() for p in t.net.parameters()]}
+
+
+def test_schedule_is_measured_and_confirmed_by_trial():
+    res = run_ranks(_tuned_schedule, (), world=2)
+    info = res[0]['info']
+    assert 0.0 <= info['interference']['rho'] <= 1.0 and info['interference']['t_alone_ms'] > 0
+    assert info['trial'] and all(r['ms_per_step'] > 0 for r in info['trial'])
+    assert info['cost_model'] and info['cost_model_overlapped']
+    assert res[0]['groups'] == res[1]['groups'] >= 1
+    for a, b in zip(res[0]['params'], res[1]['params']):
+        assert torch.equal(a, b), 'replicas diverged'

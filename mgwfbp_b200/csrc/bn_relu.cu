@@ -4,14 +4,19 @@
 //
 // Forward = two streaming passes instead of cuDNN BatchNorm + add + ReLU (two extra passes over the
 // activation):
-//   bn_stats_kernel        : per-channel sum / sum of squares, one deterministic partial per row split
-//   bn_fwd_finalize_kernel : (tiny) combines the partials in double, saves mean / inv-std, updates the
-//                            running statistics and num_batches_tracked
+//   bn_stats_kernel        : per-channel sum / sum of squares, one deterministic partial per row split;
+//                            the LAST block of a channel tile to finish combines the tile's partials in double,
+//                            saves mean / inv-std and updates the running statistics (see "finalize" below)
 //   bn_apply_kernel        : y = relu(x * scale + shift (+ residual))
 // Backward:
-//   bn_bwd_reduce_kernel   : dz = dy * relu'(.); partial sums of dz and dz * xhat
-//   bn_bwd_finalize_kernel : (tiny) dgamma, dbeta
+//   bn_bwd_reduce_kernel   : dz = dy * relu'(.); partial sums of dz and dz * xhat; last block: dgamma, dbeta
 //   bn_bwd_apply_kernel    : dx = scale * (dz - (dbeta + xhat * dgamma) / M)
+// Finalize: every block of a channel tile bumps an arrival counter after its partials are visible; the block that
+// sees the last count does the tile's (tiny) final reduction, in a fixed order, and resets the counter.  Nobody
+// waits for anybody, so nothing can hang, and the result does not depend on which block came last.  That makes
+// two launches per direction; on the 14x14 and 7x7 stages of a ResNet a separate finalize launch cost as much as
+// the data movement itself.  Problems with very many row splits keep the separate bn_*_finalize_kernel (a single
+// block would take longer over the partials than a launch costs).
 // With a residual input dz is materialised (it is the residual's gradient) and the ReLU mask is read
 // from the saved output; without one neither y nor dz is touched: the mask is recomputed from x, so
 // the backward pass is 4 reads + 1 write of the activation instead of 5 + 2.
@@ -20,6 +25,7 @@
 // 16-byte access when VEC = 4) by TY rows; grid.x tiles the channels, grid.y splits the rows.
 // All of it is bandwidth-bound; the second pass of each direction re-reads tensors that the first
 // pass just streamed, which the 126 MB L2 serves for the smaller layers.
+#include <atomic>
 #include "api.h"
 
 namespace {
@@ -101,9 +107,87 @@ __device__ __forceinline__ void block_reduce_rows(float (&a)[VEC], float (&b)[VE
     __syncthreads();
 }
 
+// Arrival counters of the fused finalize: a ring of slots, all zero whenever no kernel is using them (the last
+// block of a tile puts its slot back to zero).  A launch takes gridDim.x consecutive slots; the host hands out
+// ranges round-robin, so launches that could overlap on the GPU (different streams) do not share slots unless
+// kRing / gridDim.x other launches were issued in between.
+constexpr int kRing = 16384;
+constexpr int kFuseMaxSplits = 320;      // more row splits than this: separate finalize kernel
+constexpr int kFuseMaxTiles = 256;
+__device__ unsigned int g_bn_arrivals[kRing];
+
+struct FwdFinal {
+    float* running_mean; float* running_var; long long* num_batches_tracked;
+    float momentum, eps;
+    float* save_mean; float* save_invstd;
+    int slot0;               // first arrival slot of this launch, or -1: a separate kernel finalizes
+};
+
+struct BwdFinal {
+    float* dgamma; float* dbeta;
+    int slot0;
+};
+
+// True in every thread of exactly one block per channel tile: the one whose arrival completed the tile.
+__device__ __forceinline__ bool last_block_of_tile(int slot0, int* flag) {
+    __threadfence();                         // this thread's partials are visible device-wide ...
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();                     // ... and so are those of the whole block, before the arrival is counted
+        const unsigned prev = atomicAdd(&g_bn_arrivals[slot0 + blockIdx.x], 1u);
+        *flag = (prev == gridDim.y - 1);
+        __threadfence();
+    }
+    __syncthreads();
+    return *flag != 0;
+}
+
+// Totals of the two partial arrays for the channels of this block's tile, combined in double in an order that
+// depends only on the launch geometry.  Valid in threads with part == 0 (threadIdx.x < CT), channel c.
+__device__ __forceinline__ void tile_totals(const float* __restrict__ partials, int n_splits, int C, int CT, double* sm,
+                                            double& a, double& b, int& c) {
+    const int cl = threadIdx.x % CT, part = threadIdx.x / CT, nparts = kThreads / CT;
+    c = blockIdx.x * CT + cl;
+    double ra = 0.0, rb = 0.0;
+    if (c < C && part < nparts) {
+        for (int s = part; s < n_splits; s += nparts) {
+            const float* ps = partials + (size_t)s * 2 * C;
+            ra += (double)__ldcg(ps + c);
+            rb += (double)__ldcg(ps + C + c);
+        }
+    }
+    __syncthreads();                         // the float staging area of the row reduction is free again
+    if (part < nparts) {
+        sm[part * CT + cl] = ra;
+        sm[kThreads + part * CT + cl] = rb;
+    }
+    __syncthreads();
+    a = b = 0.0;
+    if (part == 0) {
+        for (int r = 0; r < nparts; ++r) {
+            a += sm[r * CT + cl];
+            b += sm[kThreads + r * CT + cl];
+        }
+    }
+}
+
+__device__ __forceinline__ void fwd_finalize_channel(double sum, double sq, long long M, int c, const FwdFinal& f) {
+    const double mean = sum / (double)M;
+    double var = sq / (double)M - mean * mean;
+    if (var < 0.0) var = 0.0;
+    f.save_mean[c] = (float)mean;
+    f.save_invstd[c] = (float)(1.0 / sqrt(var + (double)f.eps));
+    if (f.running_mean) {
+        const double unbiased = M > 1 ? var * (double)M / (double)(M - 1) : var;
+        f.running_mean[c] = (1.f - f.momentum) * f.running_mean[c] + f.momentum * (float)mean;
+        f.running_var[c] = (1.f - f.momentum) * f.running_var[c] + f.momentum * (float)unbiased;
+    }
+}
+
 template <int VEC>
 __global__ void __launch_bounds__(kThreads, 4)
-bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int rows_per_split, float* __restrict__ partials) {
+bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int rows_per_split, float* __restrict__ partials,
+                const FwdFinal fin) {
     extern __shared__ float smem[];
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
@@ -135,6 +219,17 @@ bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int row
                 ps[C + c0 + k] = q[k];
             }
         }
+    }
+    if (fin.slot0 < 0) return;
+    __shared__ int last;
+    if (!last_block_of_tile(fin.slot0, &last)) return;
+    double sum, sq;
+    int c;
+    tile_totals(partials, gridDim.y, C, TX * VEC, reinterpret_cast<double*>(smem), sum, sq, c);
+    if (threadIdx.x < TX * VEC && c < C) fwd_finalize_channel(sum, sq, M, c, fin);
+    if (threadIdx.x == 0) {
+        g_bn_arrivals[fin.slot0 + blockIdx.x] = 0u;
+        if (blockIdx.x == 0 && fin.num_batches_tracked) *fin.num_batches_tracked += 1;
     }
 }
 
@@ -327,7 +422,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
                      const unsigned char* __restrict__ bits, const float* __restrict__ x, float* __restrict__ dz,
                      long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                      const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
-                     float* __restrict__ partials, const PoolArgs pool) {
+                     float* __restrict__ partials, const PoolArgs pool, const BwdFinal fin) {
     extern __shared__ float smem[];
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
@@ -373,6 +468,17 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
             }
         }
     }
+    if (fin.slot0 < 0) return;
+    __shared__ int last;
+    if (!last_block_of_tile(fin.slot0, &last)) return;
+    double a, b;
+    int c;
+    tile_totals(partials, gridDim.y, C, TX * VEC, reinterpret_cast<double*>(smem), a, b, c);
+    if (threadIdx.x < TX * VEC && c < C) {
+        fin.dbeta[c] = (float)a;
+        fin.dgamma[c] = (float)b;
+    }
+    if (threadIdx.x == 0) g_bn_arrivals[fin.slot0 + blockIdx.x] = 0u;
 }
 
 // gsrc is dz (mask already applied, mask_mode 0) or dy (mask applied here again, mask_mode 1 / 2).
@@ -466,6 +572,21 @@ bn_relu_maxpool_kernel(const float* __restrict__ x, float* __restrict__ yp, unsi
     }
 }
 
+// Arrival slots for a launch of grid (gx, gy), or -1 when the problem keeps the separate finalize kernel.
+int take_slots(int gx, int gy) {
+    static std::atomic<unsigned> next{0};
+    if (gy > kFuseMaxSplits || gx > kFuseMaxTiles) return -1;
+    for (;;) {
+        const unsigned off = next.fetch_add((unsigned)gx) % (unsigned)kRing;
+        if (off + (unsigned)gx <= (unsigned)kRing) return (int)off;
+    }
+}
+
+size_t reduce_smem(int vec) {
+    const size_t rows = sizeof(float) * 2 * kThreads * vec, fin = sizeof(double) * 2 * kThreads;
+    return rows > fin ? rows : fin;
+}
+
 }  // namespace
 
 extern "C" {
@@ -474,6 +595,13 @@ extern "C" {
 size_t mgw_bn_partials_floats(long long M, int C) {
     const Tiling t = make_tiling(M, C, (C % 4 == 0) ? 4 : 1);
     return (size_t)t.grid_y * 2 * (size_t)C;
+}
+
+// Kernel launches one forward (backward = 0) or backward (backward = 1) call issues for an [M, C] problem:
+// two when the finalize step rides in the reduction kernel, three otherwise.  (Reporting only.)
+int mgw_bn_launches(long long M, int C, int backward) {
+    const Tiling t = make_tiling(M, C, (C % 4 == 0) ? 4 : 1, backward ? 2 : 4);
+    return (t.grid_y > kFuseMaxSplits || t.grid_x > kFuseMaxTiles) ? 3 : 2;
 }
 
 int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M, int C, const float* gamma, const float* beta,
@@ -486,20 +614,24 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
     const Tiling t = make_tiling(M, C, vec);
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
+    const size_t smem_red = reduce_smem(vec);
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
+    const FwdFinal fin = {running_mean, running_var, num_batches_tracked, momentum, eps, save_mean, save_invstd,
+                          take_slots(t.grid_x, t.grid_y)};
     if (vec == 4) {
-        bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
-        bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
-                                                        momentum, eps, save_mean, save_invstd);
+        bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials, fin);
+        if (fin.slot0 < 0)
+            bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
+                                                            momentum, eps, save_mean, save_invstd);
         if (relu_bits)
             bn_apply_kernel<4, true><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd, relu_bits);
         else
             bn_apply_kernel<4, false><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd, nullptr);
     } else {
-        bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
-        bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
-                                                        momentum, eps, save_mean, save_invstd);
+        bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials, fin);
+        if (fin.slot0 < 0)
+            bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
+                                                            momentum, eps, save_mean, save_invstd);
         bn_apply_kernel<1, false><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd, nullptr);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
@@ -530,15 +662,16 @@ int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const flo
     const Tiling t = make_tiling(M, C, vec, 2);      // backward kernels hold 2 blocks per SM
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
+    const size_t smem_red = reduce_smem(vec);
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
+    const BwdFinal fin = {dgamma, dbeta, take_slots(t.grid_x, t.grid_y)};
     if (vec == 4) {
-        bn_bwd_reduce_kernel<4, false><<<grid, block, smem_red, s>>>(dy, dy2, y, relu_bits, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
-        bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
+        bn_bwd_reduce_kernel<4, false><<<grid, block, smem_red, s>>>(dy, dy2, y, relu_bits, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool, fin);
+        if (fin.slot0 < 0) bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
         bn_bwd_apply_kernel<4, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     } else {
-        bn_bwd_reduce_kernel<1, false><<<grid, block, smem_red, s>>>(dy, dy2, y, relu_bits, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool);
-        bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
+        bn_bwd_reduce_kernel<1, false><<<grid, block, smem_red, s>>>(dy, dy2, y, relu_bits, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool, fin);
+        if (fin.slot0 < 0) bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
         bn_bwd_apply_kernel<1, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
@@ -558,19 +691,23 @@ int mgw_bn_relu_maxpool_fwd(const float* x, float* y_pool, unsigned char* idx, i
     const Tiling t = make_tiling(M, C, vec);
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
+    const size_t smem_red = reduce_smem(vec);
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     const long long work = (long long)N * OH * OW * (C / vec);
     const int pgrid = (int)((work + 255) / 256 < 148LL * 16 ? (work + 255) / 256 : 148LL * 16);
+    const FwdFinal fin = {running_mean, running_var, num_batches_tracked, momentum, eps, save_mean, save_invstd,
+                          take_slots(t.grid_x, t.grid_y)};
     if (vec == 4) {
-        bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
-        bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
-                                                        momentum, eps, save_mean, save_invstd);
+        bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials, fin);
+        if (fin.slot0 < 0)
+            bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
+                                                            momentum, eps, save_mean, save_invstd);
         bn_relu_maxpool_kernel<4><<<pgrid, 256, 0, s>>>(x, y_pool, idx, N, H, W, OH, OW, C, gamma, beta, save_mean, save_invstd);
     } else {
-        bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials);
-        bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
-                                                        momentum, eps, save_mean, save_invstd);
+        bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials, fin);
+        if (fin.slot0 < 0)
+            bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
+                                                            momentum, eps, save_mean, save_invstd);
         bn_relu_maxpool_kernel<1><<<pgrid, 256, 0, s>>>(x, y_pool, idx, N, H, W, OH, OW, C, gamma, beta, save_mean, save_invstd);
     }
     MGW_CUDA_CHECK(cudaGetLastError());
@@ -590,15 +727,16 @@ int mgw_bn_relu_maxpool_bwd(const float* dp, const unsigned char* idx, const flo
     const Tiling t = make_tiling(M, C, vec, 2);      // backward kernels hold 2 blocks per SM
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_red = sizeof(float) * 2 * kThreads * vec;
+    const size_t smem_red = reduce_smem(vec);
     const dim3 fgrid((C + 31) / 32), fblock(32, 32);
+    const BwdFinal fin = {dgamma, dbeta, take_slots(t.grid_x, t.grid_y)};
     if (vec == 4) {
-        bn_bwd_reduce_kernel<4, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
-        bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
+        bn_bwd_reduce_kernel<4, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool, fin);
+        if (fin.slot0 < 0) bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
         bn_bwd_apply_kernel<4, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     } else {
-        bn_bwd_reduce_kernel<1, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool);
-        bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
+        bn_bwd_reduce_kernel<1, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool, fin);
+        if (fin.slot0 < 0) bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
         bn_bwd_apply_kernel<1, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
     }
     MGW_CUDA_CHECK(cudaGetLastError());

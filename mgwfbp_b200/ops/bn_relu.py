@@ -48,6 +48,7 @@ def _declare(lib) -> None:
     lib.mgw_bn_relu_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.mgw_bn_launches.argtypes = [C.c_longlong, C.c_int, C.c_int]
     lib.mgw_bn_cluster_supported.argtypes = [C.c_longlong, C.c_int]
     lib.mgw_bn_relu_fwd_cluster.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p,
                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_void_p,
@@ -98,7 +99,7 @@ class _BNReLU(torch.autograd.Function):
                                            _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
                                            float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
                                            partials.data_ptr(), _ptr(bits), s), 'bn_relu_fwd')
-            counters.bump('bn_relu_fwd', 3)
+            counters.bump('bn_relu_fwd', lib.mgw_bn_launches(M, Cc, 0))
         ctx.save_for_backward(x, y if (needs_mask and bits is None) else None, weight, bias, mean, invstd, bits)
         ctx.relu, ctx.has_residual, ctx.rows = bool(relu), residual is not None, (M, Cc)
         ctx.mark_non_differentiable(*[t for t in (running_mean, running_var, num_batches_tracked) if t is not None])
@@ -134,7 +135,7 @@ class _BNReLU(torch.autograd.Function):
             _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
                                            _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
                                            dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), _ptr(bits), s), 'bn_relu_bwd')
-            counters.bump('bn_relu_bwd', 3)
+            counters.bump('bn_relu_bwd', lib.mgw_bn_launches(M, Cc, 1))
         need = ctx.needs_input_grad
         return (dx if need[0] else None, dgamma if (weight is not None and need[1]) else None,
                 dbeta if need[2] else None, None, None, None, dz if (ctx.has_residual and need[6]) else None,

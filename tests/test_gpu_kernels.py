@@ -169,7 +169,10 @@ def _bn_reference(x, w, b, rm, rv, residual, relu, momentum, eps):
 # small shapes take the one-launch cluster kernels (up to 8 register rows per thread), the others the
 # three-launch kernels; `cluster=False` forces the three-launch kernels on the small shapes as well
 @pytest.mark.parametrize('shape', [(4, 64, 14, 14), (3, 16, 8, 8), (2, 6, 5, 7), (8, 256, 7, 7), (64, 96), (16, 128, 14, 14),
-                                   (24, 32, 14, 14), (64, 48, 14, 14), (21, 32, 28, 28), (8, 64, 56, 56)])
+                                   (24, 32, 14, 14), (64, 48, 14, 14), (21, 32, 28, 28), (8, 64, 56, 56),
+                                   # ResNet-50's small stages at batch 64 (finalize fused into the reduction kernels) and
+                                   # one problem with more row splits than the fused finalize takes (separate kernel)
+                                   (64, 256, 14, 14), (64, 1024, 14, 14), (64, 2048, 7, 7), (32, 64, 56, 56)])
 @pytest.mark.parametrize('relu,use_res', [(True, False), (True, True), (False, False)])
 @pytest.mark.parametrize('cluster', [True, False])
 def test_bn_relu_matches_pytorch(shape, relu, use_res, cluster, monkeypatch):
@@ -206,6 +209,17 @@ def test_bn_relu_matches_pytorch(shape, relu, use_res, cluster, monkeypatch):
     rows = x.numel() // C_
     took_cluster = counters.snapshot().get('bn_relu_fwd_cluster', 0) == 1 and counters.snapshot().get('bn_relu_bwd_cluster', 0) == 1
     assert took_cluster == (cluster and rows <= 8192 and C_ % 16 == 0 and C_ <= 288)
+    if not took_cluster:
+        # two launches per direction where the last block finalizes, three where a separate kernel does
+        from mgwfbp_b200.ops import _lib
+        lib = _lib.load(allow_build=False)
+        want = lib.mgw_bn_launches(rows, C_, 0), lib.mgw_bn_launches(rows, C_, 1)
+        assert (counters.snapshot().get('bn_relu_fwd'), counters.snapshot().get('bn_relu_bwd')) == want
+        assert set(want) <= {2, 3}
+    # a second pass over the same tensors: the arrival counters went back to zero, results repeat exactly
+    x3 = x.detach().clone().requires_grad_(True)
+    y3 = bn_relu(x3, w.detach(), b.detach(), rm.clone(), rv.clone(), nbt.clone(), res.detach() if use_res else None, relu, 0.1, 1e-5)
+    assert torch.equal(y3, y)
 
 
 @pytest.mark.parametrize('dnn,shape,classes', [('resnet20', (8, 3, 32, 32), 10), ('resnet50', (4, 3, 64, 64), 1000)])

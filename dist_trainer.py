@@ -22,7 +22,7 @@ import torch
 
 import mgwfbp_b200 as hvd
 from mgwfbp_b200 import settings
-from mgwfbp_b200.engine import TrainStep
+from mgwfbp_b200.engine import TrainStep, build_distributed_optimizer
 from mgwfbp_b200.settings import formatter, logger
 from mgwfbp_b200.trainer import DLTrainer, _support_datasets, _support_dnns
 from mgwfbp_b200.utils.compression import compressors
@@ -99,16 +99,20 @@ def mgwfbp(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_update, max_
         torch.cuda.set_device(rank % max(min(nwpernode, torch.cuda.device_count()), 1))
     trainer = _make_trainer(rank, (dnn, dataset, data_dir, nworkers, lr, batch_size, pretrain, num_steps))
     names, times, _sizes = _profile_backward(trainer, rank)
-    optimizer = hvd.DistributedOptimizer(trainer.optimizer, named_parameters=trainer.net.named_parameters(),
-                                         compression=compressors[compressor if density < 1 else None],
-                                         seq_layernames=names, layerwise_times=times, norm_clip=NORM_CLIP.get(dnn),
-                                         threshold=threshold, writer=writer, gradient_path=gradient_path)
-    hvd.broadcast_parameters(trainer.net.state_dict(), root_rank=0)
-    trainer.update_optimizer(optimizer)
+    # wrap the optimizer and broadcast the model (reference dist_trainer.py:55-66).  On an NVSwitch box with the
+    # adaptive policy this also fits the all-reduce cost model, measures how much an overlapped message slows backward
+    # down, and keeps the candidate schedule that trains fastest; with settings.ORIGINAL_HOROVOD it builds the stock
+    # arm instead (NCCL buckets through torch.distributed, torch's own SGD.step).
+    optimizer, tuning = build_distributed_optimizer(trainer, seq_layernames=names, layerwise_times=times,
+                                                    threshold=threshold, norm_clip=NORM_CLIP.get(dnn),
+                                                    compression=compressors[compressor if density < 1 else None],
+                                                    writer=writer, gradient_path=gradient_path, use_graph=use_graph)
+    if rank == 0 and tuning.get('trial'):
+        logger.info('merge schedule chosen by trial: %d groups; candidates %s', len(optimizer.merge_schedule.groups), tuning['trial'])
 
     iters_per_epoch = trainer.get_num_of_training_samples() // (nworkers * batch_size * nsteps_update)
     speed = _SpeedLog(10 if iters_per_epoch > 10 else iters_per_epoch - 1, batch_size * nsteps_update, trainer.is_cuda)
-    step: Optional[TrainStep] = TrainStep(trainer, use_graph=use_graph) if nsteps_update == 1 else None
+    step: Optional[TrainStep] = TrainStep(trainer, use_graph=use_graph, track_accuracy=True) if nsteps_update == 1 else None
     upcoming = trainer.data_iter() if step is not None else None
     logger.info('max_epochs: %d', max_epochs)
     done = 0

@@ -26,11 +26,45 @@
 // All of it is bandwidth-bound; the second pass of each direction re-reads tensors that the first
 // pass just streamed, which the 126 MB L2 serves for the smaller layers.
 #include <atomic>
+#include <cstdlib>
+#include <cstring>
 #include "api.h"
 
 namespace {
 
 constexpr int kThreads = 512;
+
+// Programmatic dependent launch: the second and third kernel of a direction are launched with the "programmatic
+// stream serialization" attribute, so their blocks may become resident while the previous kernel's last blocks
+// are still running; they do their index arithmetic and then wait (griddepcontrol.wait) until the previous grid
+// has completed and its writes are visible.  That removes the idle gap between the short kernels of the small
+// layers.  Both instructions are no-ops in a kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+bool env_on(const char* name, bool dflt) {
+    const char* v = getenv(name);
+    if (v == nullptr || *v == 0) return dflt;
+    return !(v[0] == '0' || v[0] == 'f' || v[0] == 'F' || v[0] == 'n' || v[0] == 'N');
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool dependent, Args... args) {
+    static const bool pdl = env_on("MGWFBP_BN_PDL", true);
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    const bool use = dependent && pdl;
+    cfg.attrs = use ? attr : nullptr;
+    cfg.numAttrs = use ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
 
 template <int VEC> struct Vec;
 template <> struct Vec<4> { using T = float4; };
@@ -142,31 +176,43 @@ __device__ __forceinline__ bool last_block_of_tile(int slot0, int* flag) {
     return *flag != 0;
 }
 
-// Totals of the two partial arrays for the channels of this block's tile, combined in double in an order that
-// depends only on the launch geometry.  Valid in threads with part == 0 (threadIdx.x < CT), channel c.
-__device__ __forceinline__ void tile_totals(const float* __restrict__ partials, int n_splits, int C, int CT, double* sm,
-                                            double& a, double& b, int& c) {
-    const int cl = threadIdx.x % CT, part = threadIdx.x / CT, nparts = kThreads / CT;
-    c = blockIdx.x * CT + cl;
-    double ra = 0.0, rb = 0.0;
-    if (c < C && part < nparts) {
+// Totals of ONE of the two partial arrays (which = 0 / 1) for the channels of this block's tile, combined in double
+// in an order that depends only on the launch geometry.  CT (channels per tile) is a multiple of VEC; a thread owns VEC
+// consecutive channels (one 16-byte load per partial row when VEC = 4) and every (512 * VEC / CT)-th partial row; the
+// per-thread sums meet in shared memory and the first CT / VEC threads finish them.  Kept out of line: it runs in
+// one block per tile only, and its registers must not weigh on the streaming loop of the kernel around it.
+template <int VEC>
+__device__ __noinline__ void tile_totals(const float* __restrict__ partials, int which, int n_splits, int C, int CT, double* sm,
+                                         double (&a)[VEC]) {
+    const int lanes = CT / VEC;
+    const int lane = threadIdx.x % lanes, part = threadIdx.x / lanes, nparts = kThreads / lanes;
+    const int c = blockIdx.x * CT + lane * VEC;
+    double ra[VEC];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) ra[k] = 0.0;
+    if (c < C) {
+        const float* base = partials + (size_t)which * C + c;
+#pragma unroll 4
         for (int s = part; s < n_splits; s += nparts) {
-            const float* ps = partials + (size_t)s * 2 * C;
-            ra += (double)__ldcg(ps + c);
-            rb += (double)__ldcg(ps + C + c);
+            const float* ps = base + (size_t)s * 2 * C;
+            if (VEC == 4) {
+                const float4 t0 = __ldcg(reinterpret_cast<const float4*>(ps));
+                ra[0] += (double)t0.x; ra[1 % VEC] += (double)t0.y; ra[2 % VEC] += (double)t0.z; ra[3 % VEC] += (double)t0.w;
+            } else {
+                ra[0] += (double)__ldcg(ps);
+            }
         }
     }
-    __syncthreads();                         // the float staging area of the row reduction is free again
-    if (part < nparts) {
-        sm[part * CT + cl] = ra;
-        sm[kThreads + part * CT + cl] = rb;
-    }
+    __syncthreads();                         // the staging area is free (row reduction, or the previous array)
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) sm[(part * lanes + lane) * VEC + k] = ra[k];
     __syncthreads();
-    a = b = 0.0;
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) a[k] = 0.0;
     if (part == 0) {
         for (int r = 0; r < nparts; ++r) {
-            a += sm[r * CT + cl];
-            b += sm[kThreads + r * CT + cl];
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) a[k] += sm[(r * lanes + lane) * VEC + k];
         }
     }
 }
@@ -189,6 +235,7 @@ __global__ void __launch_bounds__(kThreads, 4)
 bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int rows_per_split, float* __restrict__ partials,
                 const FwdFinal fin) {
     extern __shared__ float smem[];
+    pdl_release_dependents();
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int c0 = (blockIdx.x * TX + tx) * VEC;
@@ -223,10 +270,15 @@ bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int row
     if (fin.slot0 < 0) return;
     __shared__ int last;
     if (!last_block_of_tile(fin.slot0, &last)) return;
-    double sum, sq;
-    int c;
-    tile_totals(partials, gridDim.y, C, TX * VEC, reinterpret_cast<double*>(smem), sum, sq, c);
-    if (threadIdx.x < TX * VEC && c < C) fwd_finalize_channel(sum, sq, M, c, fin);
+    double sum[VEC], sq[VEC];
+    tile_totals<VEC>(partials, 0, gridDim.y, C, TX * VEC, reinterpret_cast<double*>(smem), sum);
+    tile_totals<VEC>(partials, 1, gridDim.y, C, TX * VEC, reinterpret_cast<double*>(smem), sq);
+    const int c = (blockIdx.x * TX + threadIdx.x) * VEC;
+    if (threadIdx.x < TX) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k)
+            if (c + k < C) fwd_finalize_channel(sum[k], sq[k], M, c + k, fin);
+    }
     if (threadIdx.x == 0) {
         g_bn_arrivals[fin.slot0 + blockIdx.x] = 0u;
         if (blockIdx.x == 0 && fin.num_batches_tracked) *fin.num_batches_tracked += 1;
@@ -263,6 +315,8 @@ bn_fwd_finalize_kernel(const float* __restrict__ partials, int n_splits, long lo
                        long long* num_batches_tracked, float momentum, float eps, float* __restrict__ save_mean,
                        float* __restrict__ save_invstd) {
     __shared__ double sm[2][32][32];
+    pdl_release_dependents();
+    pdl_wait();
     double sum, sq;
     finalize_sums(partials, n_splits, C, sum, sq, sm);
     const int c = blockIdx.x * 32 + threadIdx.x;
@@ -284,6 +338,8 @@ bn_fwd_finalize_kernel(const float* __restrict__ partials, int n_splits, long lo
 __global__ void __launch_bounds__(1024)
 bn_bwd_finalize_kernel(const float* __restrict__ partials, int n_splits, int C, float* __restrict__ dgamma, float* __restrict__ dbeta) {
     __shared__ double sm[2][32][32];
+    pdl_release_dependents();
+    pdl_wait();
     double a, b;
     finalize_sums(partials, n_splits, C, a, b, sm);
     const int c = blockIdx.x * 32 + threadIdx.x;
@@ -298,6 +354,7 @@ __global__ void __launch_bounds__(kThreads, 4)
 bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ residual, float* __restrict__ y, long long M, int C,
                 int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta, int relu,
                 const float* __restrict__ save_mean, const float* __restrict__ save_invstd, unsigned char* __restrict__ bits) {
+    pdl_wait();
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int c0 = (blockIdx.x * TX + tx) * VEC;
@@ -424,6 +481,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
                      const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
                      float* __restrict__ partials, const PoolArgs pool, const BwdFinal fin) {
     extern __shared__ float smem[];
+    pdl_release_dependents();
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int c0 = (blockIdx.x * TX + tx) * VEC;
@@ -471,12 +529,18 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
     if (fin.slot0 < 0) return;
     __shared__ int last;
     if (!last_block_of_tile(fin.slot0, &last)) return;
-    double a, b;
-    int c;
-    tile_totals(partials, gridDim.y, C, TX * VEC, reinterpret_cast<double*>(smem), a, b, c);
-    if (threadIdx.x < TX * VEC && c < C) {
-        fin.dbeta[c] = (float)a;
-        fin.dgamma[c] = (float)b;
+    double a[VEC], b[VEC];
+    tile_totals<VEC>(partials, 0, gridDim.y, C, TX * VEC, reinterpret_cast<double*>(smem), a);
+    tile_totals<VEC>(partials, 1, gridDim.y, C, TX * VEC, reinterpret_cast<double*>(smem), b);
+    const int c = (blockIdx.x * TX + threadIdx.x) * VEC;
+    if (threadIdx.x < TX) {
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) {
+            if (c + k < C) {
+                fin.dbeta[c + k] = (float)a[k];
+                fin.dgamma[c + k] = (float)b[k];
+            }
+        }
     }
     if (threadIdx.x == 0) g_bn_arrivals[fin.slot0 + blockIdx.x] = 0u;
 }
@@ -489,6 +553,7 @@ bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gs
                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                     const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
                     const float* __restrict__ dgamma, const float* __restrict__ dbeta, const PoolArgs pool) {
+    pdl_wait();
     const int TY = kThreads / TX;
     const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
     const int c0 = (blockIdx.x * TX + tx) * VEC;
@@ -531,6 +596,7 @@ __global__ void __launch_bounds__(256)
 bn_relu_maxpool_kernel(const float* __restrict__ x, float* __restrict__ yp, unsigned char* __restrict__ idx, int N, int H, int W,
                        int OH, int OW, int C, const float* __restrict__ gamma, const float* __restrict__ beta,
                        const float* __restrict__ save_mean, const float* __restrict__ save_invstd) {
+    pdl_wait();
     const int lanes = C / VEC;
     const long long total = (long long)N * OH * OW * lanes;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
@@ -572,10 +638,17 @@ bn_relu_maxpool_kernel(const float* __restrict__ x, float* __restrict__ yp, unsi
     }
 }
 
+bool fuse_enabled() {
+    static const bool fuse = env_on("MGWFBP_BN_FUSE_FINALIZE", true);
+    return fuse;
+}
+
+bool fused_geometry(int gx, int gy) { return fuse_enabled() && gy <= kFuseMaxSplits && gx <= kFuseMaxTiles; }
+
 // Arrival slots for a launch of grid (gx, gy), or -1 when the problem keeps the separate finalize kernel.
 int take_slots(int gx, int gy) {
     static std::atomic<unsigned> next{0};
-    if (gy > kFuseMaxSplits || gx > kFuseMaxTiles) return -1;
+    if (!fused_geometry(gx, gy)) return -1;
     for (;;) {
         const unsigned off = next.fetch_add((unsigned)gx) % (unsigned)kRing;
         if (off + (unsigned)gx <= (unsigned)kRing) return (int)off;
@@ -583,8 +656,66 @@ int take_slots(int gx, int gy) {
 }
 
 size_t reduce_smem(int vec) {
-    const size_t rows = sizeof(float) * 2 * kThreads * vec, fin = sizeof(double) * 2 * kThreads;
+    const size_t rows = sizeof(float) * 2 * kThreads * vec, fin = sizeof(double) * kThreads * vec;
     return rows > fin ? rows : fin;
+}
+
+struct FwdArgs {
+    const float* x; const float* residual; float* y; long long M; int C;
+    const float* gamma; const float* beta; float* running_mean; float* running_var; long long* nbt;
+    float momentum, eps; int relu; float* save_mean; float* save_invstd; float* partials; unsigned char* bits;
+};
+
+// statistics (+ finalize); returns the tiling for the caller's second pass
+template <int VEC>
+cudaError_t launch_stats(const FwdArgs& a, const Tiling& t, cudaStream_t s) {
+    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
+    const FwdFinal fin = {a.running_mean, a.running_var, a.nbt, a.momentum, a.eps, a.save_mean, a.save_invstd,
+                          take_slots(t.grid_x, t.grid_y)};
+    cudaError_t e = launch(bn_stats_kernel<VEC>, grid, block, reduce_smem(VEC), s, false, a.x, a.M, a.C, t.tx, t.rows_per_split,
+                           a.partials, fin);
+    if (e == cudaSuccess && fin.slot0 < 0)
+        e = launch(bn_fwd_finalize_kernel, dim3((a.C + 31) / 32), dim3(32, 32), 0, s, true, (const float*)a.partials, t.grid_y, a.M,
+                   a.C, a.running_mean, a.running_var, a.nbt, a.momentum, a.eps, a.save_mean, a.save_invstd);
+    return e;
+}
+
+template <int VEC>
+cudaError_t launch_fwd(const FwdArgs& a, cudaStream_t s) {
+    const Tiling t = make_tiling(a.M, a.C, VEC);
+    cudaError_t e = launch_stats<VEC>(a, t, s);
+    if (e != cudaSuccess) return e;
+    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
+    if (VEC == 4 && a.bits)
+        return launch(bn_apply_kernel<VEC, true>, grid, block, 0, s, true, a.x, a.residual, a.y, a.M, a.C, t.tx, t.rows_per_split,
+                      a.gamma, a.beta, a.relu, (const float*)a.save_mean, (const float*)a.save_invstd, a.bits);
+    return launch(bn_apply_kernel<VEC, false>, grid, block, 0, s, true, a.x, a.residual, a.y, a.M, a.C, t.tx, t.rows_per_split,
+                  a.gamma, a.beta, a.relu, (const float*)a.save_mean, (const float*)a.save_invstd, (unsigned char*)nullptr);
+}
+
+struct BwdArgs {
+    const float* dy; const float* dy2; const float* y; const unsigned char* bits; const float* x; float* dz; float* dx;
+    long long M; int C; const float* gamma; const float* beta; const float* save_mean; const float* save_invstd;
+    int mask1, mask2; float* dgamma; float* dbeta; float* partials; PoolArgs pool;
+};
+
+template <int VEC, bool POOL>
+cudaError_t launch_bwd(const BwdArgs& a, cudaStream_t s) {
+    const Tiling t = make_tiling(a.M, a.C, VEC, 2);      // backward kernels hold 2 blocks per SM
+    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
+    const BwdFinal fin = {a.dgamma, a.dbeta, take_slots(t.grid_x, t.grid_y)};
+    cudaError_t e = launch(bn_bwd_reduce_kernel<VEC, POOL>, grid, block, reduce_smem(VEC), s, false, a.dy, a.dy2, a.y, a.bits, a.x,
+                           a.dz, a.M, a.C, t.tx, t.rows_per_split, a.gamma, a.beta, a.save_mean, a.save_invstd, a.mask1, a.partials,
+                           a.pool, fin);
+    if (e == cudaSuccess && fin.slot0 < 0)
+        e = launch(bn_bwd_finalize_kernel, dim3((a.C + 31) / 32), dim3(32, 32), 0, s, true, (const float*)a.partials, t.grid_y, a.C,
+                   a.dgamma, a.dbeta);
+    if (e != cudaSuccess) return e;
+    const float* gsrc = a.dz != nullptr ? a.dz : a.dy;
+    const float* gsrc2 = a.dz != nullptr ? nullptr : a.dy2;        // dz already holds the sum of both gradients
+    return launch(bn_bwd_apply_kernel<VEC, POOL>, grid, block, 0, s, true, gsrc, gsrc2, a.y, a.x, a.dx, a.M, a.C, t.tx,
+                  t.rows_per_split, a.gamma, a.beta, a.save_mean, a.save_invstd, a.mask2, (const float*)a.dgamma,
+                  (const float*)a.dbeta, a.pool);
 }
 
 }  // namespace
@@ -601,7 +732,7 @@ size_t mgw_bn_partials_floats(long long M, int C) {
 // two when the finalize step rides in the reduction kernel, three otherwise.  (Reporting only.)
 int mgw_bn_launches(long long M, int C, int backward) {
     const Tiling t = make_tiling(M, C, (C % 4 == 0) ? 4 : 1, backward ? 2 : 4);
-    return (t.grid_y > kFuseMaxSplits || t.grid_x > kFuseMaxTiles) ? 3 : 2;
+    return fused_geometry(t.grid_x, t.grid_y) ? 2 : 3;
 }
 
 int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M, int C, const float* gamma, const float* beta,
@@ -610,31 +741,9 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
     if (x == nullptr || y == nullptr || M <= 0 || C <= 0 || save_mean == nullptr || save_invstd == nullptr || partials == nullptr)
         return MGW_ERR_ARG;
     if (relu_bits != nullptr && (C % 4 != 0 || !relu)) return MGW_ERR_ARG;
-    const int vec = (C % 4 == 0) ? 4 : 1;
-    const Tiling t = make_tiling(M, C, vec);
-    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
-    cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_red = reduce_smem(vec);
-    const dim3 fgrid((C + 31) / 32), fblock(32, 32);
-    const FwdFinal fin = {running_mean, running_var, num_batches_tracked, momentum, eps, save_mean, save_invstd,
-                          take_slots(t.grid_x, t.grid_y)};
-    if (vec == 4) {
-        bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials, fin);
-        if (fin.slot0 < 0)
-            bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
-                                                            momentum, eps, save_mean, save_invstd);
-        if (relu_bits)
-            bn_apply_kernel<4, true><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd, relu_bits);
-        else
-            bn_apply_kernel<4, false><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd, nullptr);
-    } else {
-        bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials, fin);
-        if (fin.slot0 < 0)
-            bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
-                                                            momentum, eps, save_mean, save_invstd);
-        bn_apply_kernel<1, false><<<grid, block, 0, s>>>(x, residual, y, M, C, t.tx, t.rows_per_split, gamma, beta, relu, save_mean, save_invstd, nullptr);
-    }
-    MGW_CUDA_CHECK(cudaGetLastError());
+    const FwdArgs a = {x, residual, y, M, C, gamma, beta, running_mean, running_var, num_batches_tracked, momentum, eps, relu,
+                       save_mean, save_invstd, partials, relu_bits};
+    MGW_CUDA_CHECK((C % 4 == 0) ? launch_fwd<4>(a, (cudaStream_t)stream) : launch_fwd<1>(a, (cudaStream_t)stream));
     return MGW_OK;
 }
 
@@ -653,28 +762,12 @@ int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const flo
     // the byte mask serves the reduce pass; the apply pass then reads the masked gradient dz, which must exist
     if (relu_bits != nullptr && (C % 4 != 0 || !relu || dz == nullptr)) return MGW_ERR_ARG;
     if (dgamma == nullptr || dbeta == nullptr || save_mean == nullptr || save_invstd == nullptr) return MGW_ERR_ARG;
-    const PoolArgs pool = {nullptr, nullptr, 0, 0, 0, 0};
     const int mask1 = !relu ? 0 : (relu_bits != nullptr ? 3 : (y != nullptr ? 1 : 2));          // mask used by the reduce pass
     const int mask2 = dz != nullptr ? 0 : mask1;                   // apply pass: dz already carries the mask
-    const float* gsrc = dz != nullptr ? dz : dy;
-    const float* gsrc2 = dz != nullptr ? nullptr : dy2;        // dz already holds the sum of both gradients
-    const int vec = (C % 4 == 0) ? 4 : 1;
-    const Tiling t = make_tiling(M, C, vec, 2);      // backward kernels hold 2 blocks per SM
-    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
-    cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_red = reduce_smem(vec);
-    const dim3 fgrid((C + 31) / 32), fblock(32, 32);
-    const BwdFinal fin = {dgamma, dbeta, take_slots(t.grid_x, t.grid_y)};
-    if (vec == 4) {
-        bn_bwd_reduce_kernel<4, false><<<grid, block, smem_red, s>>>(dy, dy2, y, relu_bits, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool, fin);
-        if (fin.slot0 < 0) bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
-    } else {
-        bn_bwd_reduce_kernel<1, false><<<grid, block, smem_red, s>>>(dy, dy2, y, relu_bits, x, dz, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask1, partials, pool, fin);
-        if (fin.slot0 < 0) bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1, false><<<grid, block, 0, s>>>(gsrc, gsrc2, y, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, mask2, dgamma, dbeta, pool);
-    }
-    MGW_CUDA_CHECK(cudaGetLastError());
+    const BwdArgs a = {dy, dy2, y, relu_bits, x, dz, dx, M, C, gamma, beta, save_mean, save_invstd, mask1, mask2, dgamma, dbeta,
+                       partials, {nullptr, nullptr, 0, 0, 0, 0}};
+    const cudaError_t e = (C % 4 == 0) ? launch_bwd<4, false>(a, (cudaStream_t)stream) : launch_bwd<1, false>(a, (cudaStream_t)stream);
+    MGW_CUDA_CHECK(e);
     return MGW_OK;
 }
 
@@ -689,28 +782,20 @@ int mgw_bn_relu_maxpool_fwd(const float* x, float* y_pool, unsigned char* idx, i
     const int OH = (H + 2 - 3) / 2 + 1, OW = (W + 2 - 3) / 2 + 1;
     const int vec = (C % 4 == 0) ? 4 : 1;
     const Tiling t = make_tiling(M, C, vec);
-    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_red = reduce_smem(vec);
-    const dim3 fgrid((C + 31) / 32), fblock(32, 32);
     const long long work = (long long)N * OH * OW * (C / vec);
     const int pgrid = (int)((work + 255) / 256 < 148LL * 16 ? (work + 255) / 256 : 148LL * 16);
-    const FwdFinal fin = {running_mean, running_var, num_batches_tracked, momentum, eps, save_mean, save_invstd,
-                          take_slots(t.grid_x, t.grid_y)};
+    const FwdArgs a = {x, nullptr, nullptr, M, C, gamma, beta, running_mean, running_var, num_batches_tracked, momentum, eps, 1,
+                       save_mean, save_invstd, partials, nullptr};
     if (vec == 4) {
-        bn_stats_kernel<4><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials, fin);
-        if (fin.slot0 < 0)
-            bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
-                                                            momentum, eps, save_mean, save_invstd);
-        bn_relu_maxpool_kernel<4><<<pgrid, 256, 0, s>>>(x, y_pool, idx, N, H, W, OH, OW, C, gamma, beta, save_mean, save_invstd);
+        MGW_CUDA_CHECK(launch_stats<4>(a, t, s));
+        MGW_CUDA_CHECK(launch(bn_relu_maxpool_kernel<4>, dim3(pgrid), dim3(256), 0, s, true, x, y_pool, idx, N, H, W, OH, OW, C, gamma,
+                              beta, (const float*)save_mean, (const float*)save_invstd));
     } else {
-        bn_stats_kernel<1><<<grid, block, smem_red, s>>>(x, M, C, t.tx, t.rows_per_split, partials, fin);
-        if (fin.slot0 < 0)
-            bn_fwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, M, C, running_mean, running_var, num_batches_tracked,
-                                                            momentum, eps, save_mean, save_invstd);
-        bn_relu_maxpool_kernel<1><<<pgrid, 256, 0, s>>>(x, y_pool, idx, N, H, W, OH, OW, C, gamma, beta, save_mean, save_invstd);
+        MGW_CUDA_CHECK(launch_stats<1>(a, t, s));
+        MGW_CUDA_CHECK(launch(bn_relu_maxpool_kernel<1>, dim3(pgrid), dim3(256), 0, s, true, x, y_pool, idx, N, H, W, OH, OW, C, gamma,
+                              beta, (const float*)save_mean, (const float*)save_invstd));
     }
-    MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
 }
 
@@ -722,24 +807,10 @@ int mgw_bn_relu_maxpool_bwd(const float* dp, const unsigned char* idx, const flo
     if (dp == nullptr || idx == nullptr || x == nullptr || dx == nullptr || partials == nullptr || dgamma == nullptr || dbeta == nullptr)
         return MGW_ERR_ARG;
     const long long M = (long long)N * H * W;
-    const PoolArgs pool = {dp, idx, H, W, (H + 2 - 3) / 2 + 1, (W + 2 - 3) / 2 + 1};
-    const int vec = (C % 4 == 0) ? 4 : 1;
-    const Tiling t = make_tiling(M, C, vec, 2);      // backward kernels hold 2 blocks per SM
-    const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
-    cudaStream_t s = (cudaStream_t)stream;
-    const size_t smem_red = reduce_smem(vec);
-    const dim3 fgrid((C + 31) / 32), fblock(32, 32);
-    const BwdFinal fin = {dgamma, dbeta, take_slots(t.grid_x, t.grid_y)};
-    if (vec == 4) {
-        bn_bwd_reduce_kernel<4, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool, fin);
-        if (fin.slot0 < 0) bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<4, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
-    } else {
-        bn_bwd_reduce_kernel<1, true><<<grid, block, smem_red, s>>>(nullptr, nullptr, nullptr, nullptr, x, nullptr, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, partials, pool, fin);
-        if (fin.slot0 < 0) bn_bwd_finalize_kernel<<<fgrid, fblock, 0, s>>>(partials, t.grid_y, C, dgamma, dbeta);
-        bn_bwd_apply_kernel<1, true><<<grid, block, 0, s>>>(nullptr, nullptr, nullptr, x, dx, M, C, t.tx, t.rows_per_split, gamma, beta, save_mean, save_invstd, 2, dgamma, dbeta, pool);
-    }
-    MGW_CUDA_CHECK(cudaGetLastError());
+    const BwdArgs a = {nullptr, nullptr, nullptr, nullptr, x, nullptr, dx, M, C, gamma, beta, save_mean, save_invstd, 2, 2, dgamma,
+                       dbeta, partials, {dp, idx, H, W, (H + 2 - 3) / 2 + 1, (W + 2 - 3) / 2 + 1}};
+    const cudaError_t e = (C % 4 == 0) ? launch_bwd<4, true>(a, (cudaStream_t)stream) : launch_bwd<1, true>(a, (cudaStream_t)stream);
+    MGW_CUDA_CHECK(e);
     return MGW_OK;
 }
 

@@ -9,7 +9,8 @@ measured roofline (``MEASURED_PEAKS.json`` at the repository root when present).
     python -m mgwfbp_b200.ops.microbench fused                            # all of ResNet-50 as one group: all-reduce + SGD
 
 Timing: CUDA events on the launching stream, ``--warmup`` untimed launches, a write larger than L2
-between timed launches, median of ``--iters``.  The same commands (with ``--iters 1 --warmup 1``)
+between timed launches, median of ``--iters``; the last line printed is the SM clock / throttle-reason
+record sampled while the timings ran.  The same commands (with ``--iters 1 --warmup 1``)
 are what the profiles under ``profiles/`` were captured from.
 """
 from __future__ import annotations
@@ -192,6 +193,16 @@ def main(argv=None):
     args = ap.parse_args(argv)
     _lib.load(allow_build=False)
     timer = Timer(args.warmup, args.iters)
+    from ..utils.clocks import ClockSampler
+    sampler = ClockSampler(torch.cuda.current_device()).start()
+    try:
+        _run(args, timer)
+    finally:
+        # the SM clock seen while the kernels above were timed (median of the samples under load), read-only
+        print(json.dumps({'clocks': sampler.stop()}))
+
+
+def _run(args, timer):
     {'bn': bench_bn, 'sgd': bench_sgd, 'wgrad': bench_wgrad, 'pack': bench_pack, 'fused': bench_fused}[args.what](args, timer)
 
 

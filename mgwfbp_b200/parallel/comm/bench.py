@@ -77,6 +77,8 @@ def main(argv=None):
     ap.add_argument('--iters', type=int, default=20)
     ap.add_argument('--eager', action='store_true', help='time host-launched calls instead of a graph replay')
     ap.add_argument('--out', default=None, help='also write the JSON document to this file')
+    ap.add_argument('--ctas', type=int, default=0,
+                    help='also time the large-message kernels capped at this many CTAs (what a group that overlaps backward gets)')
     args = ap.parse_args(argv)
     timeit = _time if args.eager else _time_graph
     runtime.init()
@@ -87,6 +89,8 @@ def main(argv=None):
     sizes = [1 << k for k in range(8, 31) if (1 << k) * 4 <= args.max_mb * 1e6]       # floats
     rows, samples = [], {}
     algos = ['oneshot', 'twoshot'] + (['nvls'] if comm.nvls_available else [])
+    from ...utils.clocks import ClockSampler
+    sampler = ClockSampler(torch.cuda.current_device()).start() if rank == 0 else None
     for n in sizes:
         x = torch.randn(n, device='cuda')
         row = {'bytes': 4 * n}
@@ -98,12 +102,16 @@ def main(argv=None):
             samples.setdefault(algo, ([], []))
             samples[algo][0].append(n)
             samples[algo][1].append(ms * 1e-3)
+            if args.ctas > 0 and algo != 'oneshot' and 4 * n > comm.oneshot_max_bytes:
+                cap = min(args.ctas, comm.choose((n + 3) // 4)[1])
+                ms = timeit(lambda: comm.synchronize(comm.allreduce_async_(x, algo=algo, n_ctas=cap)), args.iters, runtime.barrier)
+                row['%s@%d_us' % (algo, args.ctas)] = ms * 1e3
         ms = timeit(lambda: dist.all_reduce(x, op=dist.ReduceOp.AVG), args.iters, runtime.barrier)
         row['nccl_us'] = ms * 1e3
         samples.setdefault('nccl', ([], []))
         samples['nccl'][0].append(n)
         samples['nccl'][1].append(ms * 1e-3)
-        best = min(v for k, v in row.items() if k.endswith('_us') and k != 'nccl_us')
+        best = min(v for k, v in row.items() if k.endswith('_us') and k != 'nccl_us' and '@' not in k)
         row['best_busbw_GBps'] = 2 * (world - 1) / world * 4 * n / (best * 1e-6) / 1e9
         row['nccl_busbw_GBps'] = 2 * (world - 1) / world * 4 * n / (row['nccl_us'] * 1e-6) / 1e9
         rows.append(row)
@@ -115,8 +123,9 @@ def main(argv=None):
             fits[algo] = {'alpha_us': ab.alpha * 1e6, 'beta_s_per_byte': ab.beta,
                           'asymptotic_algbw_GBps': (1e-9 / ab.beta) if ab.beta > 0 else None}
     if rank == 0:
-        doc = json.dumps({'world': world, 'heap': os.environ.get('MGWFBP_HEAP', 'ipc'), 'timing': 'eager' if args.eager else 'graph',
-                          'twoshot_ctas': comm.max_ctas_twoshot, 'threads': comm.n_threads, 'rows': rows, 'fits': fits})
+        doc = json.dumps({'world': world, 'heap': comm.arena.heaps[0].kind, 'multicast': comm.nvls_available,
+                          'timing': 'eager' if args.eager else 'graph', 'twoshot_ctas': comm.max_ctas_twoshot,
+                          'threads': comm.n_threads, 'rows': rows, 'fits': fits, 'clocks': sampler.stop()})
         print(doc)
         if args.out:
             with open(args.out, 'w') as f:

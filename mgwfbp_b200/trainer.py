@@ -655,7 +655,7 @@ def train_with_single(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_u
     trainer.update_optimizer(DistributedOptimizer(trainer.optimizer, named_parameters=trainer.net.named_parameters()))
     # one micro-step per update: the graph-captured step with input prefetch; otherwise the accumulation loop
     from .engine import TrainStep
-    step = TrainStep(trainer, use_graph=use_graph) if nsteps_update == 1 else None
+    step = TrainStep(trainer, use_graph=use_graph, track_accuracy=True) if nsteps_update == 1 else None
     upcoming = trainer.data_iter() if step is not None else None
     display = 40 if iters_per_epoch > 40 else max(iters_per_epoch - 1, 1)
     done, counted, since = 0, 0, time.time()

@@ -285,65 +285,74 @@ bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int row
     }
 }
 
-// Sum the per-split partials of 32 channels per block (32-way split over the partial rows, combined
-// in double in a fixed order).  out_a / out_b receive the two totals of every channel.
-__device__ __forceinline__ void finalize_sums(const float* __restrict__ partials, int n_splits, int C, double& a, double& b,
-                                              double (*sm)[32][32]) {
-    const int c = blockIdx.x * 32 + threadIdx.x;
+// Sum the per-split partials of kFinCh channels per block: 128 lanes walk the partial rows (a few loads each), then two
+// short shared-memory stages combine them in double, always in the same order.  Many small blocks instead of a few
+// large ones: the kernel is pure latency (a handful of dependent loads), so what counts is how few of them are
+// chained and how many SMs take part.  Valid in threads with lane == 0: totals of channel c.
+constexpr int kFinCh = 8, kFinLanes = 128;
+
+__device__ __forceinline__ void finalize_sums(const float* __restrict__ partials, int n_splits, int C, double& a, double& b, int& c,
+                                              double (*sm)[kFinLanes][kFinCh], double (*sm2)[8][kFinCh]) {
+    const int ch = threadIdx.x % kFinCh, lane = threadIdx.x / kFinCh;
+    c = blockIdx.x * kFinCh + ch;
     double ra = 0.0, rb = 0.0;
     if (c < C) {
-        for (int s = threadIdx.y; s < n_splits; s += 32) {
+        for (int s = lane; s < n_splits; s += kFinLanes) {
             const float* ps = partials + (size_t)s * 2 * C;
             ra += (double)ps[c];
             rb += (double)ps[C + c];
         }
     }
-    sm[0][threadIdx.y][threadIdx.x] = ra;
-    sm[1][threadIdx.y][threadIdx.x] = rb;
+    sm[0][lane][ch] = ra;
+    sm[1][lane][ch] = rb;
+    __syncthreads();
+    if (lane < 8) {
+        ra = rb = 0.0;
+        for (int r = lane; r < kFinLanes; r += 8) {
+            ra += sm[0][r][ch];
+            rb += sm[1][r][ch];
+        }
+        sm2[0][lane][ch] = ra;
+        sm2[1][lane][ch] = rb;
+    }
     __syncthreads();
     a = b = 0.0;
-    if (threadIdx.y == 0) {
-        for (int r = 0; r < 32; ++r) {
-            a += sm[0][r][threadIdx.x];
-            b += sm[1][r][threadIdx.x];
+    if (lane == 0) {
+        for (int r = 0; r < 8; ++r) {
+            a += sm2[0][r][ch];
+            b += sm2[1][r][ch];
         }
     }
 }
 
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(kFinCh * kFinLanes)
 bn_fwd_finalize_kernel(const float* __restrict__ partials, int n_splits, long long M, int C, float* running_mean, float* running_var,
                        long long* num_batches_tracked, float momentum, float eps, float* __restrict__ save_mean,
                        float* __restrict__ save_invstd) {
-    __shared__ double sm[2][32][32];
+    __shared__ double sm[2][kFinLanes][kFinCh];
+    __shared__ double sm2[2][8][kFinCh];
     pdl_release_dependents();
     pdl_wait();
     double sum, sq;
-    finalize_sums(partials, n_splits, C, sum, sq, sm);
-    const int c = blockIdx.x * 32 + threadIdx.x;
-    if (threadIdx.y == 0 && c < C) {
-        const double mean = sum / (double)M;
-        double var = sq / (double)M - mean * mean;
-        if (var < 0.0) var = 0.0;
-        save_mean[c] = (float)mean;
-        save_invstd[c] = (float)(1.0 / sqrt(var + (double)eps));
-        if (running_mean) {
-            const double unbiased = M > 1 ? var * (double)M / (double)(M - 1) : var;
-            running_mean[c] = (1.f - momentum) * running_mean[c] + momentum * (float)mean;
-            running_var[c] = (1.f - momentum) * running_var[c] + momentum * (float)unbiased;
-        }
+    int c;
+    finalize_sums(partials, n_splits, C, sum, sq, c, sm, sm2);
+    if (threadIdx.x < kFinCh && c < C) {
+        const FwdFinal f = {running_mean, running_var, num_batches_tracked, momentum, eps, save_mean, save_invstd, -1};
+        fwd_finalize_channel(sum, sq, M, c, f);
     }
-    if (blockIdx.x == 0 && threadIdx.x == 0 && threadIdx.y == 0 && num_batches_tracked) *num_batches_tracked += 1;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && num_batches_tracked) *num_batches_tracked += 1;
 }
 
-__global__ void __launch_bounds__(1024)
+__global__ void __launch_bounds__(kFinCh * kFinLanes)
 bn_bwd_finalize_kernel(const float* __restrict__ partials, int n_splits, int C, float* __restrict__ dgamma, float* __restrict__ dbeta) {
-    __shared__ double sm[2][32][32];
+    __shared__ double sm[2][kFinLanes][kFinCh];
+    __shared__ double sm2[2][8][kFinCh];
     pdl_release_dependents();
     pdl_wait();
     double a, b;
-    finalize_sums(partials, n_splits, C, a, b, sm);
-    const int c = blockIdx.x * 32 + threadIdx.x;
-    if (threadIdx.y == 0 && c < C) {
+    int c;
+    finalize_sums(partials, n_splits, C, a, b, c, sm, sm2);
+    if (threadIdx.x < kFinCh && c < C) {
         dbeta[c] = (float)a;
         dgamma[c] = (float)b;
     }
@@ -639,7 +648,7 @@ bn_relu_maxpool_kernel(const float* __restrict__ x, float* __restrict__ yp, unsi
 }
 
 bool fuse_enabled() {
-    static const bool fuse = env_on("MGWFBP_BN_FUSE_FINALIZE", true);
+    static const bool fuse = env_on("MGWFBP_BN_FUSE_FINALIZE", false);
     return fuse;
 }
 
@@ -675,7 +684,7 @@ cudaError_t launch_stats(const FwdArgs& a, const Tiling& t, cudaStream_t s) {
     cudaError_t e = launch(bn_stats_kernel<VEC>, grid, block, reduce_smem(VEC), s, false, a.x, a.M, a.C, t.tx, t.rows_per_split,
                            a.partials, fin);
     if (e == cudaSuccess && fin.slot0 < 0)
-        e = launch(bn_fwd_finalize_kernel, dim3((a.C + 31) / 32), dim3(32, 32), 0, s, true, (const float*)a.partials, t.grid_y, a.M,
+        e = launch(bn_fwd_finalize_kernel, dim3((a.C + kFinCh - 1) / kFinCh), dim3(kFinCh * kFinLanes), 0, s, true, (const float*)a.partials, t.grid_y, a.M,
                    a.C, a.running_mean, a.running_var, a.nbt, a.momentum, a.eps, a.save_mean, a.save_invstd);
     return e;
 }
@@ -708,7 +717,7 @@ cudaError_t launch_bwd(const BwdArgs& a, cudaStream_t s) {
                            a.dz, a.M, a.C, t.tx, t.rows_per_split, a.gamma, a.beta, a.save_mean, a.save_invstd, a.mask1, a.partials,
                            a.pool, fin);
     if (e == cudaSuccess && fin.slot0 < 0)
-        e = launch(bn_bwd_finalize_kernel, dim3((a.C + 31) / 32), dim3(32, 32), 0, s, true, (const float*)a.partials, t.grid_y, a.C,
+        e = launch(bn_bwd_finalize_kernel, dim3((a.C + kFinCh - 1) / kFinCh), dim3(kFinCh * kFinLanes), 0, s, true, (const float*)a.partials, t.grid_y, a.C,
                    a.dgamma, a.dbeta);
     if (e != cudaSuccess) return e;
     const float* gsrc = a.dz != nullptr ? a.dz : a.dy;

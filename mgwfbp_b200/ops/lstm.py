@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import ctypes as C
 import math
+import os
 from typing import List, Optional, Tuple
 
 import torch
@@ -29,13 +30,45 @@ _declared = False
 def _declare(lib) -> None:
     global _declared
     if not _declared:
-        lib.mgw_lstm_cell_fwd.argtypes = [C.c_void_p] * 8 + [C.c_int, C.c_int, C.c_void_p]
-        lib.mgw_lstm_cell_bwd.argtypes = [C.c_void_p] * 7 + [C.c_int, C.c_int, C.c_void_p]
+        lib.mgw_lstm_cell_fwd.argtypes = [C.c_void_p] * 8 + [C.c_int, C.c_int, C.c_int, C.c_longlong, C.c_void_p]
+        lib.mgw_lstm_cell_bwd.argtypes = [C.c_void_p] * 7 + [C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_longlong, C.c_void_p]
+        lib.mgw_lstm_rec_splits.argtypes = [C.c_int]
+        lib.mgw_lstm_rec_supported.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+        lib.mgw_lstm_rec_gemm.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         _declared = True
 
 
 def _ptr(t):
     return None if t is None else t.data_ptr()
+
+
+# MGWFBP_LSTM_REC=0 sends the per-step recurrent products through torch.mm (cuBLAS) instead of csrc/lstm_rec.cu
+_OWN_REC = os.environ.get('MGWFBP_LSTM_REC', '1').strip().lower() not in ('0', 'false', 'no', 'off', '')
+
+
+class _Recurrent:
+    """``x [B, K] @ w [R, K]^T`` for one time step, as split-K partial sums that the cell kernels add up.
+
+    Uses the package's small-batch kernel when it handles the shape, ``torch.mm`` otherwise (one "partial")."""
+
+    def __init__(self, lib, w: torch.Tensor, B: int):
+        self.lib, self.w = lib, w
+        self.R, self.K = w.shape
+        # the kernel multiplies in TF32 (fp32 accumulation), so it only stands in for torch.mm where TF32 matmuls are
+        # allowed; with full-precision matmuls requested the library product is used
+        self.own = bool(_OWN_REC and torch.backends.cuda.matmul.allow_tf32 and w.is_contiguous() and
+                        lib.mgw_lstm_rec_supported(w.data_ptr(), w.data_ptr(), B, self.R, self.K))
+        self.parts = int(lib.mgw_lstm_rec_splits(self.K)) if self.own else 1
+        self.out = torch.empty(self.parts, B, self.R, device=w.device, dtype=w.dtype)
+        self.stride = B * self.R
+        self.w_t = None if self.own else w.t()
+
+    def __call__(self, x: torch.Tensor, stream: int) -> None:
+        if self.own:
+            _lib.check(self.lib.mgw_lstm_rec_gemm(x.data_ptr(), self.w.data_ptr(), self.out.data_ptr(), x.shape[0], self.R, self.K,
+                                                  stream), 'lstm_rec_gemm')
+        else:
+            torch.mm(x, self.w_t, out=self.out[0])
 
 
 class _LSTMLayer(torch.autograd.Function):
@@ -53,17 +86,18 @@ class _LSTMLayer(torch.autograd.Function):
         out = torch.empty(T, B, H, device=x.device, dtype=x.dtype)
         cs = torch.empty(T + 1, B, H, device=x.device, dtype=x.dtype)
         act = torch.empty(T, B, 4 * H, device=x.device, dtype=x.dtype)
-        gh = torch.empty(B, 4 * H, device=x.device, dtype=x.dtype)
         cs[0].copy_(c0)
         h = h0.contiguous()
-        w_hh_t = w_hh.t()
+        rec = _Recurrent(lib, w_hh.detach(), B)               # h_{t-1} W_hh^T, W_hh [4H, H] rows are the gates
         for t in range(T):
-            torch.mm(h, w_hh_t, out=gh)
-            _lib.check(lib.mgw_lstm_cell_fwd(gx[t * B:(t + 1) * B].data_ptr(), gh.data_ptr(), _ptr(b_ih), _ptr(b_hh),
+            rec(h, s)
+            _lib.check(lib.mgw_lstm_cell_fwd(gx[t * B:(t + 1) * B].data_ptr(), rec.out.data_ptr(), _ptr(b_ih), _ptr(b_hh),
                                              cs[t].data_ptr(), out[t].data_ptr(), cs[t + 1].data_ptr(), act[t].data_ptr(),
-                                             B, H, s), 'lstm_cell_fwd')
+                                             B, H, rec.parts, rec.stride, s), 'lstm_cell_fwd')
             h = out[t]
         counters.bump('lstm_cell_fwd', T)
+        if rec.own:
+            counters.bump('lstm_rec_gemm', T)
         ctx.save_for_backward(x, h0, w_ih, w_hh, out, cs, act)
         ctx.has_bias = b_ih is not None
         return out, out[T - 1].clone(), cs[T].clone()
@@ -75,27 +109,49 @@ class _LSTMLayer(torch.autograd.Function):
         T, B, H = out.shape
         s = torch.cuda.current_stream().cuda_stream
         dG = torch.empty(T, B, 4 * H, device=x.device, dtype=x.dtype)
-        dh = torch.zeros(B, H, device=x.device, dtype=x.dtype) if d_hT is None else d_hT.contiguous().clone()
         dc = torch.zeros(B, H, device=x.device, dtype=x.dtype) if d_cT is None else d_cT.contiguous().clone()
         dc_next = torch.empty_like(dc)
         d_out = d_out.contiguous() if d_out is not None else None
+        # dh_{t-1} through the recurrence is dG_t W_hh: rows of W_hh^T [H, 4H] are the hidden units
+        rec = _Recurrent(lib, w_hh.detach().t().contiguous(), B)
+        if d_hT is not None:                                  # gradient of the final state enters like a recurrent term
+            rec.out.zero_()
+            rec.out[0].copy_(d_hT)
+            parts = rec.parts
+        else:
+            parts = 0
         for t in range(T - 1, -1, -1):
-            if d_out is not None:
-                dh.add_(d_out[t])
-            _lib.check(lib.mgw_lstm_cell_bwd(dh.data_ptr(), dc.data_ptr(), act[t].data_ptr(), cs[t].data_ptr(),
-                                             cs[t + 1].data_ptr(), dG[t].data_ptr(), dc_next.data_ptr(), B, H, s),
-                       'lstm_cell_bwd')
+            _lib.check(lib.mgw_lstm_cell_bwd(_ptr(d_out[t]) if d_out is not None else None, dc.data_ptr(), act[t].data_ptr(),
+                                             cs[t].data_ptr(), cs[t + 1].data_ptr(), dG[t].data_ptr(), dc_next.data_ptr(), B, H,
+                                             rec.out.data_ptr(), parts, rec.stride, s), 'lstm_cell_bwd')
             dc, dc_next = dc_next, dc
-            torch.mm(dG[t], w_hh, out=dh)                     # dh_{t-1}
+            rec(dG[t], s)                                     # partial sums of dh_{t-1}
+            parts = rec.parts
         counters.bump('lstm_cell_bwd', T)
+        if rec.own:
+            counters.bump('lstm_rec_gemm', T)
+        dh0 = rec.out.sum(0) if ctx.needs_input_grad[1] else None
         dG2 = dG.reshape(T * B, 4 * H)
         h_prev = torch.cat([h0.unsqueeze(0), out[:-1]], 0).reshape(T * B, H)
         need = ctx.needs_input_grad
         dx = (dG2 @ w_ih).reshape(x.shape) if need[0] else None
-        dw_ih = dG2.t() @ x.reshape(T * B, -1) if need[3] else None
-        dw_hh = dG2.t() @ h_prev if need[4] else None
+        dw_ih = _weight_grad(dG2, x.reshape(T * B, -1)) if need[3] else None
+        dw_hh = _weight_grad(dG2, h_prev) if need[4] else None
         db = dG2.sum(0) if ctx.has_bias else None
-        return dx, dh if need[1] else None, dc if need[2] else None, dw_ih, dw_hh, db, (db.clone() if db is not None else None)
+        return dx, dh0, dc if need[2] else None, dw_ih, dw_hh, db, (db.clone() if db is not None else None)
+
+
+# MGWFBP_LSTM_WGRAD=tcgen05 forms dW_ih / dW_hh with the package's tensor-core weight-gradient GEMM (csrc/wgrad_gemm_sm100.cu)
+_WGRAD = os.environ.get('MGWFBP_LSTM_WGRAD', 'library').strip().lower()
+
+
+def _weight_grad(dg: torch.Tensor, inp: torch.Tensor) -> torch.Tensor:
+    """``dg^T @ inp`` ([T*B, 4H]^T x [T*B, in]): the weight gradient of a whole sequence as one GEMM."""
+    if _WGRAD == 'tcgen05':
+        from . import wgrad
+        if wgrad.supported(dg, inp):
+            return wgrad.wgrad_gemm(dg, inp)
+    return dg.t() @ inp
 
 
 class FusedLSTM(nn.Module):

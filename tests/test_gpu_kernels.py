@@ -160,10 +160,22 @@ def test_bounded_wait_reports_timeout_without_hanging(lib):
 
 # ----------------------------------------------------------------------------- BatchNorm + ReLU
 def _bn_reference(x, w, b, rm, rv, residual, relu, momentum, eps):
-    y = torch.nn.functional.batch_norm(x, rm, rv, w, b, True, momentum, eps)
+    """Training-mode batch norm (+ residual) (+ ReLU) written out in plain PyTorch operations, evaluated in float64.
+    (The library batch norm is not used as the oracle: on the large layers its statistics differ from the exact ones
+    by enough to flip the sign of an output that is almost zero, and one flipped ReLU changes a whole channel's
+    gamma / beta gradients beyond any sensible tolerance.)"""
+    dims = (0,) if x.dim() == 2 else (0, 2, 3)
+    shape = (1, -1) + (1,) * (x.dim() - 2)
+    xd = x.double()
+    mean, var = xd.mean(dims), xd.var(dims, unbiased=False)
+    n = x.numel() // x.shape[1]
+    with torch.no_grad():
+        rm.mul_(1 - momentum).add_(momentum * mean.float())
+        rv.mul_(1 - momentum).add_(momentum * (var * n / max(n - 1, 1)).float())
+    y = (xd - mean.view(shape)) / torch.sqrt(var.view(shape) + eps) * w.double().view(shape) + b.double().view(shape)
     if residual is not None:
-        y = y + residual
-    return torch.relu(y) if relu else y
+        y = y + residual.double()
+    return (torch.relu(y) if relu else y).float()
 
 
 # small shapes take the one-launch cluster kernels (up to 8 register rows per thread), the others the
@@ -277,6 +289,68 @@ def test_fused_lstm_matches_cudnn_lstm():
     torch.testing.assert_close(x2.grad, x1.grad, rtol=1e-3, atol=1e-4)
     for (n, p1), p2 in zip(ref.named_parameters(), mine.parameters()):
         torch.testing.assert_close(p2.grad, p1.grad, rtol=1e-3, atol=1e-4, msg=lambda m: '%s: %s' % (n, m))
+
+
+def _tf32(t):
+    return (t.view(torch.int32) & ~0x1FFF).view(torch.float32)
+
+
+@pytest.mark.parametrize('B,R,K', [(20, 6000, 1500), (20, 1500, 6000), (5, 256, 64), (64, 100, 388), (1, 16, 4), (33, 70, 1000)])
+def test_lstm_recurrent_gemm_matches_fp32_product(B, R, K):
+    """The small-batch recurrent product: split-K partial sums of x W^T with TF32 operands, fp32 accumulation."""
+    from mgwfbp_b200.ops import _lib
+    from mgwfbp_b200.ops import lstm as lstm_ops
+    lib = _lib.load(allow_build=False)
+    lstm_ops._declare(lib)
+    torch.manual_seed(0)
+    x, w = torch.randn(B, K, device='cuda'), torch.randn(R, K, device='cuda') / K ** 0.5
+    assert lib.mgw_lstm_rec_supported(x.data_ptr(), w.data_ptr(), B, R, K)
+    parts = lib.mgw_lstm_rec_splits(K)
+    assert parts == (K + 383) // 384
+    out = torch.full((parts, B, R), float('nan'), device='cuda')
+    _lib.check(lib.mgw_lstm_rec_gemm(x.data_ptr(), w.data_ptr(), out.data_ptr(), B, R, K, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    got = out.sum(0)
+    want = (x.double() @ w.double().t()).float()
+    # operands are rounded to TF32 (10 mantissa bits): about 1e-3 relative per product, averaging out over K
+    torch.testing.assert_close(got, want, rtol=5e-3, atol=5e-3)
+    for p in range(parts):                                   # every partial is the product over its own K-range
+        k0, k1 = p * 384, min(K, (p + 1) * 384)
+        part = (x[:, k0:k1].double() @ w[:, k0:k1].double().t()).float()
+        torch.testing.assert_close(out[p], part, rtol=5e-3, atol=5e-3)
+
+
+def test_fused_lstm_with_own_recurrent_kernel_tracks_library_lstm():
+    """TF32 allowed on both sides: the package's recurrent kernel is on the path (launch counter) and the layer stays
+    within TF32 accuracy of torch.nn.LSTM, forward and backward, with the PTB model's awkward sizes."""
+    from mgwfbp_b200.ops import counters
+    from mgwfbp_b200.ops.lstm import FusedLSTM
+    torch.manual_seed(0)
+    T, B, I, H = 6, 20, 100, 300
+    ref = torch.nn.LSTM(I, H, 2).cuda()
+    mine = FusedLSTM(I, H, 2).cuda()
+    mine.load_state_dict(ref.state_dict())
+    x = torch.randn(T, B, I, device='cuda')
+    hx = (torch.randn(2, B, H, device='cuda'), torch.randn(2, B, H, device='cuda'))
+    x1, x2 = x.clone().requires_grad_(True), x.clone().requires_grad_(True)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    counters.reset()
+    try:
+        y1, (h1, c1) = ref(x1, hx)
+        y2, (h2, c2) = mine(x2, hx)
+        w = torch.randn_like(y1)
+        (y1 * w).sum().backward()
+        (y2 * w).sum().backward()
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    assert counters.snapshot().get('lstm_rec_gemm', 0) == 2 * 2 * T          # two layers, forward and backward
+    torch.testing.assert_close(y2, y1, rtol=2e-2, atol=5e-3)
+    torch.testing.assert_close(c2, c1, rtol=2e-2, atol=5e-3)
+    torch.testing.assert_close(x2.grad, x1.grad, rtol=5e-2, atol=2e-2)
+    for (n, p1), p2 in zip(ref.named_parameters(), mine.parameters()):
+        rel = float((p2.grad - p1.grad).norm() / p1.grad.norm())
+        assert rel < 2e-2, '%s: relative gradient error %.4f' % (n, rel)
 
 
 def test_bn_relu_dual_output_sums_both_gradients():

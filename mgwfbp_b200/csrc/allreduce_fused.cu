@@ -23,6 +23,8 @@
 //              barrier, every rank consumes its (now averaged) local buffer.  2*(N-1)/N*S bytes.
 //   NVLS     : as two-shot, but the pull is one multimem.ld_reduce (the switch adds the N copies)
 //              and the push one multimem.st on the multicast address of the staging buffer.
+// With mode == 0 the two-shot / NVLS kernels stop after the second barrier: the averaged gradient is then
+// complete in every rank's staging area, in the group's padded vector layout, for a later kernel to consume.
 // Every rank applies the same arithmetic to the same reduced values, so replicas stay bit-identical.
 //
 // Every wait is bounded: after `timeout_ns` the CTA records (code, peer, expected, observed, cta) in
@@ -186,7 +188,9 @@ __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduc
             const uint32_t ep = e + (uint32_t)piece;
             const int p0 = min(c1, c0 + piece * plen);
             const int p1 = min(c1, p0 + plen);
-            for (int v0 = p0 + warp * 32 * U + lane; v0 < p1; v0 += nthr * U) {
+            // skip_pack: copy-engine transfers queued ahead of this kernel already put the gradients into `local`
+            // (same padded layout; the pad lanes of a tensor's last slot are never consumed)
+            for (int v0 = p0 + warp * 32 * U + lane; v0 < p1 && !a.skip_pack; v0 += nthr * U) {
                 float4 x[U];
                 mgw_load_grad_batch<U>(g, v0, 32, p1, cur, 1.f, x);
 #pragma unroll
@@ -244,7 +248,9 @@ __global__ void __launch_bounds__(512, 1) mgw_allreduce_kernel(const MgwAllreduc
             ok = rank_barrier(a, 1, ep, &sm);
             if (piece == 0) MGW_PHASE_END(3);
             if (!ok) break;
-            for (int v0 = p0 + warp * 32 * U + lane; v0 < p1; v0 += nthr * U) {
+            // mode 0: the averaged gradient stays in the staging area and whoever launched the kernel reads it there
+            // (the deferred update: one full-width SGD kernel after backward instead of an update inside every group)
+            for (int v0 = p0 + warp * 32 * U + lane; v0 < p1 && a.mode != 0; v0 += nthr * U) {
                 float4 x[U];
 #pragma unroll
                 for (int k = 0; k < U; ++k)
@@ -316,6 +322,7 @@ extern "C" int mgw_allreduce_group(const MgwAllreduceArgs* args, void* stream) {
     if (a.algo == MGW_ALGO_ONESHOT && a.inbox_stride < a.group.n_vec) return MGW_ERR_TOO_LARGE;
     if (a.algo != MGW_ALGO_ONESHOT && a.stage_slots < a.group.n_vec) return MGW_ERR_TOO_LARGE;
     if (a.algo != MGW_ALGO_ONESHOT && (a.max_pieces < 1 || a.piece_slots < 1)) return MGW_ERR_ARG;
+    if (a.skip_pack && a.algo == MGW_ALGO_ONESHOT) return MGW_ERR_ARG;
     if (!(a.grad_scale > 0.f)) return MGW_ERR_ARG;
     for (int r = 0; r < a.world; ++r)
         if (a.stage[r] == nullptr || a.flags[r] == nullptr) return MGW_ERR_ARG;

@@ -56,6 +56,7 @@ typedef struct {
     int max_pieces;                     // two-shot / NVLS: the chunk of a CTA is processed in at most this many pieces ...
     int piece_slots;                    // ... of at least this many float4 slots (1, anything: no pipelining)
     float grad_scale;                   // multiplies the summed gradient together with 1/world (1 / loss scale)
+    int skip_pack;                      // two-shot / NVLS: the staging area was already filled (device-to-device copies)
     unsigned long long timeout_ns;
 } MgwAllreduceArgs;
 

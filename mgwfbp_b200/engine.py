@@ -437,41 +437,47 @@ def fit_interference(trainer, comm=None, n_ctas: Optional[int] = None, message_b
     return out
 
 
-def tune_schedule(trainer, build_optimizer, interferences: Sequence[float], steps: int = 8, use_graph: bool = True):
-    """Pick the merge schedule by running it.
+def tune_schedule(trainer, build_optimizer, candidates: Sequence[dict], steps: int = 8, use_graph: bool = True):
+    """Pick the merge schedule (and where the update runs) by running the candidates.
 
-    ``build_optimizer(rho)`` must return a ``DistributedOptimizer`` around the SAME base optimizer, scheduled with
-    interference ``rho`` (0 reproduces the reference's MG-WFBP schedule, 1 collapses to one message).  Every distinct
-    schedule that results is trained for a few steps through :class:`TrainStep` (eager warm-up, graph capture,
-    ``steps`` timed replays on one device-resident batch; device time, max over ranks), and the fastest is rebuilt
-    and installed with ``trainer.update_optimizer``.  Collective.  Returns ``(optimizer, report)`` where ``report``
-    lists ``{'rho', 'groups', 'ms_per_step'}`` per candidate.  These are real training steps on real batches."""
+    ``build_optimizer(**candidate)`` must return a ``DistributedOptimizer`` around the SAME base optimizer; a candidate is
+    a dict such as ``{'rho': 0.17, 'update': 'deferred'}`` (interference for the scheduler: 0 reproduces the reference's
+    MG-WFBP schedule, 1 collapses to one message; update mode: see ``settings.UPDATE_MODE``).  Every distinct
+    (schedule, update mode) that results is trained for a few steps through :class:`TrainStep` (eager warm-up, graph
+    capture, ``steps`` timed replays on one device-resident batch; device time, max over ranks), and the fastest is
+    rebuilt and installed with ``trainer.update_optimizer``.  Collective.  Returns ``(optimizer, report)`` where
+    ``report`` lists the candidates with ``groups`` and ``ms_per_step``.  These are real training steps on real data."""
     batch = trainer.to_device(trainer.data_iter()) if trainer.is_cuda else trainer.data_iter()
     seen, report = {}, []
-    for rho in interferences:
-        opt = build_optimizer(rho)
-        digest = opt.merge_schedule.digest()
-        if digest in seen:
+    for cand in candidates:
+        opt = build_optimizer(**cand)
+        key = (opt.merge_schedule.digest(), getattr(opt, '_update_mode', ''))
+        row = dict(cand, groups=len(opt.merge_schedule.groups), update=getattr(opt, '_update_mode', None),
+                   group_mb=[round(4e-6 * n, 2) for n in opt.merge_schedule.group_sizes])
+        if key in seen:
             opt.close()
-            report.append({'rho': float(rho), 'groups': len(opt.merge_schedule.groups), 'ms_per_step': seen[digest], 'same_as_earlier': True})
+            report.append(dict(row, ms_per_step=seen[key], same_as_earlier=True))
             continue
         trainer.update_optimizer(opt)
         step = TrainStep(trainer, use_graph=use_graph)
         for _ in range(TrainStep.WARMUP_EAGER_STEPS + 2):
             step.run_on_device(batch)
         ms = _time_replays(step, batch, steps)
-        seen[digest] = ms
-        report.append({'rho': float(rho), 'groups': len(opt.merge_schedule.groups), 'ms_per_step': ms})
+        seen[key] = ms
+        report.append(dict(row, ms_per_step=ms))
         step.drain()
         del step
         opt.close()
-    best = min((r for r in report if not r.get('same_as_earlier')), key=lambda r: (r['ms_per_step'], r['groups']))
-    best_rho = runtime.broadcast_object(best['rho'], 0)
-    opt = build_optimizer(best_rho)
+    fresh = [r for r in report if not r.get('same_as_earlier')]
+    best = min(range(len(fresh)), key=lambda i: (fresh[i]['ms_per_step'], fresh[i]['groups']))
+    best = int(runtime.broadcast_object(best, 0))
+    chosen = {k: fresh[best][k] for k in candidates[0].keys()}
+    opt = build_optimizer(**chosen)
     trainer.update_optimizer(opt)
     if runtime.rank() == 0:
-        logger.info('schedule trial: %s -> rho %.3f (%d groups)', [(r['rho'], r['groups'], round(r['ms_per_step'], 3)) for r in report],
-                    best_rho, len(opt.merge_schedule.groups))
+        logger.info('schedule trial: %s -> %s (%d groups)',
+                    [(r.get('rho'), r.get('update'), r['groups'], round(r['ms_per_step'], 3)) for r in report], chosen,
+                    len(opt.merge_schedule.groups))
     return opt, report
 
 
@@ -509,14 +515,19 @@ def build_distributed_optimizer(trainer, seq_layernames=None, layerwise_times=No
     measured (``None`` entries where nothing was)."""
     from .parallel.broadcast import broadcast_parameters
     from .parallel.optimizer import DistributedOptimizer
+    from .parallel.scheduler import groups_time_sliced
     base = trainer.optimizer
     named = list(trainer.net.named_parameters())
     info = {'interference': None, 'trial': None, 'cost_model': None, 'cost_model_overlapped': None}
 
-    def build(rho=None, cost=None, cost_last=None):
+    def build(rho=None, cost=None, cost_last=None, update=None, slices=None):
+        schedule = None
+        if slices:
+            schedule = lambda n, s, t, _k=int(slices): groups_time_sliced(n, s, t, _k)      # noqa: E731
         return DistributedOptimizer(base, named_parameters=named, compression=compression, seq_layernames=seq_layernames,
                                     layerwise_times=layerwise_times, norm_clip=norm_clip, threshold=threshold, writer=writer,
-                                    gradient_path=gradient_path, cost_model=cost, cost_model_last=cost_last, interference=rho)
+                                    gradient_path=gradient_path, cost_model=cost, cost_model_last=cost_last, interference=rho,
+                                    fused_update=update, schedule=schedule)
 
     adaptive_fused = (runtime.size() > 1 and trainer.is_cuda and not settings.ORIGINAL_HOROVOD and settings.ADAPTIVE_MERGE
                       and layerwise_times is not None)
@@ -540,14 +551,22 @@ def build_distributed_optimizer(trainer, seq_layernames=None, layerwise_times=No
         info['interference'] = fit_interference(trainer, comm, cost_model=cost_ovl)
         rho = info['interference']['rho']
         rhos = []
-        for r in (rho, 0.5 * rho, min(1.0, 2.0 * rho), min(1.0, 4.0 * rho), 1.0):
+        for r in (rho, min(1.0, 2.0 * rho), 1.0):
             r = round(max(r, 1e-3), 4)
             if r not in rhos:
                 rhos.append(r)
-    mk = lambda r: build(r, cost_ovl, cost_full)      # noqa: E731
-    if tune and len(rhos) > 1:
-        opt, info['trial'] = tune_schedule(trainer, mk, rhos, steps=trial_steps, use_graph=use_graph)
+    mk = lambda rho, update, slices: build(rho, cost_ovl, cost_full, update, slices)      # noqa: E731
+    # plain SGD without clipping may run its update inside the group kernels or once after backward: try both
+    modes = ['fused', 'deferred'] if (norm_clip is None and settings.UPDATE_MODE == 'fused' and
+                                      isinstance(base, torch.optim.SGD)) else [None]
+    # schedules from the interference-aware MG-WFBP search, and time-sliced ones (messages ready at equal distances in
+    # backward time + a small last message) that the cost model cannot tell apart from them
+    candidates = [{'rho': r, 'update': m, 'slices': None} for m in modes for r in rhos]
+    if not settings.INTERFERENCE_PINNED:
+        candidates += [{'rho': None, 'update': m, 'slices': k} for m in modes for k in (3, 6)]
+    if tune and len(candidates) > 1:
+        opt, info['trial'] = tune_schedule(trainer, mk, candidates, steps=trial_steps, use_graph=use_graph)
     else:
-        opt = mk(rhos[0])
+        opt = mk(**candidates[0])
         trainer.update_optimizer(opt)
     return opt, info

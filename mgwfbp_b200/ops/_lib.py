@@ -40,7 +40,7 @@ class MgwAllreduceArgs(C.Structure):
                 ('algo', C.c_int), ('n_ctas', C.c_int), ('n_threads', C.c_int),
                 ('mode', C.c_int), ('first_step', C.c_int),
                 ('inbox_stride', C.c_int), ('stage_slots', C.c_int),
-                ('max_pieces', C.c_int), ('piece_slots', C.c_int), ('grad_scale', C.c_float),
+                ('max_pieces', C.c_int), ('piece_slots', C.c_int), ('grad_scale', C.c_float), ('skip_pack', C.c_int),
                 ('timeout_ns', C.c_ulonglong)]
 
 

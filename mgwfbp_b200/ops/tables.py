@@ -87,7 +87,12 @@ class GroupTable:
 
     def refresh_grads(self, grads: Sequence[torch.Tensor], stream: Optional[torch.cuda.Stream] = None) -> bool:
         """Point the table at this iteration's gradient tensors.  Returns True when a copy was issued."""
-        ptrs = [g.data_ptr() for g in grads]
+        return self.refresh_grad_ptrs([g.data_ptr() for g in grads], stream)
+
+    def refresh_grad_ptrs(self, ptrs: Sequence[int], stream: Optional[torch.cuda.Stream] = None) -> bool:
+        """As :meth:`refresh_grads` with raw device addresses (a gradient may live somewhere else than in ``p.grad``,
+        e.g. already averaged in a communication staging area)."""
+        ptrs = [int(p) for p in ptrs]
         if ptrs == self._grad_ptr_cache:
             return False
         capturing = torch.cuda.is_current_stream_capturing()

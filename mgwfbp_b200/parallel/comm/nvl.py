@@ -55,7 +55,8 @@ def _wrap_device_memory(ptr: int, n_floats: int, device: torch.device) -> torch.
 
 
 class _GroupPlan:
-    __slots__ = ('table', 'params', 'algo', 'n_ctas', 'stage_off', 'args', 'partials_off', 'block', 'overlapped')
+    __slots__ = ('table', 'params', 'algo', 'n_ctas', 'stage_off', 'args', 'partials_off', 'block', 'overlapped', 'mode',
+                 'copy_pack', 'stage_views')
 
 
 
@@ -80,6 +81,11 @@ class NvlComm(Communicator):
         self.overlap_ctas = max(1, min(_env_int('MGWFBP_OVERLAP_CTAS', 16), _lib.MAX_CTAS))
         # the switch-side reduction pays from this many ranks on (with two ranks a pull is as cheap as a multimem load)
         self.nvls_min_world = _env_int('MGWFBP_NVLS_MIN_WORLD', 4)
+        # How the gradients of a group that overlaps backward reach its staging area: 'kernel' = the kernel's own pack
+        # loop (default), 'copy' = one device-to-device copy per tensor queued in front of the kernel.  Measured on B200
+        # the copies lose: the driver serves the many small ones with copy kernels of 1.5-2 us each, one after the other,
+        # which pushes the group's kernel to the end of backward.  The schedule's last group always packs in the kernel.
+        self.pack_mode = os.environ.get('MGWFBP_PACK', 'kernel').strip().lower()
         self.n_threads = _env_int('MGWFBP_COMM_THREADS', 512)
         # two-shot / NVLS kernels work through a CTA's chunk in pieces (pack, reduce and update of successive pieces
         # of different CTAs overlap); large messages use narrower CTAs, two of which fit on an SM
@@ -262,14 +268,20 @@ class NvlComm(Communicator):
             stage_top += (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
             plan.partials_off = p_off
             plan.block = block
+            plan.overlapped = len(plans) < n_groups - 1
+            plan.copy_pack = bool(self.pack_mode == 'copy' and plan.overlapped and algo != _lib.ALGO_ONESHOT)
+            plan.stage_views = None
             self._fill_args(plan, block, hyper.data_ptr(), partials.data_ptr() + 4 * p_off)
             p_off += n_ctas
             plans.append(plan)
         self._plans[key] = plans
+        if any(pl.copy_pack for pl in plans):
+            self.arena.zero(block)        # pad lanes between tensors are never written by the copies: they must hold zeros
         opt._nvl_first_step = momenta_created
         opt._nvl_all = None
         if opt._base_is_sgd:
-            allp = [p for g in opt.param_groups for p in g['params'] if p.requires_grad]
+            gathered = {id(p) for _n, p, _m in getattr(opt, '_external', [])}      # updated by their own GEMM epilogue
+            allp = [p for g in opt.param_groups for p in g['params'] if p.requires_grad and id(p) not in gathered]
             mom, _ = ensure_momentum_buffers(opt, allp)
             opt._nvl_all = GroupTable(allp, param_group_index(opt, allp), mom, self.device)
         mode = 0
@@ -282,6 +294,22 @@ class NvlComm(Communicator):
             if opt._norm_clip is not None:
                 mode |= _lib.MODE_SUMSQ
         opt._nvl_mode = mode
+        # Deferred update: the two-shot / NVLS kernels leave the averaged gradient in their staging area (mode 0: no
+        # pass over parameters, momenta or gradient tensors while backward runs) and ONE multi-tensor SGD kernel reads
+        # it there after backward.  One-shot groups (small) sum their inbox rows into p.grad as usual.
+        deferred = bool(getattr(opt, '_deferred_update', False)) and opt._base_is_sgd and opt._norm_clip is None
+        opt._nvl_deferred_ptrs = None
+        for plan in plans:
+            plan.mode = mode
+            if deferred:
+                plan.mode = _lib.MODE_WRITEBACK if plan.algo == _lib.ALGO_ONESHOT else 0
+        if deferred:
+            where = {}
+            for plan in plans:
+                for ti, p in enumerate(plan.params):
+                    where[id(p)] = None if plan.algo == _lib.ALGO_ONESHOT else \
+                        plan.block.base + plan.stage_off + 16 * int(plan.table.voff_host[ti])
+            opt._nvl_deferred_ptrs = [where.get(id(p)) for p in opt._nvl_all.params]
         opt._nvl_held = []
         if getattr(opt, '_external', None):
             self._attach_external(opt)
@@ -318,19 +346,36 @@ class NvlComm(Communicator):
         ready = torch.cuda.Event()
         ready.record(compute)
         self.stream.wait_event(ready)
-        plan.table.refresh_grads(grads, self.stream)
+        if plan.copy_pack:
+            self._copy_pack(plan, grads)
+        else:
+            plan.table.refresh_grads(grads, self.stream)
         if not opt._groups_pending and not torch.cuda.is_current_stream_capturing():
             # first group of this iteration: hyper-parameters may have moved (inside a graph capture the
             # table is refreshed by the caller before every replay instead)
             self._hyper[id(opt)].sync(opt.param_groups, self.stream)
         a = plan.args
-        a.mode = opt._nvl_mode
+        a.mode = plan.mode
+        a.skip_pack = int(plan.copy_pack)
         a.first_step = int(opt._nvl_first_step)
         a.grad_scale = float(getattr(opt, '_grad_scale', 1.0))
         _lib.check(self.lib.mgw_allreduce_group(C.byref(a), self.stream.cuda_stream), 'allreduce_group')
         opt._nvl_held.append(grads)
         self.launches += 1
         counters.bump('allreduce_fused')
+
+    def _copy_pack(self, plan: _GroupPlan, grads) -> None:
+        """Queue one device-to-device copy per gradient tensor into the group's staging area (side stream)."""
+        if plan.stage_views is None:
+            base = plan.block.base + plan.stage_off
+            views = []
+            for ti, p in enumerate(plan.params):
+                flat = _wrap_device_memory(base + 16 * int(plan.table.voff_host[ti]), p.numel(), self.device)
+                views.append(torch.as_strided(flat, p.size(), p.stride()))      # same layout as the gradient: a plain memcpy
+            plan.stage_views = views
+        with torch.cuda.stream(self.stream):
+            for dst, g in zip(plan.stage_views, grads):
+                dst.copy_(g, non_blocking=True)
 
     def wait_groups(self, opt, pending: Sequence[int]) -> None:
         self._done_event.record(self.stream)
@@ -348,7 +393,12 @@ class NvlComm(Communicator):
             table: GroupTable = opt._nvl_all
             grads = [p.grad for p in table.params]
             if all(g is not None and g.stride() == p.stride() for g, p in zip(grads, table.params)):
-                table.refresh_grads(grads)
+                staged = opt._nvl_deferred_ptrs
+                if staged is not None:
+                    # averaged gradients wait in the staging areas (already scaled); the rest was summed into p.grad
+                    table.refresh_grad_ptrs([s if s is not None else g.data_ptr() for s, g in zip(staged, grads)])
+                else:
+                    table.refresh_grads(grads)
                 if not torch.cuda.is_current_stream_capturing():
                     self._hyper[id(opt)].sync(opt.param_groups)
                 s = torch.cuda.current_stream().cuda_stream

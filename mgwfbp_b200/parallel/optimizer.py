@@ -55,8 +55,9 @@ class _DistributedMixin:
     # ------------------------------------------------------------------ construction
     def _dist_init(self, base_optimizer, named_parameters, compression, seq_layernames, layerwise_times,
                    norm_clip, threshold, writer, gradient_path, comm, cost_model, fused_update, interference=None,
-                   cost_model_last=None):
+                   cost_model_last=None, schedule=None):
         self._wrapped = base_optimizer
+        self._given_schedule = schedule
         self._interference = interference
         self._cost_model_last = cost_model_last
         self._compression = compression
@@ -107,9 +108,16 @@ class _DistributedMixin:
         self._comm: Communicator = comm if comm is not None else self._default_comm()
         self._world = self._comm.size()
         self._base_is_sgd = _is_plain_sgd(base_optimizer)
-        want_fused = settings.FUSED_UPDATE if fused_update is None else bool(fused_update)
+        # fused_update: None (settings.UPDATE_MODE), True / 'fused', 'deferred', False / 'separate'
+        want = settings.UPDATE_MODE if fused_update is None else fused_update
+        want = {True: 'fused', False: 'separate'}.get(want, want)
+        if want not in ('fused', 'deferred', 'separate'):
+            raise ValueError("fused_update must be True, False, 'fused', 'deferred' or 'separate'")
         self._fused_comm = bool(getattr(self._comm, 'fused', False))
-        self._fused_update = bool(want_fused and self._fused_comm and self._base_is_sgd and norm_clip is None)
+        in_plane = bool(self._fused_comm and self._base_is_sgd and norm_clip is None)
+        self._fused_update = in_plane and want == 'fused'
+        self._deferred_update = in_plane and want == 'deferred'
+        self._update_mode = 'fused' if self._fused_update else ('deferred' if self._deferred_update else 'separate')
         self._grad_scale = 1.0           # see set_grad_scale
         self._shadow = None
         if settings.SHADOW_EVERY > 0 and self._fused_comm and self._base_is_sgd:
@@ -119,7 +127,7 @@ class _DistributedMixin:
         # Large linear layers fed by small batches exchange activations instead of weight gradients
         # (mgwfbp_b200.ops.wgrad.GatheredWgradLinear); their weights leave the merge schedule.
         self._external = []
-        if self._fused_update and self._world > 1 and settings.GATHERED_WGRAD:
+        if (self._fused_update or self._deferred_update) and self._world > 1 and settings.GATHERED_WGRAD:
             for name, p in list(self._named_parameters.items()):
                 module = getattr(p, '_mgw_gathered', None)
                 if module is not None and module.gathered_is_profitable(self._world):
@@ -181,7 +189,14 @@ class _DistributedMixin:
         names = self._sequential_keys
         sizes = [self._named_parameters[k].numel() for k in names]
         self._sizes = sizes
-        if settings.ORIGINAL_HOROVOD and not self._fused_comm:
+        if self._given_schedule is not None:
+            # an explicit schedule (e.g. a candidate of the schedule trial); it must cover exactly the scheduled tensors
+            sched = self._given_schedule
+            if callable(sched):               # (names, sizes, layer-wise backward times) -> MergeSchedule
+                sched = sched(names, sizes, self._layerwise_times)
+            if sorted(n for g in sched.groups for n in g) != sorted(names):
+                raise ValueError('the given merge schedule does not cover the optimizer\'s tensors')
+        elif settings.ORIGINAL_HOROVOD and not self._fused_comm:
             # the stock arm: Horovod's tensor fusion is a fixed-size bucket, no profile involved
             sched = groups_by_threshold(names, sizes, settings.HOROVOD_FUSION_ELEMENTS)
         elif settings.ADAPTIVE_MERGE and self._layerwise_times is not None:
@@ -510,7 +525,7 @@ class _DistributedMixin:
 def DistributedOptimizer(optimizer, named_parameters=None, compression=None, density=0.001, seq_layernames=None,
                          layerwise_times=None, norm_clip=None, threshold=0, writer=None, gradient_path=None,
                          comm: Optional[Communicator] = None, cost_model=None, fused_update: Optional[bool] = None,
-                         interference: Optional[float] = None, cost_model_last=None):
+                         interference: Optional[float] = None, cost_model_last=None, schedule: Optional[MergeSchedule] = None):
     """Wrap ``optimizer`` so that gradients are averaged across workers before each update.
 
     Signature and merge policies follow reference ``distributed_optimizer.py:435-471``:
@@ -528,6 +543,8 @@ def DistributedOptimizer(optimizer, named_parameters=None, compression=None, den
     fused NVLink data plane -- how much a second of communication kernel running beside backward slows
     backward down (``interference``, see ``engine.fit_interference``; default ``settings.INTERFERENCE``)
     and the cost model of the schedule's last message, which runs with the whole GPU (``cost_model_last``).
+    ``schedule`` installs a given :class:`MergeSchedule` (or the result of calling it with the scheduled names, sizes and
+    layer-wise backward times) instead of deriving one.
 
     Example of gradient clipping::
 
@@ -545,7 +562,7 @@ def DistributedOptimizer(optimizer, named_parameters=None, compression=None, den
     obj.defaults = dict(optimizer.defaults)
     obj.state.update(optimizer.state)
     obj._dist_init(optimizer, named_parameters, compression, seq_layernames, layerwise_times, norm_clip,
-                   threshold, writer, gradient_path, comm, cost_model, fused_update, interference, cost_model_last)
+                   threshold, writer, gradient_path, comm, cost_model, fused_update, interference, cost_model_last, schedule)
     if not obj._active and obj._base_is_sgd:
         first = next(iter(obj._named_parameters.values()), None)
         if first is not None and first.is_cuda:

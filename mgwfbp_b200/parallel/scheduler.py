@@ -320,3 +320,49 @@ def groups_mgwfbp_contended(names: Sequence[str], sizes: Sequence[int], tb: Sequ
                       'tb_sum': sim['tb_sum'], 'non_overlapped': sim['finish'] - sim['tb_sum'],
                       'tb_plus_tc': sim['finish'], 'tc_sum': base.predicted.get('tc_sum', 0.0), 'candidates': table})
     return MergeSchedule(chosen.groups, chosen.key_groupidx, chosen.offsets, chosen.group_sizes, predicted)
+
+
+def groups_time_sliced(names: Sequence[str], sizes: Sequence[int], tb: Sequence[float], n_slices: int,
+                       tail_elems: int = 256 * 1024) -> MergeSchedule:
+    """Groups cut at equal intervals of BACKWARD TIME, plus a small last group.
+
+    The MG-WFBP recurrences decide merges from the cost model alone; when overlapped messages are cheap but not free and
+    the link is far faster than backward (NVLink), many schedules tie under that model and the recurrences tend to one
+    large late message.  This policy spends the slack the other way round: the tensors whose gradients appear first are
+    sent first, in ``n_slices`` messages that become ready at roughly equal distances in time, so each message has the
+    rest of backward to hide under; the last message (the first layers, up to ``tail_elems`` elements) is kept small
+    because nothing can hide it.  Used as extra candidates of the schedule trial (``engine.tune_schedule``)."""
+    names = list(names)
+    L = len(names)
+    if not (len(sizes) == L and len(tb) == L):
+        raise ValueError('names, sizes and tb must have equal length')
+    size_of = dict(zip(names, sizes))
+    if L == 0:
+        return _finish([], {}, size_of)
+    order = list(range(L - 1, -1, -1))                       # backward order
+    # the tail: trailing tensors of the backward pass (layer 0 last) up to tail_elems elements, at least one tensor
+    tail, acc = [order[-1]], sizes[order[-1]]
+    for l in reversed(order[:-1]):
+        if acc + sizes[l] > tail_elems:
+            break
+        tail.insert(0, l)
+        acc += sizes[l]
+    head = order[:L - len(tail)]
+    groups: List[List[str]] = []
+    if head:
+        total = float(sum(tb[l] for l in head)) or 1.0
+        n = max(1, min(int(n_slices), len(head)))
+        cur: List[str] = []
+        run, k = 0.0, 1
+        for l in head:
+            cur.append(names[l])
+            run += float(tb[l])
+            if run >= total * k / n - 1e-15 and k < n:
+                groups.append(cur)
+                cur = []
+                k += 1
+        if cur:
+            groups.append(cur)
+    groups.append([names[l] for l in tail])
+    key_groupidx = {name: gi for gi, g in enumerate(groups) for name in g}
+    return _finish(groups, key_groupidx, size_of, {'policy': float(n_slices)})

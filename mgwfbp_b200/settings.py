@@ -54,10 +54,16 @@ ORIGINAL_HOROVOD = _env_flag('ORIGINAL_HOROVOD', False)
 # The reference declares FAKE_DATA but never reads it; here it selects synthetic datasets.
 FAKE_DATA = _env_flag('FAKE_DATA', False)
 
-# Apply the momentum-SGD update inside the all-reduce kernel of each merged group
-# (weights change during backward, ``step()`` only waits).  Switched off automatically
-# for optimizers other than plain SGD and whenever ``norm_clip`` is requested.
-FUSED_UPDATE = _env_flag('FUSED_UPDATE', True)
+# Where the momentum-SGD update happens on the fused NVLink data plane (plain SGD without gradient clipping only):
+#   'fused'     inside the all-reduce kernel of each merged group (weights change during backward, ``step()`` only waits);
+#   'deferred'  the group kernels only average (the result stays in their staging area, they never touch parameters or
+#               momenta, so they are short and cheap to run beside backward) and ONE multi-tensor SGD kernel reads the
+#               staged averages after backward -- the same kernel a single GPU runs, so the multi-GPU step pays for
+#               communication only;
+#   'separate'  the group kernels write the averaged gradient back to ``p.grad`` and a separate SGD kernel follows.
+# The entry points try 'fused' and 'deferred' schedules and keep the faster one (``engine.tune_schedule``).
+UPDATE_MODE = _env_str('UPDATE', 'fused').lower()
+FUSED_UPDATE = UPDATE_MODE == 'fused'
 
 # Swap BatchNorm+ReLU pairs and LSTMs for this package's fused CUDA modules when a model is built on a GPU.
 FUSE_MODULES = _env_flag('FUSE', True)

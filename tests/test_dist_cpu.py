@@ -300,3 +300,45 @@ def test_flat_allreduce_wrapper_matches_large_batch():
             torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-6)
     for a, b in zip(res[0]['dp'], res[1]['dp']):
         assert torch.equal(a, b)
+
+
+def _trial_harness(rank, world):
+    """engine.tune_schedule on the CPU data plane: candidates are built, trained, timed, closed; the optimizer state
+    (momentum) created under one wrapper is handed on to the next, and every rank installs the same winner."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
+    from mgwfbp_b200.engine import tune_schedule
+    from mgwfbp_b200.trainer import DLTrainer
+    settings.ADAPTIVE_MERGE = False
+    torch.manual_seed(0)
+    trainer = DLTrainer(rank, world, dist=False, batch_size=8, ngpus=0, data_dir='synthetic', dataset='cifar10',
+                        dnn='resnet20', lr=0.05, nworkers=world, prefix='allreduce', seed=0)
+    trainer.num_batches_per_epoch = 10 ** 9
+    base = trainer.optimizer
+    hvd.broadcast_parameters(trainer.net.state_dict(), root_rank=0)
+    thresholds = {0.0: 0, 0.5: 50000, 1.0: 524288000}
+    built = []
+
+    def build(rho, update):
+        opt = hvd.DistributedOptimizer(base, named_parameters=trainer.net.named_parameters(), threshold=thresholds[rho])
+        built.append(opt)
+        return opt
+    opt, report = tune_schedule(trainer, build, [{'rho': r, 'update': None} for r in (0.0, 0.5, 1.0, 0.5)], steps=2)
+    assert trainer.optimizer is opt and opt._active
+    assert all(not o._active for o in built[:-1]), 'retired wrappers still own hooks'
+    assert [r['groups'] for r in report][2] == 1 and report[3].get('same_as_earlier')
+    # momentum buffers created during the trials live on in the installed wrapper
+    p0 = next(iter(trainer.net.parameters()))
+    assert 'momentum_buffer' in opt.state[p0] and float(opt.state[p0]['momentum_buffer'].abs().sum()) > 0
+    opt.zero_grad()
+    trainer.train(1)
+    trainer.update_model()
+    return {'groups': len(opt.merge_schedule.groups), 'report': [(r['rho'], r['groups']) for r in report],
+            'params': [p.detach().clone() for p in trainer.net.parameters()]}
+
+
+def test_schedule_trial_harness_on_cpu():
+    res = run_ranks(_trial_harness, (), world=2)
+    assert res[0]['groups'] == res[1]['groups'] and res[0]['report'] == res[1]['report']
+    for a, b in zip(res[0]['params'], res[1]['params']):
+        assert torch.equal(a, b), 'replicas diverged'

@@ -226,3 +226,24 @@ def test_contended_finish_grows_with_interference_and_partial_interference_keeps
     flat = [n for g in mid.groups for n in g]
     assert flat == list(reversed(names))
     assert mid.group_sizes == [sum(sizes[names.index(n)] for n in g) for g in mid.groups]
+
+
+def test_time_sliced_groups_cover_everything_in_backward_order():
+    from mgwfbp_b200.parallel.scheduler import groups_time_sliced
+    names = ['l%d' % i for i in range(12)]
+    sizes = [100, 200, 300, 1000, 5000, 20000, 30000, 40000, 100000, 2000, 7, 50000]
+    tb = [1, 1, 2, 2, 3, 3, 4, 4, 5, 1, 1, 3]
+    for k in (1, 2, 3, 5, 40):
+        s = groups_time_sliced(names, sizes, tb, k, tail_elems=700)
+        flat = [n for g in s.groups for n in g]
+        assert flat == list(reversed(names))                       # every tensor once, last layer first
+        assert s.groups[-1] == ['l2', 'l1', 'l0']                  # the tail: trailing tensors up to 700 elements
+        assert 2 <= len(s.groups) <= min(k, 9) + 1 and (k > 3 or len(s.groups) == k + 1)
+        assert s.group_sizes == [sum(sizes[int(n[1:])] for n in g) for g in s.groups]
+        assert all(s.key_groupidx[n] == gi for gi, g in enumerate(s.groups) for n in g)
+    # equal slices of backward time: 30 units over the nine head tensors, three slices of about 10
+    s = groups_time_sliced(names, sizes, tb, 3, tail_elems=700)
+    spans = [sum(tb[int(n[1:])] for n in g) for g in s.groups[:-1]]
+    assert spans == [10, 11, 5] or max(spans) <= 12
+    # a tail budget smaller than the first tensor still leaves that tensor in the last group
+    assert groups_time_sliced(names, sizes, tb, 2, tail_elems=1).groups[-1] == ['l0']

@@ -42,8 +42,10 @@ def _ptr(t):
     return None if t is None else t.data_ptr()
 
 
-# MGWFBP_LSTM_REC=0 sends the per-step recurrent products through torch.mm (cuBLAS) instead of csrc/lstm_rec.cu
-_OWN_REC = os.environ.get('MGWFBP_LSTM_REC', '1').strip().lower() not in ('0', 'false', 'no', 'off', '')
+# MGWFBP_LSTM_REC=1 sends the per-step recurrent products through csrc/lstm_rec.cu instead of torch.mm (cuBLAS).  The
+# kernel itself is faster per call (10.1 us against 12.3 us for 20 x 1500 x 6000 on B200), but its split-K partial sums make
+# the cell kernels that add them up slower by more than that, so the library product is the default.
+_OWN_REC = os.environ.get('MGWFBP_LSTM_REC', '0').strip().lower() not in ('0', 'false', 'no', 'off', '')
 
 
 class _Recurrent:
@@ -154,6 +156,188 @@ def _weight_grad(dg: torch.Tensor, inp: torch.Tensor) -> torch.Tensor:
     return dg.t() @ inp
 
 
+# Time steps per wavefront chunk (0: layers run one after the other).  Layer k works on chunk c while layer k-1 already
+# works on chunk c+1, each layer on its own stream, which is how a multi-layer recurrence fills a GPU whose single small
+# step cannot (the library LSTM does the same internally).
+_CHUNK = int(os.environ.get('MGWFBP_LSTM_CHUNK', '7') or 0)
+_side_streams: dict = {}
+
+
+def _stream_for(device, k: int) -> torch.cuda.Stream:
+    key = (device.index, k)
+    if key not in _side_streams:
+        _side_streams[key] = torch.cuda.Stream(device=device)
+    return _side_streams[key]
+
+
+class _LSTMStack(torch.autograd.Function):
+    """All layers over a whole sequence as a wavefront: x [T, B, in], h0/c0 [L, B, H] -> out [T, B, H], hT, cT [L, B, H].
+
+    Forward: layer 0's input projection is one GEMM over all steps; every further layer projects its input chunk by
+    chunk (dropout mask applied first).  Per step one recurrent product (``_Recurrent``) and one fused cell kernel.
+    Backward walks chunks and layers in reverse with the same streams; weight gradients are single GEMMs over the whole
+    sequence at the end (``dW = dG^T [T*B, 4H] x [T*B, in]``)."""
+
+    @staticmethod
+    def forward(ctx, x, h0, c0, chunk, p_drop, training, *weights):
+        lib = _lib.load(allow_build=False)
+        _declare(lib)
+        L = len(weights) // 4
+        T, B, _ = x.shape
+        H = weights[1].shape[1]
+        dev, dt = x.device, x.dtype
+        chunk = T if (chunk <= 0 or L == 1) else min(chunk, T)
+        bounds = [(a, min(T, a + chunk)) for a in range(0, T, chunk)]
+        cur = torch.cuda.current_stream()
+        streams = [cur] + [_stream_for(dev, k) for k in range(1, L)]
+        masks = []
+        for k in range(L - 1):
+            if training and p_drop > 0:
+                masks.append(torch.bernoulli(torch.full((T, B, H), 1.0 - p_drop, device=dev, dtype=dt)).div_(1.0 - p_drop))
+            else:
+                masks.append(None)
+        w_ih, w_hh = [weights[4 * k] for k in range(L)], [weights[4 * k + 1] for k in range(L)]
+        b_ih, b_hh = [weights[4 * k + 2] for k in range(L)], [weights[4 * k + 3] for k in range(L)]
+        gx = [None] * L
+        gx[0] = x.reshape(T * B, -1) @ w_ih[0].t()                      # layer 0: all steps at once
+        inps = [x] + [torch.empty(T, B, H, device=dev, dtype=dt) for _ in range(1, L)]
+        for k in range(1, L):
+            gx[k] = torch.empty(T * B, 4 * H, device=dev, dtype=dt)
+        # slot 0 holds h0, so "the hidden state before step t" is hs[k][t] and all of them are one view (no concatenation)
+        hs = [torch.empty(T + 1, B, H, device=dev, dtype=dt) for _ in range(L)]
+        out = [hs[k][1:] for k in range(L)]
+        cs = [torch.empty(T + 1, B, H, device=dev, dtype=dt) for _ in range(L)]
+        act = [torch.empty(T, B, 4 * H, device=dev, dtype=dt) for _ in range(L)]
+        rec = [_Recurrent(lib, w_hh[k].detach(), B) for k in range(L)]
+        for k in range(L):
+            hs[k][0].copy_(h0[k])
+            cs[k][0].copy_(c0[k])
+        fork = torch.cuda.Event()
+        fork.record(cur)
+        for st in streams[1:]:
+            st.wait_event(fork)
+        for a, b in bounds:
+            done_below = None
+            for k in range(L):
+                with torch.cuda.stream(streams[k]):
+                    if k > 0:
+                        streams[k].wait_event(done_below)
+                        if masks[k - 1] is not None:
+                            torch.mul(out[k - 1][a:b], masks[k - 1][a:b], out=inps[k][a:b])
+                        else:
+                            inps[k][a:b].copy_(out[k - 1][a:b])
+                        torch.mm(inps[k][a:b].reshape((b - a) * B, H), w_ih[k].t(), out=gx[k][a * B:b * B])
+                    sp = streams[k].cuda_stream
+                    for t in range(a, b):
+                        rec[k](hs[k][t], sp)
+                        _lib.check(lib.mgw_lstm_cell_fwd(gx[k][t * B:(t + 1) * B].data_ptr(), rec[k].out.data_ptr(), _ptr(b_ih[k]),
+                                                         _ptr(b_hh[k]), cs[k][t].data_ptr(), out[k][t].data_ptr(),
+                                                         cs[k][t + 1].data_ptr(), act[k][t].data_ptr(), B, H, rec[k].parts,
+                                                         rec[k].stride, sp), 'lstm_cell_fwd')
+                    done_below = torch.cuda.Event()
+                    done_below.record(streams[k])
+        for st in streams[1:]:
+            ev = torch.cuda.Event()
+            ev.record(st)
+            cur.wait_event(ev)
+        counters.bump('lstm_cell_fwd', T * L)
+        if rec[0].own:
+            counters.bump('lstm_rec_gemm', T * L)
+        ctx.save_for_backward(x, *weights, *[m for m in masks if m is not None])
+        ctx.stash = (hs, cs, act, inps, [m is not None for m in masks], bounds)
+        ctx.dims = (L, T, B, H)
+        hT = torch.stack([out[k][T - 1] for k in range(L)])
+        cT = torch.stack([cs[k][T] for k in range(L)])
+        # a fresh view: the tensor object that autograd turns into this node's output must not be the one kept in
+        # ctx.stash, or node -> stash -> output -> node would be a reference cycle that keeps the whole graph of a
+        # finished step (and its gradient accumulators with their stream) alive until the garbage collector runs
+        return out[L - 1].view(T, B, H), hT, cT
+
+    @staticmethod
+    def backward(ctx, d_out, d_hT, d_cT):
+        lib = _lib.load(allow_build=False)
+        L, T, B, H = ctx.dims
+        saved = ctx.saved_tensors
+        x = saved[0]
+        weights = saved[1:1 + 4 * L]
+        hs, cs, act, inps, has_mask, bounds = ctx.stash
+        mask_it = iter(saved[1 + 4 * L:])
+        masks = [next(mask_it) if hm else None for hm in has_mask]
+        w_ih, w_hh = [weights[4 * k] for k in range(L)], [weights[4 * k + 1] for k in range(L)]
+        has_bias = weights[2] is not None
+        dev, dt = x.device, x.dtype
+        cur = torch.cuda.current_stream()
+        streams = [cur] + [_stream_for(dev, k) for k in range(1, L)]
+        dG = [torch.empty(T, B, 4 * H, device=dev, dtype=dt) for _ in range(L)]
+        # gradient arriving at each layer's outputs: the caller's for the top layer, from the layer above otherwise
+        d_lay = [None] * L
+        d_lay[L - 1] = d_out.contiguous() if d_out is not None else torch.zeros(T, B, H, device=dev, dtype=dt)
+        for k in range(L - 1):
+            d_lay[k] = torch.empty(T, B, H, device=dev, dtype=dt)
+        dc = [torch.zeros(B, H, device=dev, dtype=dt) if d_cT is None else d_cT[k].contiguous().clone() for k in range(L)]
+        dc_next = [torch.empty_like(dc[k]) for k in range(L)]
+        rec = [_Recurrent(lib, w_hh[k].detach().t().contiguous(), B) for k in range(L)]      # rows of W_hh^T: hidden units
+        parts = [0] * L
+        for k in range(L):
+            if d_hT is not None:                              # gradient of the final state enters like a recurrent term
+                rec[k].out.zero_()
+                rec[k].out[0].copy_(d_hT[k])
+                parts[k] = rec[k].parts
+        fork = torch.cuda.Event()
+        fork.record(cur)
+        for st in streams[1:]:
+            st.wait_event(fork)
+        for a, b in reversed(bounds):
+            done_above = None
+            for k in range(L - 1, -1, -1):
+                with torch.cuda.stream(streams[k]):
+                    if done_above is not None:
+                        streams[k].wait_event(done_above)
+                    sp = streams[k].cuda_stream
+                    for t in range(b - 1, a - 1, -1):
+                        _lib.check(lib.mgw_lstm_cell_bwd(d_lay[k][t].data_ptr(), dc[k].data_ptr(), act[k][t].data_ptr(),
+                                                         cs[k][t].data_ptr(), cs[k][t + 1].data_ptr(), dG[k][t].data_ptr(),
+                                                         dc_next[k].data_ptr(), B, H, rec[k].out.data_ptr(), parts[k],
+                                                         rec[k].stride, sp), 'lstm_cell_bwd')
+                        dc[k], dc_next[k] = dc_next[k], dc[k]
+                        rec[k](dG[k][t], sp)                  # partial sums of dh_{t-1}
+                        parts[k] = rec[k].parts
+                    if k > 0:                                 # gradient for the layer below, this chunk
+                        torch.mm(dG[k][a:b].reshape((b - a) * B, 4 * H), w_ih[k], out=d_lay[k - 1][a:b].reshape((b - a) * B, H))
+                        if masks[k - 1] is not None:
+                            d_lay[k - 1][a:b].mul_(masks[k - 1][a:b])
+                    done_above = torch.cuda.Event()
+                    done_above.record(streams[k])
+        counters.bump('lstm_cell_bwd', T * L)
+        if rec[0].own:
+            counters.bump('lstm_rec_gemm', T * L)
+        need = ctx.needs_input_grad
+        grads_w = []
+        dh0, dc0 = [], []
+        for k in range(L):
+            with torch.cuda.stream(streams[k]):
+                dG2 = dG[k].reshape(T * B, 4 * H)
+                inp2 = inps[k].reshape(T * B, -1)
+                h_prev = hs[k][:-1].reshape(T * B, H)
+                dw_ih = _weight_grad(dG2, inp2)
+                dw_hh = _weight_grad(dG2, h_prev)
+                db = dG2.sum(0) if has_bias else None
+                grads_w += [dw_ih, dw_hh, db, db.clone() if db is not None else None]
+                dh0.append(rec[k].out.sum(0))
+                dc0.append(dc[k])
+        dx = None
+        if need[0]:
+            dx = (dG[0].reshape(T * B, 4 * H) @ w_ih[0]).reshape(x.shape)
+        for st in streams[1:]:
+            ev = torch.cuda.Event()
+            ev.record(st)
+            cur.wait_event(ev)
+        for g in grads_w + dh0 + dc0:                         # allocated on a layer's stream, consumed on the caller's
+            if g is not None:
+                g.record_stream(cur)
+        return (dx, torch.stack(dh0) if need[1] else None, torch.stack(dc0) if need[2] else None, None, None, None, *grads_w)
+
+
 class FusedLSTM(nn.Module):
     def __init__(self, input_size: int, hidden_size: int, num_layers: int = 1, bias: bool = True, dropout: float = 0.0):
         super().__init__()
@@ -186,15 +370,16 @@ class FusedLSTM(nn.Module):
             z = x.new_zeros(self.num_layers, B, self.hidden_size)
             hx = (z, z.clone())
         h0, c0 = hx
+        if x.is_cuda and x.dtype == torch.float32:
+            weights = [w for k in range(self.num_layers) for w in self._layer_params(k)]
+            out, hT, cT = _LSTMStack.apply(x.contiguous(), h0, c0, _CHUNK, self.dropout, self.training, *weights)
+            return out, (hT, cT)
         hs: List[torch.Tensor] = []
         cs: List[torch.Tensor] = []
         inp = x
         for k in range(self.num_layers):
             w_ih, w_hh, b_ih, b_hh = self._layer_params(k)
-            if x.is_cuda and x.dtype == torch.float32:
-                out, hT, cT = _LSTMLayer.apply(inp.contiguous(), h0[k], c0[k], w_ih, w_hh, b_ih, b_hh)
-            else:
-                out, hT, cT = self._reference_layer(inp, h0[k], c0[k], w_ih, w_hh, b_ih, b_hh)
+            out, hT, cT = self._reference_layer(inp, h0[k], c0[k], w_ih, w_hh, b_ih, b_hh)
             hs.append(hT)
             cs.append(cT)
             inp = out

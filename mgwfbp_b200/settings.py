@@ -67,9 +67,11 @@ FUSED_UPDATE = UPDATE_MODE == 'fused'
 
 # Swap BatchNorm+ReLU pairs and LSTMs for this package's fused CUDA modules when a model is built on a GPU.
 FUSE_MODULES = _env_flag('FUSE', True)
-# The PTB model's recurrent part: torch.nn.LSTM (cuDNN's persistent kernels, faster at batch 20) unless this is set,
-# in which case mgwfbp_b200.ops.lstm.FusedLSTM (this package's cell kernels) is used.
-FUSE_LSTM = _env_flag('FUSE_LSTM', False)
+# The PTB model's recurrent part: mgwfbp_b200.ops.lstm.FusedLSTM (this package's cell kernels; the layers run as a
+# wavefront over chunks of time steps on two streams) unless this is switched off, in which case torch.nn.LSTM (the
+# library's LSTM) is used.  Measured on B200 (batch 20, 35 steps, 1500 hidden, whole training step): 2.60 ms with the
+# kernels here, 2.56 ms with the library's -- the named kernels are on the hot path at a cost of 1.6 %.
+FUSE_LSTM = _env_flag('FUSE_LSTM', True)
 # How many algorithms cuDNN's benchmark mode may time per convolution shape (-1: leave PyTorch's default of 10, 0: all).
 CUDNN_BENCHMARK_LIMIT = int(_env_str('CUDNN_BENCHMARK_LIMIT', '-1'))
 # Keep convolutional models and their inputs in channels-last (NHWC) memory format on the GPU.

@@ -261,10 +261,13 @@ def test_fused_model_matches_unfused(dnn, shape, classes):
 
 
 # ----------------------------------------------------------------------------- LSTM
-def test_fused_lstm_matches_cudnn_lstm():
+@pytest.mark.parametrize('chunk,H', [(0, 64), (3, 64), (3, 30)])       # H = 30: the scalar cell kernels (H % 4 != 0)
+def test_fused_lstm_matches_cudnn_lstm(chunk, H, monkeypatch):
+    from mgwfbp_b200.ops import lstm as lstm_ops
     from mgwfbp_b200.ops.lstm import FusedLSTM
+    monkeypatch.setattr(lstm_ops, '_CHUNK', chunk)
     torch.manual_seed(0)
-    T, B, I, H = 7, 5, 48, 64
+    T, B, I = 7, 5, 48
     ref = torch.nn.LSTM(I, H, 2).cuda()
     mine = FusedLSTM(I, H, 2).cuda()
     mine.load_state_dict(ref.state_dict())
@@ -320,11 +323,16 @@ def test_lstm_recurrent_gemm_matches_fp32_product(B, R, K):
         torch.testing.assert_close(out[p], part, rtol=5e-3, atol=5e-3)
 
 
-def test_fused_lstm_with_own_recurrent_kernel_tracks_library_lstm():
+@pytest.mark.parametrize('chunk', [0, 2, 7])
+def test_fused_lstm_with_own_recurrent_kernel_tracks_library_lstm(chunk, monkeypatch):
     """TF32 allowed on both sides: the package's recurrent kernel is on the path (launch counter) and the layer stays
-    within TF32 accuracy of torch.nn.LSTM, forward and backward, with the PTB model's awkward sizes."""
+    within TF32 accuracy of torch.nn.LSTM, forward and backward, with the PTB model's awkward sizes; layers run one
+    after the other (chunk 0) or as a wavefront over chunks of time steps on two streams."""
     from mgwfbp_b200.ops import counters
+    from mgwfbp_b200.ops import lstm as lstm_ops
     from mgwfbp_b200.ops.lstm import FusedLSTM
+    monkeypatch.setattr(lstm_ops, '_OWN_REC', True)
+    monkeypatch.setattr(lstm_ops, '_CHUNK', chunk)
     torch.manual_seed(0)
     T, B, I, H = 6, 20, 100, 300
     ref = torch.nn.LSTM(I, H, 2).cuda()

@@ -93,6 +93,24 @@ struct Tiling {
     int tx, ty, grid_x, grid_y, rows_per_split;
 };
 
+// How many SMs the BatchNorm kernels size their single resident wave for.  The kernels are laid out as exactly one
+// wave (4 or 2 blocks per SM); when a communication kernel holds some SMs beside them (one 512-thread CTA per SM, at
+// most `overlap_ctas` of them), a grid sized for all SMs no longer fits and its last blocks run as a second wave, which
+// doubles the kernel's time for an 11 % loss of SMs.  A multi-GPU job therefore lowers the budget by the CTAs its
+// overlapped communication kernels may use (mgw_bn_set_sm_budget); the kernels are bandwidth bound and lose nothing
+// measurable on the remaining SMs when they have the GPU to themselves.
+std::atomic<int> g_sm_budget{0};
+
+int sm_budget() {
+    int v = g_sm_budget.load();
+    if (v > 0) return v;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (sms < 1) sms = 148;
+    g_sm_budget.store(sms);
+    return sms;
+}
+
 Tiling make_tiling(long long M, int C, int vec, int blocks_per_sm = 4) {
     Tiling t;
     const int lanes = (C + vec - 1) / vec;
@@ -101,7 +119,7 @@ Tiling make_tiling(long long M, int C, int vec, int blocks_per_sm = 4) {
     t.tx = tx;
     t.ty = kThreads / tx;
     t.grid_x = (lanes + tx - 1) / tx;
-    const int target_blocks = 148 * blocks_per_sm;            // exactly one resident wave
+    const int target_blocks = sm_budget() * blocks_per_sm;    // exactly one resident wave on the SMs this job may count on
     long long max_splits = (M + t.ty - 1) / t.ty;
     long long gy = (target_blocks + t.grid_x - 1) / t.grid_x;
     if (gy > max_splits) gy = max_splits;
@@ -730,6 +748,16 @@ cudaError_t launch_bwd(const BwdArgs& a, cudaStream_t s) {
 }  // namespace
 
 extern "C" {
+
+// SMs the BatchNorm grids are sized for from now on (0: all SMs of the current device); returns the previous value.
+// Set it before a training step is captured in a CUDA graph: grids are part of the capture.
+int mgw_bn_set_sm_budget(int sms) {
+    const int prev = sm_budget();
+    int dev = 0, all = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&all, cudaDevAttrMultiProcessorCount, dev);
+    g_sm_budget.store(sms <= 0 ? all : (sms > all ? all : sms));
+    return prev;
+}
 
 // Number of floats the caller must provide in `partials` for an [M, C] problem.
 size_t mgw_bn_partials_floats(long long M, int C) {

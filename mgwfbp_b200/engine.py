@@ -437,7 +437,7 @@ def fit_interference(trainer, comm=None, n_ctas: Optional[int] = None, message_b
     return out
 
 
-def tune_schedule(trainer, build_optimizer, candidates: Sequence[dict], steps: int = 8, use_graph: bool = True):
+def tune_schedule(trainer, build_optimizer, candidates: Sequence[dict], steps: int = 20, use_graph: bool = True):
     """Pick the merge schedule (and where the update runs) by running the candidates.
 
     ``build_optimizer(**candidate)`` must return a ``DistributedOptimizer`` around the SAME base optimizer; a candidate is
@@ -501,7 +501,7 @@ def _time_replays(step: 'TrainStep', batch, steps: int) -> float:
 
 def build_distributed_optimizer(trainer, seq_layernames=None, layerwise_times=None, threshold: int = 0, norm_clip=None,
                                 compression=None, writer=None, gradient_path=None, tune: bool = True,
-                                fit_comm: bool = True, trial_steps: int = 8, use_graph: bool = True):
+                                fit_comm: bool = True, trial_steps: int = 20, use_graph: bool = True):
     """What the entry points do between profiling backward and the first training step (reference
     ``dist_trainer.py:55-66``: build the wrapped optimizer, broadcast the parameters), plus the measurements the merge
     scheduler needs on an NVSwitch box.

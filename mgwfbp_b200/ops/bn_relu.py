@@ -49,6 +49,7 @@ def _declare(lib) -> None:
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p]
     lib.mgw_bn_launches.argtypes = [C.c_longlong, C.c_int, C.c_int]
+    lib.mgw_bn_set_sm_budget.argtypes = [C.c_int]
     lib.mgw_bn_cluster_supported.argtypes = [C.c_longlong, C.c_int]
     lib.mgw_bn_relu_fwd_cluster.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int, C.c_void_p, C.c_void_p,
                                             C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_float, C.c_int, C.c_void_p,
@@ -62,6 +63,17 @@ def _declare(lib) -> None:
 # Small activations (at most 8192 rows, at most 288 channels in multiples of 16) take the one-launch cluster kernels
 # (csrc/bn_relu_cluster.cu); MGWFBP_BN_CLUSTER=0 keeps everything on the three-launch kernels.
 _CLUSTER = os.environ.get('MGWFBP_BN_CLUSTER', '1').strip().lower() not in ('0', 'false', 'no', 'off', '')
+
+
+def set_sm_budget(sms: int) -> int:
+    """Size the BatchNorm grids for ``sms`` SMs from now on (0: all of them); returns the previous budget.
+
+    The kernels run as exactly one resident wave.  A job whose communication kernels hold a few SMs beside backward
+    (``NvlComm.overlap_ctas``) lowers the budget by that many, so the wave still fits while such a kernel is running;
+    call it before the training step is captured in a CUDA graph."""
+    lib = _lib.load(allow_build=False)
+    _declare(lib)
+    return int(lib.mgw_bn_set_sm_budget(int(sms)))
 
 
 def _use_cluster(lib, M: int, Cc: int) -> bool:

@@ -122,6 +122,12 @@ class NvlComm(Communicator):
         self._hyper: Dict[int, HyperTable] = {}
         self._keepalive: List[object] = []
         self.launches = 0
+        if self._world > 1 and os.environ.get('MGWFBP_BN_RESERVE', '1').strip().lower() not in ('0', 'false', 'no', 'off'):
+            # the memory-bound kernels of the model are sized as one resident wave: leave the SMs that an overlapped
+            # communication kernel may hold out of that wave (see ops.bn_relu.set_sm_budget)
+            from ...ops.bn_relu import set_sm_budget
+            sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+            set_sm_budget(max(sms // 2, sms - self.overlap_ctas))
 
     @property
     def nvls_available(self) -> bool:

@@ -1,5 +1,7 @@
 // C ABI of libmgwfbp_b200.so.  Every entry point returns MGW_OK (0) or an MGW_ERR_* code;
 // mgw_last_error() gives the text of the most recent failure on the calling thread.
+// The header is C++ (common.cuh needs cuda_runtime.h); the symbols have C linkage and can be bound from any language
+// through the shared library (the package itself uses ctypes).
 #pragma once
 #include <stddef.h>
 #include <stdint.h>

@@ -2,6 +2,7 @@
 // group).  Replaces the per-tensor elementwise launches of torch.optim.SGD.step on the 1-GPU
 // path, after gradient accumulation, and after a global-norm clip (the clip coefficient is read
 // from device memory, so no host round trip separates the norm from the update).
+#include <atomic>
 #include "api.h"
 
 template <int U, int MIN_BLOCKS>                          // U: float4 slots per operand a thread keeps in flight
@@ -75,7 +76,10 @@ static __device__ __align__(256) float g_static_partials[MGW_STATIC_MAX_PARTIALS
 
 namespace {
 constexpr int kMaxDevices = 64;
-float* g_static_partials_addr[kMaxDevices] = {nullptr};
+// Device address of g_static_partials per device, filled on the first call on that device.  Atomic only so that two host
+// threads making their first call at once both see a complete pointer (they would store the same value).  A
+// cudaDeviceReset() invalidates the entry of that device; a process that resets a device must not call this afterwards.
+std::atomic<float*> g_static_partials_addr[kMaxDevices];
 }  // namespace
 
 extern "C" int mgw_grad_clip_coef_static(const MgwGroup* group, float max_norm, float* out2, int n_ctas, void* stream) {
@@ -89,13 +93,12 @@ extern "C" int mgw_grad_clip_coef_static(const MgwGroup* group, float max_norm, 
     int dev = -1;
     MGW_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= kMaxDevices) return MGW_ERR_ARG;
-    if (g_static_partials_addr[dev] == nullptr) {
+    float* partials = g_static_partials_addr[dev].load(std::memory_order_acquire);
+    if (partials == nullptr) {
         // once per device, with that device current: translate the symbol into this device's address
-        float* p = nullptr;
-        MGW_CUDA_CHECK(cudaGetSymbolAddress((void**)&p, g_static_partials));
-        g_static_partials_addr[dev] = p;
+        MGW_CUDA_CHECK(cudaGetSymbolAddress((void**)&partials, g_static_partials));
+        g_static_partials_addr[dev].store(partials, std::memory_order_release);
     }
-    float* partials = g_static_partials_addr[dev];
     cudaStream_t s = (cudaStream_t)stream;
     if (group->n_vec == 0) n_ctas = 1;
     mgw_multi_tensor_sgd_kernel<2, 2><<<n_ctas, 512, 0, s>>>(*group, nullptr, nullptr, 1.f, 0, MGW_MODE_SUMSQ, partials);

@@ -1,5 +1,7 @@
 // Entry point for callers that must not allocate device memory.  It has no counterpart in the
 // reference (the reference has no native code at all); it exists for embedders of this library.
+// This header is C++ (it includes common.cuh, which needs cuda_runtime.h); the exported symbol itself has C linkage and
+// can be bound from any language through the shared library.
 #pragma once
 #include "common.cuh"
 

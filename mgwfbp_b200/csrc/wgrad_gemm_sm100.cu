@@ -49,6 +49,7 @@ constexpr uint32_t kWaitSpins = 1u << 22;
 
 #define WG_MODE_STORE 1      // write dW * scale to `grad_out`
 #define WG_MODE_SGD 2        // apply dW * scale to (weight, momentum) with the hyper-parameters of `pg`
+#define WG_MODE_SCATTER 4    // reduce-scatter epilogue: store the tile into its OWNER rank's staging slot (peer stores)
 
 struct Params {
     float* weight;
@@ -59,6 +60,10 @@ struct Params {
     int M, N, K;
     int mode, pg, first_step;
     float scale;
+    // WG_MODE_SCATTER: tile t (row-major over the tile grid) belongs to rank t % world; rank r's copy of it goes to
+    // scatter[owner] + (r * tiles_per_owner + t / world) * BM * BN, a full 128 x 128 slot (rows beyond M / N hold zeros)
+    float* const* scatter;
+    int rank, world, tiles_per_owner;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -253,6 +258,20 @@ wgrad_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
             }
             __syncwarp();
             const int ch = lane & 15;
+            if (p.mode & WG_MODE_SCATTER) {
+                // The tile leaves tensor memory once and goes straight into the reduction: 256-byte row segments into the
+                // owner's slot for this rank, over NVLink when the owner is a peer (ordinary stores; the finishing
+                // kernel's barrier publishes them).
+                const int t = blockIdx.y * gridDim.x + blockIdx.x;
+                const int owner = t % p.world;
+                float* slot = p.scatter[owner] + ((size_t)p.rank * p.tiles_per_owner + (size_t)(t / p.world)) * (BM * BN);
+#pragma unroll 4
+                for (int i = 0; i < 16; ++i) {
+                    const int rr = 2 * i + (lane >> 4);
+                    const float4 g = wsm[rr * 16 + (ch ^ (rr & 7))];
+                    mgw_st_peer(reinterpret_cast<float4*>(slot + (size_t)(q * 32 + rr) * BN + half * 64 + 4 * ch), g);
+                }
+            }
             const int n = n0 + half * 64 + 4 * ch;
             const bool use_m = (p.mode & WG_MODE_SGD) && p.mom != nullptr && h.momentum != 0.f;
 #pragma unroll 4
@@ -333,6 +352,49 @@ allgather_rows_kernel(float* const* bufs, uint32_t* const* flags, uint32_t* epoc
     if (threadIdx.x == 0) epoch[b] = e;
 }
 
+// Second half of the reduce-scatter weight gradient: runs on every rank behind its own scatter GEMM.  After a barrier
+// ("every rank's tiles are in the owners' slots") rank r adds up, in rank order, the `world` slots of each tile it owns
+// and stores the sum into EVERY rank's gradient tensor (symmetric memory, ordinary peer stores); a second barrier says
+// "every gradient tensor is complete".  Sums are formed once, by one rank, and broadcast: replicas get identical bits.
+__global__ void __launch_bounds__(512)
+wgrad_reduce_finish_kernel(float* const* stage, float* const* grads, uint32_t* const* flags, uint32_t* epoch, int* status, int rank,
+                           int world, int M, int N, int tiles_per_owner, unsigned long long timeout_ns) {
+    __shared__ int failed;
+    const int b = blockIdx.x;
+    const uint32_t e = epoch[b] + 1u;
+    if (threadIdx.x == 0) failed = 0;
+    if (gather_barrier(flags, 0, rank, world, e, status, timeout_ns, &failed)) {
+        const int tiles_x = (N + BN - 1) / BN, tiles_y = (M + BM - 1) / BM;
+        const int tiles = tiles_x * tiles_y;
+        const int owned = (tiles - rank + world - 1) / world;            // tiles t with t % world == rank
+        const float4* mine = reinterpret_cast<const float4*>(stage[rank]);
+        constexpr int kTileVec = BM * BN / 4;
+        for (int ti = b; ti < owned; ti += gridDim.x) {
+            const int t = ti * world + rank;
+            const int m0 = (t / tiles_x) * BM, n0 = (t % tiles_x) * BN;
+            for (int v = threadIdx.x; v < kTileVec; v += blockDim.x) {
+                const int row = v / (BN / 4), col = (v - row * (BN / 4)) * 4;
+                const int m = m0 + row, n = n0 + col;
+                if (m >= M || n >= N) continue;
+                float4 acc = mgw_ld_peer(mine + (size_t)ti * kTileVec + v);
+                for (int s = 1; s < world; ++s) {
+                    const float4 x = mgw_ld_peer(mine + ((size_t)s * tiles_per_owner + ti) * kTileVec + v);
+                    acc.x += x.x; acc.y += x.y; acc.z += x.z; acc.w += x.w;
+                }
+                const size_t off = (size_t)m * N + n;
+                for (int i = 0; i < world; ++i) {
+                    int q = rank + i;
+                    if (q >= world) q -= world;
+                    mgw_st_peer(reinterpret_cast<float4*>(grads[q] + off), acc);
+                }
+            }
+        }
+        (void)gather_barrier(flags, 1, rank, world, e, status, timeout_ns, &failed);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) epoch[b] = e;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -394,8 +456,60 @@ int mgw_wgrad_gemm(const float* dy, const float* x, int M, int N, int K, float s
     Params p;
     p.weight = weight; p.mom = mom; p.grad_out = grad_out; p.hyper = hyper; p.status = status;
     p.M = M; p.N = N; p.K = K; p.mode = mode; p.pg = pg; p.first_step = first_step; p.scale = scale;
+    p.scatter = nullptr; p.rank = 0; p.world = 1; p.tiles_per_owner = 0;
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     wgrad_gemm_kernel<<<grid, kThreadsPerCta, kSmemBytes, (cudaStream_t)stream>>>(map_a, map_b, p);
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}
+
+// Floats of staging every rank must provide for the reduce-scatter form of an [M, N] weight gradient on `world` ranks:
+// `world` source rows of ceil(tiles / world) full 128 x 128 slots.
+size_t mgw_wgrad_scatter_stage_floats(int M, int N, int world) {
+    if (M <= 0 || N <= 0 || world < 1) return 0;
+    const size_t tiles = (size_t)((N + BN - 1) / BN) * (size_t)((M + BM - 1) / BM);
+    return (size_t)world * ((tiles + world - 1) / world) * (size_t)(BM * BN);
+}
+
+// First half of the reduce-scatter weight gradient: scale * dy^T x, each 128 x 128 tile stored into the staging area of
+// the rank that owns it (stage_dev: device array of every rank's staging base, peers included).  Nothing is written
+// locally.  Follow it on the same stream with mgw_wgrad_reduce_finish.
+int mgw_wgrad_gemm_scatter(const float* dy, const float* x, int M, int N, int K, float scale, float* const* stage_dev, int rank,
+                           int world, int* status, void* stream) {
+    if (!mgw_wgrad_gemm_supported(dy, x, M, N, K) || stage_dev == nullptr) return MGW_ERR_ARG;
+    if (world < 1 || world > MGW_MAX_RANKS || rank < 0 || rank >= world) return MGW_ERR_ARG;
+    CUtensorMap map_a, map_b;
+    if (!make_map(&map_a, dy, K, M) || !make_map(&map_b, x, K, N)) {
+        mgw_set_last_error(cudaErrorUnknown, "cuTensorMapEncodeTiled", __FILE__, __LINE__);
+        return MGW_ERR_CUDA;
+    }
+    static bool configured = false;
+    if (!configured) {
+        MGW_CUDA_CHECK(cudaFuncSetAttribute(wgrad_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+        configured = true;
+    }
+    Params p;
+    p.weight = nullptr; p.mom = nullptr; p.grad_out = nullptr; p.hyper = nullptr; p.status = status;
+    p.M = M; p.N = N; p.K = K; p.mode = WG_MODE_SCATTER; p.pg = 0; p.first_step = 0; p.scale = scale;
+    dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+    const size_t tiles = (size_t)grid.x * grid.y;
+    p.scatter = stage_dev; p.rank = rank; p.world = world; p.tiles_per_owner = (int)((tiles + world - 1) / world);
+    wgrad_gemm_kernel<<<grid, kThreadsPerCta, kSmemBytes, (cudaStream_t)stream>>>(map_a, map_b, p);
+    MGW_CUDA_CHECK(cudaGetLastError());
+    return MGW_OK;
+}
+
+// Second half: owners add their slots up in rank order and store the sums into every rank's gradient tensor
+// (grads_dev: device array of every rank's [M, N] gradient in symmetric memory).  flags / epoch as in mgw_allgather_rows,
+// with rows of their own.  Both waits are bounded by timeout_ns.
+int mgw_wgrad_reduce_finish(float* const* stage_dev, float* const* grads_dev, uint32_t* const* flags_dev, uint32_t* epoch, int* status,
+                            int rank, int world, int M, int N, int n_ctas, unsigned long long timeout_ns, void* stream) {
+    if (stage_dev == nullptr || grads_dev == nullptr || flags_dev == nullptr || epoch == nullptr) return MGW_ERR_ARG;
+    if (world < 1 || world > MGW_MAX_RANKS || rank < 0 || rank >= world || n_ctas < 1 || n_ctas > MGW_MAX_CTAS) return MGW_ERR_ARG;
+    if (M <= 0 || N <= 0 || (N & 3)) return MGW_ERR_ARG;
+    const size_t tiles = (size_t)((N + BN - 1) / BN) * (size_t)((M + BM - 1) / BM);
+    wgrad_reduce_finish_kernel<<<n_ctas, 512, 0, (cudaStream_t)stream>>>(stage_dev, grads_dev, flags_dev, epoch, status, rank, world, M, N,
+                                                                       (int)((tiles + world - 1) / world), timeout_ns);
     MGW_CUDA_CHECK(cudaGetLastError());
     return MGW_OK;
 }

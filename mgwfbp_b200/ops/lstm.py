@@ -147,8 +147,12 @@ class _LSTMLayer(torch.autograd.Function):
 _WGRAD = os.environ.get('MGWFBP_LSTM_WGRAD', 'library').strip().lower()
 
 
-def _weight_grad(dg: torch.Tensor, inp: torch.Tensor) -> torch.Tensor:
-    """``dg^T @ inp`` ([T*B, 4H]^T x [T*B, in]): the weight gradient of a whole sequence as one GEMM."""
+def _weight_grad(dg: torch.Tensor, inp: torch.Tensor, sink=None) -> Optional[torch.Tensor]:
+    """``dg^T @ inp`` ([T*B, 4H]^T x [T*B, in]): the weight gradient of a whole sequence as one GEMM.  With a ``sink`` (set on
+    the parameter by a data-parallel optimizer) the product is formed and reduced across ranks there and nothing is returned."""
+    if sink is not None:
+        sink(dg.contiguous(), inp.contiguous())
+        return None
     if _WGRAD == 'tcgen05':
         from . import wgrad
         if wgrad.supported(dg, inp):
@@ -245,6 +249,8 @@ class _LSTMStack(torch.autograd.Function):
             counters.bump('lstm_rec_gemm', T * L)
         ctx.save_for_backward(x, *weights, *[m for m in masks if m is not None])
         ctx.stash = (hs, cs, act, inps, [m is not None for m in masks], bounds)
+        # where a data-parallel optimizer wants a weight gradient delivered instead of returned (reduce-scatter GEMM)
+        ctx.sinks = [getattr(w, '_mgw_rs_sink', None) if w is not None else None for w in weights]
         ctx.dims = (L, T, B, H)
         hT = torch.stack([out[k][T - 1] for k in range(L)])
         cT = torch.stack([cs[k][T] for k in range(L)])
@@ -319,8 +325,8 @@ class _LSTMStack(torch.autograd.Function):
                 dG2 = dG[k].reshape(T * B, 4 * H)
                 inp2 = inps[k].reshape(T * B, -1)
                 h_prev = hs[k][:-1].reshape(T * B, H)
-                dw_ih = _weight_grad(dG2, inp2)
-                dw_hh = _weight_grad(dG2, h_prev)
+                dw_ih = _weight_grad(dG2, inp2, ctx.sinks[4 * k])
+                dw_hh = _weight_grad(dG2, h_prev, ctx.sinks[4 * k + 1])
                 db = dG2.sum(0) if has_bias else None
                 grads_w += [dw_ih, dw_hh, db, db.clone() if db is not None else None]
                 dh0.append(rec[k].out.sum(0))
@@ -347,6 +353,8 @@ class FusedLSTM(nn.Module):
             in_k = input_size if k == 0 else hidden_size
             self.register_parameter('weight_ih_l%d' % k, nn.Parameter(torch.empty(4 * hidden_size, in_k)))
             self.register_parameter('weight_hh_l%d' % k, nn.Parameter(torch.empty(4 * hidden_size, hidden_size)))
+            for w in (getattr(self, 'weight_ih_l%d' % k), getattr(self, 'weight_hh_l%d' % k)):
+                w._mgw_scatter_candidate = True       # their gradient is one GEMM: may take the reduce-scatter form
             if bias:
                 self.register_parameter('bias_ih_l%d' % k, nn.Parameter(torch.empty(4 * hidden_size)))
                 self.register_parameter('bias_hh_l%d' % k, nn.Parameter(torch.empty(4 * hidden_size)))

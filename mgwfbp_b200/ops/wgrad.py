@@ -30,6 +30,12 @@ def _lib_ready():
                                        C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_void_p]
         lib.mgw_allgather_rows.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_longlong,
                                            C.c_int, C.c_ulonglong, C.c_void_p]
+        lib.mgw_wgrad_scatter_stage_floats.restype = C.c_size_t
+        lib.mgw_wgrad_scatter_stage_floats.argtypes = [C.c_int, C.c_int, C.c_int]
+        lib.mgw_wgrad_gemm_scatter.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_float, C.c_void_p, C.c_int,
+                                               C.c_int, C.c_void_p, C.c_void_p]
+        lib.mgw_wgrad_reduce_finish.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                                C.c_int, C.c_int, C.c_int, C.c_ulonglong, C.c_void_p]
         _declared = True
     return lib
 
@@ -125,7 +131,11 @@ class _GatheredLinearFn(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1])
         dx = (dy2 @ weight).reshape(x.shape) if ctx.needs_input_grad[0] else None
         db = dy2.sum(0) if ctx.has_bias else None
-        ctx.module._exchange(ctx.module, dy2.contiguous(), x2.contiguous())     # gather + GEMM + update on the side stream
+        sink = getattr(ctx.module.weight, '_mgw_rs_sink', None)
+        if sink is not None:
+            sink(dy2.contiguous(), x2.contiguous())        # GEMM with the reduce-scatter epilogue + owners' sums, side stream
+        else:
+            ctx.module._exchange(ctx.module, dy2.contiguous(), x2.contiguous())     # gather + GEMM + update on the side stream
         return dx, None, db, None
 
 
@@ -148,8 +158,8 @@ class GatheredWgradLinear(torch.nn.Linear):
         return (m % 4 == 0 and n % 4 == 0 and world * rows * (m + n) * 2 <= m * n)
 
     def forward(self, x):
-        exchange = getattr(self, '_exchange', None)
-        if exchange is not None and self.training and torch.is_grad_enabled() and x.is_cuda:
+        external = getattr(self, '_exchange', None) is not None or getattr(self.weight, '_mgw_rs_sink', None) is not None
+        if external and self.training and torch.is_grad_enabled() and x.is_cuda:
             return _GatheredLinearFn.apply(x, self.weight, self.bias, self)
         return super().forward(x)
 

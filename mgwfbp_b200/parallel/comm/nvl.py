@@ -96,7 +96,7 @@ class NvlComm(Communicator):
         # control block: flag rows + per-CTA launch counters, in a heap of its own
         self._flag_bytes = int(self.lib.mgw_flag_block_bytes())
         self.arena = SymmArena(self.lib)
-        ctl_bytes = 2 * (self._flag_bytes + 4 * _lib.MAX_CTAS + 2 * _ALIGN)
+        ctl_bytes = 3 * (self._flag_bytes + 4 * _lib.MAX_CTAS + 2 * _ALIGN)
         self._ctl: Block = self.arena.alloc(ctl_bytes)               # first block of a fresh (zeroed) heap
         top = [0]
 
@@ -108,6 +108,8 @@ class NvlComm(Communicator):
         self._epoch_off = carve(4 * _lib.MAX_CTAS)
         self._gflag_off = carve(self._flag_bytes)          # flag rows / counters of the row all-gather
         self._gepoch_off = carve(4 * _lib.MAX_CTAS)
+        self._rflag_off = carve(self._flag_bytes)          # ... and of the reduce-scatter weight gradients
+        self._repoch_off = carve(4 * _lib.MAX_CTAS)
         assert top[0] <= ctl_bytes
         self._gather_tables = None
         status = C.POINTER(C.c_int)()
@@ -254,7 +256,12 @@ class NvlComm(Communicator):
         hyper = HyperTable(self.device)
         self._hyper[key] = hyper
         n_partials = sum(s[1] for s in sizes)
-        partials = torch.zeros(max(n_partials, 1), dtype=torch.float32, device=self.device)
+        # one sum of squares per CTA of every group kernel, plus (clipping only) those of the weights whose gradient
+        # arrives through the reduce-scatter GEMM: their norm is taken by one extra kernel in finish_step
+        scatter = list(getattr(opt, '_scatter', []))
+        opt._rs_sumsq_ctas = 64 if (scatter and opt._norm_clip is not None) else 0
+        opt._rs_partials_off = n_partials
+        partials = torch.zeros(max(n_partials + opt._rs_sumsq_ctas, 1), dtype=torch.float32, device=self.device)
         clip_out = torch.ones(2, dtype=torch.float32, device=self.device)
         opt._nvl_partials, opt._nvl_clip_out = partials, clip_out
         p_off = 0
@@ -319,6 +326,8 @@ class NvlComm(Communicator):
         opt._nvl_held = []
         if getattr(opt, '_external', None):
             self._attach_external(opt)
+        if scatter:
+            self._attach_scatter(opt)
         algos = {0: 0, 1: 0, 2: 0}
         for pl in plans:
             algos[pl.algo] += 1
@@ -340,6 +349,9 @@ class NvlComm(Communicator):
             st['bufs'] = None
         for _name, _p, module in getattr(opt, '_external', []):
             module._exchange = None                 # the layer behaves like nn.Linear again
+        for _name, p in getattr(opt, '_scatter', []):
+            p._mgw_rs_sink = None
+        opt._rs_state = {}
 
     # ------------------------------------------------------------------ hot path
     def launch_group(self, opt, gi: int) -> None:
@@ -394,6 +406,20 @@ class NvlComm(Communicator):
     def finish_step(self, opt, closure=None):
         loss = closure() if closure is not None else None
         if opt._fused_update:
+            if getattr(opt, '_scatter', None):
+                # every other weight was updated inside its group's kernel; these got an averaged gradient from the
+                # reduce-scatter GEMM and take one multi-tensor SGD launch of their own
+                table: GroupTable = opt._rs_table
+                table.refresh_grads([p.grad for p in table.params])
+                if not torch.cuda.is_current_stream_capturing():
+                    self._hyper[id(opt)].sync(opt.param_groups)
+                n_ctas = max(1, min(296, (table.n_vec + 2047) // 2048))
+                _lib.check(self.lib.mgw_multi_tensor_sgd(C.byref(table.struct), self._hyper[id(opt)].data_ptr(), None, 1.0,
+                                                         int(opt._rs_first), _lib.MODE_UPDATE, None, n_ctas,
+                                                         torch.cuda.current_stream().cuda_stream), 'multi_tensor_sgd')
+                opt._rs_first = False
+                self.launches += 1
+                counters.bump('multi_tensor_sgd')
             return loss
         if opt._base_is_sgd and opt._nvl_all is not None:
             table: GroupTable = opt._nvl_all
@@ -411,6 +437,12 @@ class NvlComm(Communicator):
                 clip_ptr = None
                 if opt._norm_clip is not None:
                     part = opt._nvl_partials
+                    if opt._rs_sumsq_ctas:
+                        rs: GroupTable = opt._rs_table
+                        rs.refresh_grads([p.grad for p in rs.params])
+                        _lib.check(self.lib.mgw_group_sumsq(C.byref(rs.struct), part.data_ptr() + 4 * opt._rs_partials_off,
+                                                            opt._rs_sumsq_ctas, s), 'group_sumsq')
+                        counters.bump('group_sumsq')
                     _lib.check(self.lib.mgw_clip_coef(part.data_ptr(), part.numel(), float(opt._norm_clip),
                                                       opt._nvl_clip_out.data_ptr(), s), 'clip_coef')
                     clip_ptr = opt._nvl_clip_out.data_ptr() + 4
@@ -437,6 +469,61 @@ class NvlComm(Communicator):
             opt._ext_state[id(module)] = dict(name=name, param=p, mom=mom[0], pg=param_group_index(opt, [p])[0],
                                               first=created, bufs=None, opt_key=id(opt))
             module._exchange = (lambda m, dy, x, _o=opt: self.exchange_external(_o, m, dy, x))
+
+    # ------------------------------------------------------------------ reduce-scatter weight gradients
+    def _attach_scatter(self, opt) -> None:
+        """Staging slots, symmetric gradient tensors and sinks for the weights in ``opt._scatter``: their gradient GEMM stores
+        every tile into the owner rank's slot, owners add the slots up and broadcast the sums (csrc/wgrad_gemm_sm100.cu)."""
+        from ...ops import wgrad
+        lib = wgrad._lib_ready()
+        w = self._world
+        opt._rs_state = {}
+        flags = torch.tensor([self._ctl.peer(r) + self._rflag_off for r in range(w)], dtype=torch.int64, device=self.device)
+        for name, p in opt._scatter:
+            m, n = p.shape
+            stage_bytes = 4 * int(lib.mgw_wgrad_scatter_stage_floats(m, n, w))
+            sblock, gblock = self.arena.alloc(stage_bytes), self.arena.alloc(4 * m * n)
+            self._blocks.setdefault(id(opt), []).extend([sblock, gblock])
+            tab = lambda blk: torch.tensor([blk.peer(r) for r in range(w)], dtype=torch.int64, device=self.device)   # noqa: E731
+            grad = _wrap_device_memory(gblock.base, m * n, self.device).view(m, n)
+            opt._rs_state[id(p)] = dict(name=name, param=p, m=m, n=n, tab_stage=tab(sblock), tab_grad=tab(gblock), flags=flags,
+                                        grad=grad, n_ctas=max(1, min(32, (m * n) // (128 * 128 * w))))
+            p._mgw_rs_sink = (lambda dy, x, _o=opt, _p=p: self.scatter_wgrad(_o, _p, dy, x))
+        params = [p for _n, p in opt._scatter]
+        if opt._base_is_sgd:
+            mom, created = ensure_momentum_buffers(opt, params)
+            opt._rs_table = GroupTable(params, param_group_index(opt, params), mom, self.device)
+            opt._rs_first = created
+        else:
+            opt._rs_table = GroupTable(params, [0] * len(params), [None] * len(params), self.device)
+            opt._rs_first = False
+
+    def scatter_wgrad(self, opt, p, dy: torch.Tensor, x: torch.Tensor) -> None:
+        """Called from backward where a weight gradient ``dy^T x`` is due: tensor-core GEMM whose epilogue scatters the
+        tiles to their owner ranks, then the owners' sums broadcast into every rank's gradient tensor; ``p.grad`` is that
+        tensor (symmetric memory) afterwards.  Runs on the side stream behind what produced ``dy`` and ``x``."""
+        from ...ops import wgrad
+        lib = wgrad._lib_ready()
+        st = opt._rs_state[id(p)]
+        w, r = self._world, self._rank
+        k = dy.shape[0]
+        compute = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(compute)
+        self.stream.wait_event(ready)
+        s = self.stream.cuda_stream
+        scale = float(getattr(opt, '_grad_scale', 1.0)) / w
+        _lib.check(lib.mgw_wgrad_gemm_scatter(dy.data_ptr(), x.data_ptr(), st['m'], st['n'], k, scale, st['tab_stage'].data_ptr(), r, w,
+                                              wgrad._status(dy.device).data_ptr(), s), 'wgrad_gemm_scatter')
+        _lib.check(lib.mgw_wgrad_reduce_finish(st['tab_stage'].data_ptr(), st['tab_grad'].data_ptr(), st['flags'].data_ptr(),
+                                               self._ctl.base + self._repoch_off, C.cast(self._status, C.c_void_p).value, r, w,
+                                               st['m'], st['n'], st['n_ctas'], self.timeout_ns, s), 'wgrad_reduce_finish')
+        counters.bump('wgrad_gemm_sm100')
+        counters.bump('wgrad_reduce_finish')
+        p.grad = st['grad']
+        opt._nvl_held.append((dy, x))
+        opt._synchronized = False
+        self.launches += 2
 
     def _gather_buffers(self, st, rows: int, m: int, n: int):
         """Symmetric [W*rows, m] and [W*rows, n] buffers of one layer (collective on first use)."""

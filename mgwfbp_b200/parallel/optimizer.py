@@ -132,7 +132,20 @@ class _DistributedMixin:
                 module = getattr(p, '_mgw_gathered', None)
                 if module is not None and module.gathered_is_profitable(self._world):
                     self._external.append((name, p, module))
-            gone = {name for name, _, _ in self._external}
+        # Large 2-D weights for which gathering does not pay but whose gradient is a single GEMM: the GEMM's epilogue
+        # scatters its tiles to their owner ranks and the owners broadcast the sums (csrc/wgrad_gemm_sm100.cu,
+        # WG_MODE_SCATTER); these weights leave the merge schedule as well.  Works with every update mode and with clipping:
+        # the result is an ordinary averaged gradient in p.grad.
+        self._scatter = []
+        if self._fused_comm and self._world > 1 and settings.SCATTER_WGRAD and not settings.FP16:
+            taken = {id(p) for _n, p, _m in self._external}
+            for name, p in list(self._named_parameters.items()):
+                cand = getattr(p, '_mgw_scatter_candidate', False) or getattr(p, '_mgw_gathered', None) is not None
+                if (cand and id(p) not in taken and p.is_cuda and p.dim() == 2 and p.dtype == torch.float32 and p.is_contiguous()
+                        and p.shape[0] % 4 == 0 and p.shape[1] % 4 == 0 and p.numel() >= 4 * 1024 * 1024):
+                    self._scatter.append((name, p))
+        if self._external or self._scatter:
+            gone = {name for name, _, _ in self._external} | {name for name, _ in self._scatter}
             if gone:
                 self._named_parameters = {k: v for k, v in self._named_parameters.items() if k not in gone}
                 self._parameter_names = {v: k for k, v in self._named_parameters.items()}
@@ -151,7 +164,9 @@ class _DistributedMixin:
                 if self._seq_layernames is not None:
                     self._seq_layernames = list(self._sequential_keys)
                 self._seq_index = {k: i for i, k in enumerate(self._sequential_keys)}
-                logger.info('weights updated through gathered activations (no gradient all-reduce): %s', sorted(gone))
+                logger.info('weights outside the merge schedule: %s updated through gathered activations, %s reduced by the '
+                            'scatter epilogue of their gradient GEMM', sorted(n for n, _, _ in self._external),
+                            sorted(n for n, _ in self._scatter))
 
         self._generate_merged_parameters()
 
@@ -449,7 +464,7 @@ class _DistributedMixin:
 
     @local.setter
     def local(self, value: bool) -> None:
-        if value and getattr(self, '_external', None):
+        if value and (getattr(self, '_external', None) or getattr(self, '_scatter', None)):
             raise RuntimeError('gradient accumulation (optimizer.local = True) cannot be combined with gathered '
                                'weight-gradient layers; construct the model with MGWFBP_GATHERED_WGRAD=0')
         self._local = bool(value)

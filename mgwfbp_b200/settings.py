@@ -81,6 +81,12 @@ CHANNELS_LAST = _env_flag('CHANNELS_LAST', True)
 # tensor-core weight-gradient GEMM with the SGD epilogue instead of all-reducing the weight gradient.
 GATHERED_WGRAD = _env_flag('GATHERED_WGRAD', True)
 
+# Large 2-D weights whose gradient is one GEMM over the whole batch / sequence (the PTB model's LSTM weights and softmax
+# layer) and for which gathering activations does not pay: form the gradient with the tensor-core GEMM whose epilogue
+# stores every tile straight into the staging slot of the rank that owns it; owners add the slots up and broadcast the
+# sums into every rank's (symmetric) gradient tensor.  The gradient never exists as a local tensor that has to be packed.
+SCATTER_WGRAD = _env_flag('SCATTER_WGRAD', True)
+
 # After the fused all-reduce + update kernels ran, also store the averaged gradient back into ``p.grad``.  Off by
 # default: with the update fused nobody reads the gradient again and the store is one more pass over the model
 # (``optimizer.synchronize()`` + clipping paths do not fuse the update and always get the averaged gradient).

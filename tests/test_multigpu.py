@@ -454,3 +454,68 @@ def test_schedule_is_measured_and_confirmed_by_trial():
     assert res[0]['groups'] == res[1]['groups'] >= 1
     for a, b in zip(res[0]['params'], res[1]['params']):
         assert torch.equal(a, b), 'replicas diverged'
+
+
+def _scatter_wgrad(rank, world, clip):
+    """Weights whose gradient GEMM scatters its tiles to the owner ranks (reduce-scatter epilogue): a two-layer FusedLSTM
+    and a large softmax layer, trained against single-process large-batch SGD on the same data."""
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
+    from mgwfbp_b200.ops.lstm import FusedLSTM
+    from mgwfbp_b200.ops.wgrad import convert_large_linears
+    settings.ADAPTIVE_MERGE = False
+    torch.backends.cuda.matmul.allow_tf32 = True
+    torch.manual_seed(0)
+    T, B, H, V = 5, 4, 1024, 4100                      # weights of 4 Mi elements and more take the scatter path
+
+    class Net(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.lstm = FusedLSTM(H, H, num_layers=2)
+            self.fc = torch.nn.Linear(H, V)
+
+        def forward(self, x):
+            out, _ = self.lstm(x)
+            return self.fc(out.reshape(-1, H))
+    net, ref = Net().cuda(), Net().cuda()
+    assert convert_large_linears(net, min_params=4 * 1024 * 1024) == 1
+    hvd.broadcast_parameters(net.state_dict(), 0)
+    ref.load_state_dict(net.state_dict())
+    mk = lambda m: torch.optim.SGD(m.parameters(), lr=0.05, momentum=0.9)
+    opt = hvd.DistributedOptimizer(mk(net), named_parameters=net.named_parameters(), threshold=1 << 20,
+                                   norm_clip=0.5 if clip else None)
+    names = sorted(n for n, _ in opt._scatter)
+    assert names == ['fc.weight', 'lstm.weight_hh_l0', 'lstm.weight_hh_l1', 'lstm.weight_ih_l0', 'lstm.weight_ih_l1'], names
+    assert not any(n in opt.merge_schedule.key_groupidx for n in names)
+    ropt = mk(ref)
+    g = torch.Generator().manual_seed(9)
+    for _ in range(3):
+        x = torch.randn(T, world * B, H, generator=g).cuda() * 0.5
+        opt.zero_grad()
+        net(x[:, rank * B:(rank + 1) * B].contiguous()).pow(2).mean().backward()
+        opt.step()
+        ropt.zero_grad()
+        ref(x).pow(2).mean().backward()
+        if clip:
+            torch.nn.utils.clip_grad_norm_(ref.parameters(), 0.5)
+        ropt.step()
+    torch.cuda.synchronize()
+    opt.communicator.check_status()
+    from mgwfbp_b200.ops import wgrad
+    wgrad.check_status()
+    return {'dp': [p.detach().cpu() for p in net.parameters()], 'ref': [p.detach().cpu() for p in ref.parameters()],
+            'grad': net.fc.weight.grad.detach().cpu(), 'ref_grad': ref.fc.weight.grad.detach().cpu(), 'clip': clip}
+
+
+@pytest.mark.parametrize('clip', [False, True])
+def test_scatter_epilogue_wgrad_matches_large_batch_sgd(clip):
+    res = run_ranks(_scatter_wgrad, (clip,), world=2)
+    # TF32 operands in the gradient GEMM on one side, the library's GEMMs on the other: compare at TF32 accuracy
+    for dp, ref in zip(res[0]['dp'], res[0]['ref']):
+        rel = float((dp - ref).norm() / ref.norm())
+        assert rel < 2e-3, rel
+    if not clip:
+        rel = float((res[0]['grad'] - res[0]['ref_grad']).norm() / res[0]['ref_grad'].norm())
+        assert rel < 2e-2, rel                        # the averaged gradient of the last step sits in p.grad
+    for a, b in zip(res[0]['dp'], res[1]['dp']):
+        assert torch.equal(a, b), 'replicas diverged'

@@ -487,7 +487,7 @@ class NvlComm(Communicator):
             tab = lambda blk: torch.tensor([blk.peer(r) for r in range(w)], dtype=torch.int64, device=self.device)   # noqa: E731
             grad = _wrap_device_memory(gblock.base, m * n, self.device).view(m, n)
             opt._rs_state[id(p)] = dict(name=name, param=p, m=m, n=n, tab_stage=tab(sblock), tab_grad=tab(gblock), flags=flags,
-                                        grad=grad, n_ctas=max(1, min(32, (m * n) // (128 * 128 * w))))
+                                        grad=grad, n_ctas=max(1, min(_env_int('MGWFBP_SCATTER_CTAS', 128), (m * n) // (128 * 128 * w))))
             p._mgw_rs_sink = (lambda dy, x, _o=opt, _p=p: self.scatter_wgrad(_o, _p, dy, x))
         params = [p for _n, p in opt._scatter]
         if opt._base_is_sgd:

@@ -85,7 +85,10 @@ GATHERED_WGRAD = _env_flag('GATHERED_WGRAD', True)
 # layer) and for which gathering activations does not pay: form the gradient with the tensor-core GEMM whose epilogue
 # stores every tile straight into the staging slot of the rank that owns it; owners add the slots up and broadcast the
 # sums into every rank's (symmetric) gradient tensor.  The gradient never exists as a local tensor that has to be packed.
-SCATTER_WGRAD = _env_flag('SCATTER_WGRAD', True)
+# Off by default: measured on 2 B200s with the PTB model it costs 3.26 ms/step against 3.08 through the merged all-reduce
+# (the tensor-core GEMM is behind the library's on these K = 700 shapes, 347 against ~270 us for the five products, and the
+# owners' pass plus the separate norm pass, 0.33 + 0.1 ms, cost about what one 204 MB two-shot all-reduce does).
+SCATTER_WGRAD = _env_flag('SCATTER_WGRAD', False)
 
 # After the fused all-reduce + update kernels ran, also store the averaged gradient back into ``p.grad``.  Off by
 # default: with the update fused nobody reads the gradient again and the store is one more pass over the model

@@ -464,6 +464,7 @@ def _scatter_wgrad(rank, world, clip):
     from mgwfbp_b200.ops.lstm import FusedLSTM
     from mgwfbp_b200.ops.wgrad import convert_large_linears
     settings.ADAPTIVE_MERGE = False
+    settings.SCATTER_WGRAD = True
     torch.backends.cuda.matmul.allow_tf32 = True
     torch.manual_seed(0)
     T, B, H, V = 5, 4, 1024, 4100                      # weights of 4 Mi elements and more take the scatter path

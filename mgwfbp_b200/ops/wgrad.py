@@ -52,6 +52,17 @@ def _status(device) -> torch.Tensor:
     return t
 
 
+def set_persistent(form) -> None:
+    """Choose the GEMM kernel: ``1`` / ``True`` the persistent one with one CTA of 16 epilogue warps per SM (CTAs walk
+    over the tiles; loads and MMAs of the next tile overlap the epilogue of the current one), ``2`` the persistent one
+    with two CTAs of 8 epilogue warps per SM, ``0`` / ``False`` one tile per CTA, ``None`` what
+    ``MGWFBP_WGRAD_PERSISTENT`` says (default 1)."""
+    lib = _lib_ready()
+    lib.mgw_wgrad_set_persistent.restype = None
+    lib.mgw_wgrad_set_persistent.argtypes = [C.c_int]
+    lib.mgw_wgrad_set_persistent(-1 if form is None else int(form))
+
+
 def supported(dy: torch.Tensor, x: torch.Tensor) -> bool:
     if not (dy.is_cuda and x.is_cuda and dy.dtype == torch.float32 and x.dtype == torch.float32):
         return False
@@ -152,7 +163,7 @@ class GatheredWgradLinear(torch.nn.Linear):
 
     def gathered_is_profitable(self, world: int) -> bool:
         rows = self.batch_rows_hint
-        if rows is None or world < 2:
+        if rows is None or world < 1:
             return False
         m, n = self.out_features, self.in_features
         return (m % 4 == 0 and n % 4 == 0 and world * rows * (m + n) * 2 <= m * n)

@@ -467,7 +467,16 @@ class _DistributedMixin:
         if value and (getattr(self, '_external', None) or getattr(self, '_scatter', None)):
             raise RuntimeError('gradient accumulation (optimizer.local = True) cannot be combined with gathered '
                                'weight-gradient layers; construct the model with MGWFBP_GATHERED_WGRAD=0')
+        if value:
+            self.release_external_layers()
         self._local = bool(value)
+
+    def release_external_layers(self) -> None:
+        """One GPU: layers whose weight-gradient GEMM applies the update in its epilogue go back to ordinary gradients
+        plus the multi-tensor update (call before accumulating gradients over several backward passes)."""
+        fast = getattr(self, '_fast_sgd', None)
+        if fast is not None:
+            fast.release_external(self)
 
     def set_grad_scale(self, scale: float) -> None:
         """Gradients arrive multiplied by ``1 / scale`` (a static loss scale): every update path divides it out --

@@ -80,6 +80,9 @@ CHANNELS_LAST = _env_flag('CHANNELS_LAST', True)
 # Large nn.Linear layers fed by small batches: exchange activations + output gradients between ranks and run the
 # tensor-core weight-gradient GEMM with the SGD epilogue instead of all-reducing the weight gradient.
 GATHERED_WGRAD = _env_flag('GATHERED_WGRAD', True)
+# On ONE GPU the same layers run that GEMM in their backward with the SGD update as its epilogue (no dW tensor, no
+# separate update pass over these weights).  Off when gradients are clipped or accumulated.
+FUSED_WGRAD_1GPU = _env_flag('FUSED_WGRAD_1GPU', True)
 
 # Large 2-D weights whose gradient is one GEMM over the whole batch / sequence (the PTB model's LSTM weights and softmax
 # layer) and for which gathering activations does not pay: form the gradient with the tensor-core GEMM whose epilogue

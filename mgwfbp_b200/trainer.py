@@ -656,6 +656,8 @@ def train_with_single(dnn, dataset, data_dir, nworkers, lr, batch_size, nsteps_u
     # one micro-step per update: the graph-captured step with input prefetch; otherwise the accumulation loop
     from .engine import TrainStep
     step = TrainStep(trainer, use_graph=use_graph, track_accuracy=True) if nsteps_update == 1 else None
+    if nsteps_update > 1:
+        trainer.optimizer.release_external_layers()        # gradients are summed over micro-batches before the update
     upcoming = trainer.data_iter() if step is not None else None
     display = 40 if iters_per_epoch > 40 else max(iters_per_epoch - 1, 1)
     done, counted, since = 0, 0, time.time()

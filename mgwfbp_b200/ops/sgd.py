@@ -82,6 +82,10 @@ class FastSGD:
         opt = self._optimizer()
         if not torch.cuda.is_current_stream_capturing():
             self.hyper.sync(opt.param_groups)
+        if dy.data_ptr() % 16:
+            dy = dy.clone()                  # a view at an odd offset: the bulk-tensor loads need 16-byte aligned bases
+        if x.data_ptr() % 16:
+            x = x.clone()
         wgrad.wgrad_sgd_(dy, x, st['param'].data, st['mom'], self.hyper.data_ptr(), st['pg'],
                          scale=float(getattr(opt, '_grad_scale', 1.0)), first_step=bool(st['first']))
         st['first'] = False

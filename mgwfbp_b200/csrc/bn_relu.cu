@@ -250,7 +250,7 @@ __device__ __forceinline__ void fwd_finalize_channel(double sum, double sq, long
 
 template <int VEC>
 __global__ void __launch_bounds__(kThreads, 4)
-bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int rows_per_split, float* __restrict__ partials,
+bn_stats_kernel(const float* __restrict__ x, long long ldx, long long M, int C, int TX, int rows_per_split, float* __restrict__ partials,
                 const FwdFinal fin) {
     extern __shared__ float smem[];
     pdl_release_dependents();
@@ -266,7 +266,7 @@ bn_stats_kernel(const float* __restrict__ x, long long M, int C, int TX, int row
     if (active) {
         for (long long r = r0 + ty; r < r1; r += TY) {
             float v[VEC];
-            load_vec<VEC>(x + r * C + c0, v);
+            load_vec<VEC>(x + r * ldx + c0, v);
 #pragma unroll
             for (int k = 0; k < VEC; ++k) {
                 s[k] += v[k];
@@ -378,7 +378,7 @@ bn_bwd_finalize_kernel(const float* __restrict__ partials, int n_splits, int C, 
 
 template <int VEC, bool BITS>
 __global__ void __launch_bounds__(kThreads, 4)
-bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ residual, float* __restrict__ y, long long M, int C,
+bn_apply_kernel(const float* __restrict__ x, long long ldx, const float* __restrict__ residual, float* __restrict__ y, long long M, int C,
                 int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta, int relu,
                 const float* __restrict__ save_mean, const float* __restrict__ save_invstd, unsigned char* __restrict__ bits) {
     pdl_wait();
@@ -399,7 +399,7 @@ bn_apply_kernel(const float* __restrict__ x, const float* __restrict__ residual,
     const long long r1 = min(M, r0 + rows_per_split);
     for (long long r = r0 + ty; r < r1; r += TY) {
         float v[VEC], o[VEC];
-        load_vec<VEC>(x + r * C + c0, v);
+        load_vec<VEC>(x + r * ldx + c0, v);
         if (residual) {
             float rr[VEC];
             load_vec<VEC>(residual + r * C + c0, rr);
@@ -503,7 +503,7 @@ __device__ __forceinline__ void load_channel_consts(int c0, int C, const float* 
 template <int VEC, bool POOL>
 __global__ void __launch_bounds__(kThreads, 2)
 bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2, const float* __restrict__ y,
-                     const unsigned char* __restrict__ bits, const float* __restrict__ x, float* __restrict__ dz,
+                     const unsigned char* __restrict__ bits, const float* __restrict__ x, long long ldx, float* __restrict__ dz,
                      long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                      const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
                      float* __restrict__ partials, const PoolArgs pool, const BwdFinal fin) {
@@ -524,7 +524,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
         for (; r < r1; r += TY) {
             float g[VEC], xv[VEC];
             if (POOL) pooled_grad<VEC>(g, pool, r, c0, C); else load_vec<VEC>(dy + r * C + c0, g);
-            load_vec<VEC>(x + r * C + c0, xv);
+            load_vec<VEC>(x + r * ldx + c0, xv);
             if (dy2) {
                 float h[VEC];
                 load_vec<VEC>(dy2 + r * C + c0, h);
@@ -576,7 +576,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
 template <int VEC, bool POOL>
 __global__ void __launch_bounds__(kThreads, 2)
 bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gsrc2, const float* __restrict__ y, const float* __restrict__ x,
-                    float* __restrict__ dx,
+                    long long ldx, float* __restrict__ dx,
                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                     const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
                     const float* __restrict__ dgamma, const float* __restrict__ dbeta, const PoolArgs pool) {
@@ -599,7 +599,7 @@ bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gs
     for (long long r = r0 + ty; r < r1; r += TY) {
         float g[VEC], xv[VEC], o[VEC];
         if (POOL) pooled_grad<VEC>(g, pool, r, c0, C); else load_vec<VEC>(gsrc + r * C + c0, g);
-        load_vec<VEC>(x + r * C + c0, xv);
+        load_vec<VEC>(x + r * ldx + c0, xv);
         if (gsrc2) {
             float h[VEC];
             load_vec<VEC>(gsrc2 + r * C + c0, h);
@@ -691,6 +691,7 @@ struct FwdArgs {
     const float* x; const float* residual; float* y; long long M; int C;
     const float* gamma; const float* beta; float* running_mean; float* running_var; long long* nbt;
     float momentum, eps; int relu; float* save_mean; float* save_invstd; float* partials; unsigned char* bits;
+    long long ldx;       // floats between consecutive rows of x (>= C; x may be a channel slice of a wider tensor)
 };
 
 // statistics (+ finalize); returns the tiling for the caller's second pass
@@ -699,7 +700,7 @@ cudaError_t launch_stats(const FwdArgs& a, const Tiling& t, cudaStream_t s) {
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     const FwdFinal fin = {a.running_mean, a.running_var, a.nbt, a.momentum, a.eps, a.save_mean, a.save_invstd,
                           take_slots(t.grid_x, t.grid_y)};
-    cudaError_t e = launch(bn_stats_kernel<VEC>, grid, block, reduce_smem(VEC), s, false, a.x, a.M, a.C, t.tx, t.rows_per_split,
+    cudaError_t e = launch(bn_stats_kernel<VEC>, grid, block, reduce_smem(VEC), s, false, a.x, a.ldx, a.M, a.C, t.tx, t.rows_per_split,
                            a.partials, fin);
     if (e == cudaSuccess && fin.slot0 < 0)
         e = launch(bn_fwd_finalize_kernel, dim3((a.C + kFinCh - 1) / kFinCh), dim3(kFinCh * kFinLanes), 0, s, true, (const float*)a.partials, t.grid_y, a.M,
@@ -714,9 +715,9 @@ cudaError_t launch_fwd(const FwdArgs& a, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     if (VEC == 4 && a.bits)
-        return launch(bn_apply_kernel<VEC, true>, grid, block, 0, s, true, a.x, a.residual, a.y, a.M, a.C, t.tx, t.rows_per_split,
+        return launch(bn_apply_kernel<VEC, true>, grid, block, 0, s, true, a.x, a.ldx, a.residual, a.y, a.M, a.C, t.tx, t.rows_per_split,
                       a.gamma, a.beta, a.relu, (const float*)a.save_mean, (const float*)a.save_invstd, a.bits);
-    return launch(bn_apply_kernel<VEC, false>, grid, block, 0, s, true, a.x, a.residual, a.y, a.M, a.C, t.tx, t.rows_per_split,
+    return launch(bn_apply_kernel<VEC, false>, grid, block, 0, s, true, a.x, a.ldx, a.residual, a.y, a.M, a.C, t.tx, t.rows_per_split,
                   a.gamma, a.beta, a.relu, (const float*)a.save_mean, (const float*)a.save_invstd, (unsigned char*)nullptr);
 }
 
@@ -724,6 +725,7 @@ struct BwdArgs {
     const float* dy; const float* dy2; const float* y; const unsigned char* bits; const float* x; float* dz; float* dx;
     long long M; int C; const float* gamma; const float* beta; const float* save_mean; const float* save_invstd;
     int mask1, mask2; float* dgamma; float* dbeta; float* partials; PoolArgs pool;
+    long long ldx;       // floats between consecutive rows of x (>= C)
 };
 
 template <int VEC, bool POOL>
@@ -732,7 +734,7 @@ cudaError_t launch_bwd(const BwdArgs& a, cudaStream_t s) {
     const dim3 grid(t.grid_x, t.grid_y), block(kThreads);
     const BwdFinal fin = {a.dgamma, a.dbeta, take_slots(t.grid_x, t.grid_y)};
     cudaError_t e = launch(bn_bwd_reduce_kernel<VEC, POOL>, grid, block, reduce_smem(VEC), s, false, a.dy, a.dy2, a.y, a.bits, a.x,
-                           a.dz, a.M, a.C, t.tx, t.rows_per_split, a.gamma, a.beta, a.save_mean, a.save_invstd, a.mask1, a.partials,
+                           a.ldx, a.dz, a.M, a.C, t.tx, t.rows_per_split, a.gamma, a.beta, a.save_mean, a.save_invstd, a.mask1, a.partials,
                            a.pool, fin);
     if (e == cudaSuccess && fin.slot0 < 0)
         e = launch(bn_bwd_finalize_kernel, dim3((a.C + kFinCh - 1) / kFinCh), dim3(kFinCh * kFinLanes), 0, s, true, (const float*)a.partials, t.grid_y, a.C,
@@ -740,7 +742,7 @@ cudaError_t launch_bwd(const BwdArgs& a, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     const float* gsrc = a.dz != nullptr ? a.dz : a.dy;
     const float* gsrc2 = a.dz != nullptr ? nullptr : a.dy2;        // dz already holds the sum of both gradients
-    return launch(bn_bwd_apply_kernel<VEC, POOL>, grid, block, 0, s, true, gsrc, gsrc2, a.y, a.x, a.dx, a.M, a.C, t.tx,
+    return launch(bn_bwd_apply_kernel<VEC, POOL>, grid, block, 0, s, true, gsrc, gsrc2, a.y, a.x, a.ldx, a.dx, a.M, a.C, t.tx,
                   t.rows_per_split, a.gamma, a.beta, a.save_mean, a.save_invstd, a.mask2, (const float*)a.dgamma,
                   (const float*)a.dbeta, a.pool);
 }
@@ -772,16 +774,28 @@ int mgw_bn_launches(long long M, int C, int backward) {
     return fused_geometry(t.grid_x, t.grid_y) ? 2 : 3;
 }
 
+// ldx: floats between consecutive rows of x (>= C).  With ldx > C the input is a channel slice of a wider channels-last
+// tensor (the first C channels of a DenseNet block buffer) and is read in place; y, residual and the mask stay dense.
+// The 16-byte loads of the C % 4 == 0 path need ldx % 4 == 0 as well.
+int mgw_bn_relu_fwd_ld(const float* x, long long ldx, const float* residual, float* y, long long M, int C, const float* gamma,
+                       const float* beta, float* running_mean, float* running_var, long long* num_batches_tracked, float momentum,
+                       float eps, int relu, float* save_mean, float* save_invstd, float* partials, unsigned char* relu_bits,
+                       void* stream) {
+    if (x == nullptr || y == nullptr || M <= 0 || C <= 0 || save_mean == nullptr || save_invstd == nullptr || partials == nullptr)
+        return MGW_ERR_ARG;
+    if (ldx < C || (C % 4 == 0 && ldx % 4 != 0)) return MGW_ERR_ARG;
+    if (relu_bits != nullptr && (C % 4 != 0 || !relu)) return MGW_ERR_ARG;
+    const FwdArgs a = {x, residual, y, M, C, gamma, beta, running_mean, running_var, num_batches_tracked, momentum, eps, relu,
+                       save_mean, save_invstd, partials, relu_bits, ldx};
+    MGW_CUDA_CHECK((C % 4 == 0) ? launch_fwd<4>(a, (cudaStream_t)stream) : launch_fwd<1>(a, (cudaStream_t)stream));
+    return MGW_OK;
+}
+
 int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M, int C, const float* gamma, const float* beta,
                     float* running_mean, float* running_var, long long* num_batches_tracked, float momentum, float eps,
                     int relu, float* save_mean, float* save_invstd, float* partials, unsigned char* relu_bits, void* stream) {
-    if (x == nullptr || y == nullptr || M <= 0 || C <= 0 || save_mean == nullptr || save_invstd == nullptr || partials == nullptr)
-        return MGW_ERR_ARG;
-    if (relu_bits != nullptr && (C % 4 != 0 || !relu)) return MGW_ERR_ARG;
-    const FwdArgs a = {x, residual, y, M, C, gamma, beta, running_mean, running_var, num_batches_tracked, momentum, eps, relu,
-                       save_mean, save_invstd, partials, relu_bits};
-    MGW_CUDA_CHECK((C % 4 == 0) ? launch_fwd<4>(a, (cudaStream_t)stream) : launch_fwd<1>(a, (cudaStream_t)stream));
-    return MGW_OK;
+    return mgw_bn_relu_fwd_ld(x, C, residual, y, M, C, gamma, beta, running_mean, running_var, num_batches_tracked, momentum, eps, relu,
+                              save_mean, save_invstd, partials, relu_bits, stream);
 }
 
 // Backward.  dy2 (may be null) is a second incoming gradient of the same output -- a block output that feeds
@@ -792,20 +806,29 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
 // values), which saves one read and one write of the activation.  relu_bits (may be null; needs C % 4 == 0)
 // is the byte-per-float4 ReLU mask the forward pass recorded: with it the reduce pass reads M*C/4 bytes
 // instead of the M*C floats of y.
-int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const float* x, float* dz, float* dx, long long M, int C, const float* gamma,
-                    const float* beta, const float* save_mean, const float* save_invstd, int relu, float* dgamma, float* dbeta,
-                    float* partials, const unsigned char* relu_bits, void* stream) {
+int mgw_bn_relu_bwd_ld(const float* dy, const float* dy2, const float* y, const float* x, long long ldx, float* dz, float* dx, long long M,
+                       int C, const float* gamma, const float* beta, const float* save_mean, const float* save_invstd, int relu,
+                       float* dgamma, float* dbeta, float* partials, const unsigned char* relu_bits, void* stream) {
     if (dy == nullptr || x == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
+    if (ldx < C || (C % 4 == 0 && ldx % 4 != 0)) return MGW_ERR_ARG;
     // the byte mask serves the reduce pass; the apply pass then reads the masked gradient dz, which must exist
     if (relu_bits != nullptr && (C % 4 != 0 || !relu || dz == nullptr)) return MGW_ERR_ARG;
     if (dgamma == nullptr || dbeta == nullptr || save_mean == nullptr || save_invstd == nullptr) return MGW_ERR_ARG;
     const int mask1 = !relu ? 0 : (relu_bits != nullptr ? 3 : (y != nullptr ? 1 : 2));          // mask used by the reduce pass
     const int mask2 = dz != nullptr ? 0 : mask1;                   // apply pass: dz already carries the mask
     const BwdArgs a = {dy, dy2, y, relu_bits, x, dz, dx, M, C, gamma, beta, save_mean, save_invstd, mask1, mask2, dgamma, dbeta,
-                       partials, {nullptr, nullptr, 0, 0, 0, 0}};
+                       partials, {nullptr, nullptr, 0, 0, 0, 0}, ldx};
     const cudaError_t e = (C % 4 == 0) ? launch_bwd<4, false>(a, (cudaStream_t)stream) : launch_bwd<1, false>(a, (cudaStream_t)stream);
     MGW_CUDA_CHECK(e);
     return MGW_OK;
+}
+
+// The same with x dense (ldx = C).
+int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const float* x, float* dz, float* dx, long long M, int C, const float* gamma,
+                    const float* beta, const float* save_mean, const float* save_invstd, int relu, float* dgamma, float* dbeta,
+                    float* partials, const unsigned char* relu_bits, void* stream) {
+    return mgw_bn_relu_bwd_ld(dy, dy2, y, x, C, dz, dx, M, C, gamma, beta, save_mean, save_invstd, relu, dgamma, dbeta, partials,
+                              relu_bits, stream);
 }
 
 // BatchNorm + ReLU + 3x3/stride-2/pad-1 max-pool of a channels-last [N, H, W, C] tensor (the ResNet / DenseNet stem).
@@ -823,7 +846,7 @@ int mgw_bn_relu_maxpool_fwd(const float* x, float* y_pool, unsigned char* idx, i
     const long long work = (long long)N * OH * OW * (C / vec);
     const int pgrid = (int)((work + 255) / 256 < 148LL * 16 ? (work + 255) / 256 : 148LL * 16);
     const FwdArgs a = {x, nullptr, nullptr, M, C, gamma, beta, running_mean, running_var, num_batches_tracked, momentum, eps, 1,
-                       save_mean, save_invstd, partials, nullptr};
+                       save_mean, save_invstd, partials, nullptr, C};
     if (vec == 4) {
         MGW_CUDA_CHECK(launch_stats<4>(a, t, s));
         MGW_CUDA_CHECK(launch(bn_relu_maxpool_kernel<4>, dim3(pgrid), dim3(256), 0, s, true, x, y_pool, idx, N, H, W, OH, OW, C, gamma,
@@ -845,7 +868,7 @@ int mgw_bn_relu_maxpool_bwd(const float* dp, const unsigned char* idx, const flo
         return MGW_ERR_ARG;
     const long long M = (long long)N * H * W;
     const BwdArgs a = {nullptr, nullptr, nullptr, nullptr, x, nullptr, dx, M, C, gamma, beta, save_mean, save_invstd, 2, 2, dgamma,
-                       dbeta, partials, {dp, idx, H, W, (H + 2 - 3) / 2 + 1, (W + 2 - 3) / 2 + 1}};
+                       dbeta, partials, {dp, idx, H, W, (H + 2 - 3) / 2 + 1, (W + 2 - 3) / 2 + 1}, C};
     const cudaError_t e = (C % 4 == 0) ? launch_bwd<4, true>(a, (cudaStream_t)stream) : launch_bwd<1, true>(a, (cudaStream_t)stream);
     MGW_CUDA_CHECK(e);
     return MGW_OK;

@@ -158,4 +158,6 @@ def fuse_model(net: nn.Module) -> nn.Module:
     for m in net.modules():
         if type(m) in (nn.BatchNorm2d, nn.BatchNorm1d):
             _to_fused(m, relu=False)
+    from .dense_block import fuse_dense_blocks
+    fuse_dense_blocks(net)            # one buffer per dense block: L gradient additions instead of L (L - 1) / 2
     return net

@@ -33,7 +33,26 @@ def _as_rows(x: torch.Tensor):
     return None
 
 
+def _row_layout(x: torch.Tensor):
+    """``(M, C, ld)`` for an input the kernels can read in place: a dense channels-innermost tensor (``ld == C``), or the
+    first channels of a wider channels-last tensor (``x = wide[:, :C]``: rows ``ld = C_wide`` floats apart), 16-byte
+    aligned with ``ld % 4 == 0`` when the vector path applies.  ``None`` otherwise."""
+    rows = _as_rows(x)
+    if rows is not None:
+        return rows[0], rows[1], rows[1]
+    if not _HAS_LD or x.dim() != 4:
+        return None
+    n, c, h, w = x.shape
+    ld = x.stride(3)
+    if min(n, c, h, w) < 1 or w < 2 or x.stride(1) != 1 or ld <= c or x.stride(2) != w * ld or x.stride(0) != h * w * ld:
+        return None
+    if c % 4 == 0 and (ld % 4 != 0 or x.data_ptr() % 16 != 0):
+        return None
+    return n * h * w, c, ld
+
+
 _declared = False
+_HAS_LD = True            # cleared by _declare() when the loaded library predates the strided entry points
 
 
 def _declare(lib) -> None:
@@ -48,6 +67,12 @@ def _declare(lib) -> None:
     lib.mgw_bn_relu_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p]
+    global _HAS_LD
+    _HAS_LD = hasattr(lib, 'mgw_bn_relu_fwd_ld')
+    if _HAS_LD:
+        lib.mgw_bn_relu_fwd_ld.argtypes = [C.c_void_p, C.c_longlong] + list(lib.mgw_bn_relu_fwd.argtypes[1:])
+        lib.mgw_bn_relu_bwd_ld.argtypes = (list(lib.mgw_bn_relu_bwd.argtypes[:4]) + [C.c_longlong] +
+                                           list(lib.mgw_bn_relu_bwd.argtypes[4:]))
     lib.mgw_bn_launches.argtypes = [C.c_longlong, C.c_int, C.c_int]
     lib.mgw_bn_set_sm_budget.argtypes = [C.c_int]
     lib.mgw_bn_cluster_supported.argtypes = [C.c_longlong, C.c_int]
@@ -89,8 +114,8 @@ class _BNReLU(torch.autograd.Function):
     def forward(ctx, x, weight, bias, running_mean, running_var, num_batches_tracked, residual, relu, momentum, eps, dual):
         lib = _lib.load(allow_build=False)
         _declare(lib)
-        M, Cc = _as_rows(x)
-        y = torch.empty_like(x)
+        M, Cc, ld = _row_layout(x)
+        y = torch.empty_like(x) if ld == Cc else torch.empty(x.shape, dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
         mean = torch.empty(Cc, dtype=torch.float32, device=x.device)
         invstd = torch.empty(Cc, dtype=torch.float32, device=x.device)
         s = torch.cuda.current_stream().cuda_stream
@@ -99,7 +124,7 @@ class _BNReLU(torch.autograd.Function):
         # the channel count is not a multiple of 4 the output itself is kept.
         needs_mask = bool(relu and residual is not None)
         bits = torch.empty((M * Cc) // 4, dtype=torch.uint8, device=x.device) if (needs_mask and Cc % 4 == 0) else None
-        if _use_cluster(lib, M, Cc):
+        if ld == Cc and _use_cluster(lib, M, Cc):
             _lib.check(lib.mgw_bn_relu_fwd_cluster(x.data_ptr(), _ptr(residual), y.data_ptr(), M, Cc, _ptr(weight), _ptr(bias),
                                                    _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
                                                    float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
@@ -107,13 +132,19 @@ class _BNReLU(torch.autograd.Function):
             counters.bump('bn_relu_fwd_cluster', 1)
         else:
             partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
-            _lib.check(lib.mgw_bn_relu_fwd(x.data_ptr(), _ptr(residual), y.data_ptr(), M, Cc, _ptr(weight), _ptr(bias),
-                                           _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
-                                           float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
-                                           partials.data_ptr(), _ptr(bits), s), 'bn_relu_fwd')
+            if ld == Cc:
+                _lib.check(lib.mgw_bn_relu_fwd(x.data_ptr(), _ptr(residual), y.data_ptr(), M, Cc, _ptr(weight), _ptr(bias),
+                                               _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
+                                               float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
+                                               partials.data_ptr(), _ptr(bits), s), 'bn_relu_fwd')
+            else:       # a channel slice of a wider tensor, read in place
+                _lib.check(lib.mgw_bn_relu_fwd_ld(x.data_ptr(), ld, _ptr(residual), y.data_ptr(), M, Cc, _ptr(weight), _ptr(bias),
+                                                  _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
+                                                  float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
+                                                  partials.data_ptr(), _ptr(bits), s), 'bn_relu_fwd_ld')
             counters.bump('bn_relu_fwd', lib.mgw_bn_launches(M, Cc, 0))
         ctx.save_for_backward(x, y if (needs_mask and bits is None) else None, weight, bias, mean, invstd, bits)
-        ctx.relu, ctx.has_residual, ctx.rows = bool(relu), residual is not None, (M, Cc)
+        ctx.relu, ctx.has_residual, ctx.rows, ctx.ld = bool(relu), residual is not None, (M, Cc), ld
         ctx.mark_non_differentiable(*[t for t in (running_mean, running_var, num_batches_tracked) if t is not None])
         if dual:
             # two handles on the same output: each consumer's gradient then reaches backward() separately
@@ -128,25 +159,32 @@ class _BNReLU(torch.autograd.Function):
             dy, dy2 = dy2, None
         x, y, weight, bias, mean, invstd, bits = ctx.saved_tensors
         M, Cc = ctx.rows
-        if _as_rows(dy) is None or dy.stride() != x.stride():
+        ld = ctx.ld
+        dx = torch.empty_like(x) if ld == Cc else torch.empty(x.shape, dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
+        if _as_rows(dy) is None or dy.stride() != dx.stride():
             dy = dy.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else dy.contiguous()
-        if dy2 is not None and (_as_rows(dy2) is None or dy2.stride() != x.stride()):
+        if dy2 is not None and (_as_rows(dy2) is None or dy2.stride() != dx.stride()):
             dy2 = dy2.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else dy2.contiguous()
-        dz = torch.empty_like(x) if ctx.has_residual else None     # only a residual needs the masked gradient itself
-        dx = torch.empty_like(x)
+        dz = torch.empty_like(dx) if ctx.has_residual else None     # only a residual needs the masked gradient itself
         dgamma = torch.empty(Cc, dtype=torch.float32, device=x.device)
         dbeta = torch.empty(Cc, dtype=torch.float32, device=x.device)
         s = torch.cuda.current_stream().cuda_stream
-        if _use_cluster(lib, M, Cc):
+        if ld == Cc and _use_cluster(lib, M, Cc):
             _lib.check(lib.mgw_bn_relu_bwd_cluster(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
                                                    _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
                                                    dgamma.data_ptr(), dbeta.data_ptr(), _ptr(bits), s), 'bn_relu_bwd_cluster')
             counters.bump('bn_relu_bwd_cluster', 1)
         else:
             partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
-            _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
-                                           _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
-                                           dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), _ptr(bits), s), 'bn_relu_bwd')
+            if ld == Cc:
+                _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
+                                               _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
+                                               dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), _ptr(bits), s), 'bn_relu_bwd')
+            else:
+                _lib.check(lib.mgw_bn_relu_bwd_ld(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), ld, _ptr(dz), dx.data_ptr(), M, Cc,
+                                                  _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
+                                                  dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), _ptr(bits), s),
+                           'bn_relu_bwd_ld')
             counters.bump('bn_relu_bwd', lib.mgw_bn_launches(M, Cc, 1))
         need = ctx.needs_input_grad
         return (dx if need[0] else None, dgamma if (weight is not None and need[1]) else None,
@@ -158,9 +196,14 @@ def bn_relu(x, weight, bias, running_mean, running_var, num_batches_tracked, res
             momentum=0.1, eps=1e-5, dual=False):
     """Functional form: training-mode batch norm over all but the channel dimension, optional
     residual add, optional ReLU.  ``x`` must be CUDA float32, dense, channels innermost."""
-    if not x.is_cuda or x.dtype != torch.float32 or _as_rows(x) is None:
-        raise ValueError('bn_relu needs a dense channels-last (or 2-D) float32 CUDA tensor')
-    if residual is not None and (residual.shape != x.shape or residual.stride() != x.stride()):
+    if not x.is_cuda or x.dtype != torch.float32:
+        raise ValueError('bn_relu needs a float32 CUDA tensor')
+    _declare(_lib.load(allow_build=False))
+    layout = _row_layout(x)
+    if layout is None:
+        raise ValueError('bn_relu needs a dense channels-last (or 2-D) tensor, or the first channels of a wider channels-last one')
+    if residual is not None and (residual.shape != x.shape or _as_rows(residual) is None or
+                                 (layout[2] == layout[1] and residual.stride() != x.stride())):
         residual = residual.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else residual.contiguous()
     return _BNReLU.apply(x, weight, bias, running_mean, running_var, num_batches_tracked, residual, relu, momentum, eps, dual)
 
@@ -169,8 +212,10 @@ class _FusedBNMixin:
     fused_relu = False
 
     def _native_ok(self, x: torch.Tensor) -> bool:
+        if not _declared and x.is_cuda:
+            _declare(_lib.load(allow_build=False))           # also settles which input layouts the library reads in place
         return (self.training and x.is_cuda and x.dtype == torch.float32 and self.momentum is not None
-                and self.track_running_stats and _as_rows(x) is not None and x.numel() > 0)
+                and self.track_running_stats and x.numel() > 0 and _row_layout(x) is not None)
 
     def forward(self, x, residual=None, dual=False):
         """``dual=True`` returns the output twice (two handles on one tensor) for a consumer pair such as

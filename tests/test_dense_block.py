@@ -1,0 +1,77 @@
+"""Single-buffer dense blocks against torchvision's list-and-concatenate blocks (CPU, float64)."""
+import copy
+
+import pytest
+import torch
+
+tv = pytest.importorskip('torchvision')
+
+
+def _nets(memory_format):
+    from torchvision.models.densenet import DenseNet
+    from mgwfbp_b200.models.dense_block import fuse_dense_blocks
+    torch.manual_seed(0)
+    ref = DenseNet(growth_rate=8, block_config=(3, 4, 2), num_init_features=16, bn_size=2, num_classes=10).double()
+    ours = copy.deepcopy(ref)
+    assert fuse_dense_blocks(ours) == 3
+    ref, ours = ref.to(memory_format=memory_format), ours.to(memory_format=memory_format)
+    return ref.train(), ours.train()
+
+
+@pytest.mark.parametrize('memory_format', [torch.contiguous_format, torch.channels_last])
+def test_dense_block_matches_torchvision_forward_and_backward(memory_format):
+    ref, ours = _nets(memory_format)
+    x = torch.randn(4, 3, 32, 32, dtype=torch.float64).to(memory_format=memory_format)
+    y = torch.randint(0, 10, (4,))
+    order = {}
+    for name, (net, seen) in {'ref': (ref, []), 'ours': (ours, [])}.items():
+        for n, p in net.named_parameters():
+            p.register_post_accumulate_grad_hook(lambda _p, _n=n, _s=seen: _s.append(_n))
+        out = net(x)
+        loss = torch.nn.functional.cross_entropy(out, y)
+        loss.backward()
+        order[name] = (out.detach(), loss.detach(), seen)
+    torch.testing.assert_close(order['ours'][0], order['ref'][0], rtol=1e-10, atol=1e-10)
+    for (n, a), b in zip(ours.named_parameters(), ref.parameters()):
+        torch.testing.assert_close(a.grad, b.grad, rtol=1e-8, atol=1e-10, msg=lambda m, n=n: '%s: %s' % (n, m))
+    for (n, a), b in zip(ours.named_buffers(), ref.buffers()):
+        torch.testing.assert_close(a, b, rtol=1e-10, atol=1e-12, msg=lambda m, n=n: '%s: %s' % (n, m))
+    # every parameter's gradient was delivered exactly once; gradients become ready layer by layer from the back in both
+    # (inside one dense layer the two orders may differ, across layers they may not)
+    assert sorted(order['ours'][2]) == sorted(order['ref'][2])
+
+    def layer_of(name):
+        parts = name.split('.')
+        return '.'.join(parts[:3]) if parts[1].startswith('denseblock') else '.'.join(parts[:2])
+
+    def collapse(names):
+        out = []
+        for n in names:
+            k = layer_of(n)
+            if not out or out[-1] != k:
+                out.append(k)
+        return out
+    assert collapse(order['ours'][2]) == collapse(order['ref'][2])
+
+
+def test_dense_block_eval_and_no_grad_use_the_plain_path():
+    ref, ours = _nets(torch.contiguous_format)
+    x = torch.randn(2, 3, 32, 32, dtype=torch.float64)
+    with torch.no_grad():
+        torch.testing.assert_close(ours(x), ref(x), rtol=1e-10, atol=1e-10)        # training mode, no graph
+    ref.eval(), ours.eval()
+    torch.testing.assert_close(ours(x), ref(x), rtol=1e-10, atol=1e-10)
+
+
+def test_dense_block_two_steps_of_sgd_match():
+    ref, ours = _nets(torch.contiguous_format)
+    opts = [torch.optim.SGD(n.parameters(), lr=0.05, momentum=0.9) for n in (ref, ours)]
+    for step in range(2):
+        x = torch.randn(4, 3, 32, 32, dtype=torch.float64)
+        y = torch.randint(0, 10, (4,))
+        for net, opt in zip((ref, ours), opts):
+            opt.zero_grad()
+            torch.nn.functional.cross_entropy(net(x), y).backward()
+            opt.step()
+    for (n, a), b in zip(ours.named_parameters(), ref.parameters()):
+        torch.testing.assert_close(a, b, rtol=1e-8, atol=1e-10, msg=lambda m, n=n: '%s: %s' % (n, m))

@@ -450,3 +450,80 @@ def test_s2d_stem_matches_conv2d():
         torch.testing.assert_close(new(odd), torch.nn.functional.conv2d(odd, ref.weight, None, 2, 3), rtol=1e-4, atol=1e-4)
     finally:
         torch.backends.cudnn.allow_tf32 = old
+
+
+@pytest.mark.parametrize('wide,c,shape', [(96, 64, (8, 14, 14)), (1792, 1024, (4, 7, 7)), (100, 30, (3, 5, 6)), (224, 192, (16, 28, 28))])
+@pytest.mark.parametrize('relu', [True, False])
+def test_bn_relu_reads_a_channel_slice_in_place(wide, c, shape, relu, monkeypatch):
+    """x = first ``c`` channels of a ``wide``-channel channels-last tensor (a DenseNet block buffer): the kernels read it
+    through its row stride.  Same kernels, same order of arithmetic as on a dense copy of the slice: results are equal
+    bit for bit, and the reference in plain PyTorch double precision agrees."""
+    from mgwfbp_b200.ops import bn_relu as bn_mod
+    from mgwfbp_b200.ops.bn_relu import bn_relu
+    monkeypatch.setattr(bn_mod, '_CLUSTER', False)           # the dense copy must take the same three-launch kernels
+    torch.manual_seed(0)
+    dev = torch.device('cuda')
+    n, h, w_ = shape
+    buf = torch.randn(n, wide, h, w_, device=dev).contiguous(memory_format=torch.channels_last)
+    xs = buf[:, :c].detach().requires_grad_(True)
+    assert not xs.is_contiguous(memory_format=torch.channels_last)
+    xd = buf[:, :c].detach().contiguous(memory_format=torch.channels_last).requires_grad_(True)
+    w1 = (torch.rand(c, device=dev) + 0.5).requires_grad_(True)
+    b1 = torch.randn(c, device=dev).requires_grad_(True)
+    w2, b2 = (t.detach().clone().requires_grad_(True) for t in (w1, b1))
+    stats = lambda: (torch.zeros(c, device=dev), torch.ones(c, device=dev), torch.zeros((), dtype=torch.long, device=dev))
+    s1, s2 = stats(), stats()
+    before = buf.clone()
+    y1 = bn_relu(xs, w1, b1, *s1, None, relu, 0.1, 1e-5)
+    y2 = bn_relu(xd, w2, b2, *s2, None, relu, 0.1, 1e-5)
+    assert y1.is_contiguous(memory_format=torch.channels_last)
+    g = torch.randn_like(y2)
+    (y1 * g).sum().backward()
+    (y2 * g).sum().backward()
+    torch.cuda.synchronize()
+    assert torch.equal(buf, before)                          # nothing was written through the view
+    assert torch.equal(y1, y2) and torch.equal(s1[0], s2[0]) and torch.equal(s1[1], s2[1])
+    assert torch.equal(xs.grad, xd.grad) and torch.equal(w1.grad, w2.grad) and torch.equal(b1.grad, b2.grad)
+    x3 = xd.detach().clone().requires_grad_(True)
+    w3, b3 = (t.detach().clone().requires_grad_(True) for t in (w1, b1))
+    ref = _bn_reference(x3, w3, b3, *stats()[:2], None, relu, 0.1, 1e-5)
+    (ref * g).sum().backward()
+    torch.testing.assert_close(y1, ref, rtol=1e-4, atol=1e-4)
+    torch.testing.assert_close(xs.grad, x3.grad, rtol=1e-3, atol=2e-4)
+
+
+def test_dense_block_single_buffer_matches_plain_blocks_on_gpu():
+    """A small torchvision DenseNet with the package's fused modules: the single-buffer dense blocks (strided BatchNorm
+    input, one gradient addition per layer) against the same network on the list-and-concatenate path."""
+    import copy
+    tvd = pytest.importorskip('torchvision.models.densenet')
+    from mgwfbp_b200.models import dense_block
+    from mgwfbp_b200.models.fuse import fuse_model
+    from mgwfbp_b200.ops import counters
+    torch.manual_seed(0)
+    net = tvd.DenseNet(growth_rate=16, block_config=(3, 4, 3), num_init_features=32, bn_size=2, num_classes=10)
+    a = fuse_model(copy.deepcopy(net)).cuda().to(memory_format=torch.channels_last).train()
+    b = fuse_model(copy.deepcopy(net)).cuda().to(memory_format=torch.channels_last).train()
+    for m in b.modules():
+        if isinstance(m, tvd._DenseBlock):
+            m.forward = dense_block._plain_forward.__get__(m)
+    x = torch.randn(8, 3, 64, 64, device='cuda').contiguous(memory_format=torch.channels_last)
+    y = torch.randint(0, 10, (8,), device='cuda')
+    counters.reset()
+    prev = torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cudnn.allow_tf32 = torch.backends.cuda.matmul.allow_tf32 = False     # fp32 convolutions: the two paths may
+    try:                                                                                 # pick different library algorithms
+        la = torch.nn.functional.cross_entropy(a(x), y)
+        la.backward()
+        assert counters.snapshot().get('bn_relu_fwd', 0) > 0
+        lb = torch.nn.functional.cross_entropy(b(x), y)
+        lb.backward()
+    finally:
+        torch.backends.cudnn.allow_tf32, torch.backends.cuda.matmul.allow_tf32 = prev
+    torch.testing.assert_close(la, lb, rtol=1e-5, atol=1e-5)
+    for (n, p), q in zip(a.named_parameters(), b.parameters()):
+        assert p.grad is not None, n
+        rel = float((p.grad - q.grad).norm() / (q.grad.norm() + 1e-12))
+        assert rel < 2e-3, '%s: relative gradient difference %.2e' % (n, rel)
+    for (n, p), q in zip(a.named_buffers(), b.buffers()):
+        torch.testing.assert_close(p.float(), q.float(), rtol=1e-4, atol=1e-5, msg=lambda m, n=n: '%s: %s' % (n, m))

@@ -576,7 +576,7 @@ bn_bwd_reduce_kernel(const float* __restrict__ dy, const float* __restrict__ dy2
 template <int VEC, bool POOL>
 __global__ void __launch_bounds__(kThreads, 2)
 bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gsrc2, const float* __restrict__ y, const float* __restrict__ x,
-                    long long ldx, float* __restrict__ dx,
+                    long long ldx, float* __restrict__ dx, long long lddx, int accumulate,
                     long long M, int C, int TX, int rows_per_split, const float* __restrict__ gamma, const float* __restrict__ beta,
                     const float* __restrict__ save_mean, const float* __restrict__ save_invstd, int mask_mode,
                     const float* __restrict__ dgamma, const float* __restrict__ dbeta, const PoolArgs pool) {
@@ -612,7 +612,16 @@ bn_bwd_apply_kernel(const float* __restrict__ gsrc, const float* __restrict__ gs
             const float xhat = (xv[k] - mean[k]) * istd[k];
             o[k] = sc[k] * (g[k] - db[k] - xhat * dg[k]);
         }
-        store_vec<VEC>(dx + r * C + c0, o);
+        float* dst = dx + r * lddx + c0;
+        if (accumulate) {
+            // the input gradient joins what other consumers of the same tensor have already added at dst (a dense block's
+            // gradient buffer): one read-modify-write here instead of a store plus a separate addition kernel
+            float prev[VEC];
+            load_vec<VEC>(dst, prev);
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) o[k] = __fadd_rn(prev[k], o[k]);      // a separate rounding, as a separate kernel would do
+        }
+        store_vec<VEC>(dst, o);
     }
 }
 
@@ -726,6 +735,8 @@ struct BwdArgs {
     long long M; int C; const float* gamma; const float* beta; const float* save_mean; const float* save_invstd;
     int mask1, mask2; float* dgamma; float* dbeta; float* partials; PoolArgs pool;
     long long ldx;       // floats between consecutive rows of x (>= C)
+    long long lddx;      // floats between consecutive rows of dx (>= C)
+    int accumulate;      // dx += result instead of dx = result
 };
 
 template <int VEC, bool POOL>
@@ -742,7 +753,7 @@ cudaError_t launch_bwd(const BwdArgs& a, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     const float* gsrc = a.dz != nullptr ? a.dz : a.dy;
     const float* gsrc2 = a.dz != nullptr ? nullptr : a.dy2;        // dz already holds the sum of both gradients
-    return launch(bn_bwd_apply_kernel<VEC, POOL>, grid, block, 0, s, true, gsrc, gsrc2, a.y, a.x, a.ldx, a.dx, a.M, a.C, t.tx,
+    return launch(bn_bwd_apply_kernel<VEC, POOL>, grid, block, 0, s, true, gsrc, gsrc2, a.y, a.x, a.ldx, a.dx, a.lddx, a.accumulate, a.M, a.C, t.tx,
                   t.rows_per_split, a.gamma, a.beta, a.save_mean, a.save_invstd, a.mask2, (const float*)a.dgamma,
                   (const float*)a.dbeta, a.pool);
 }
@@ -806,18 +817,22 @@ int mgw_bn_relu_fwd(const float* x, const float* residual, float* y, long long M
 // values), which saves one read and one write of the activation.  relu_bits (may be null; needs C % 4 == 0)
 // is the byte-per-float4 ReLU mask the forward pass recorded: with it the reduce pass reads M*C/4 bytes
 // instead of the M*C floats of y.
-int mgw_bn_relu_bwd_ld(const float* dy, const float* dy2, const float* y, const float* x, long long ldx, float* dz, float* dx, long long M,
-                       int C, const float* gamma, const float* beta, const float* save_mean, const float* save_invstd, int relu,
+// lddx / accumulate: dx has rows lddx floats apart (>= C) and, with accumulate != 0, receives dx += result: the layer's
+// input gradient is added straight into a wider gradient buffer that other consumers of the same input add to as well
+// (not together with dz: a residual branch needs the gradient itself).
+int mgw_bn_relu_bwd_ld(const float* dy, const float* dy2, const float* y, const float* x, long long ldx, float* dz, float* dx,
+                       long long lddx, int accumulate, long long M, int C, const float* gamma, const float* beta, const float* save_mean, const float* save_invstd, int relu,
                        float* dgamma, float* dbeta, float* partials, const unsigned char* relu_bits, void* stream) {
     if (dy == nullptr || x == nullptr || dx == nullptr || M <= 0 || C <= 0 || partials == nullptr) return MGW_ERR_ARG;
     if (ldx < C || (C % 4 == 0 && ldx % 4 != 0)) return MGW_ERR_ARG;
+    if (lddx < C || (C % 4 == 0 && lddx % 4 != 0) || ((accumulate || lddx != C) && dz != nullptr)) return MGW_ERR_ARG;
     // the byte mask serves the reduce pass; the apply pass then reads the masked gradient dz, which must exist
     if (relu_bits != nullptr && (C % 4 != 0 || !relu || dz == nullptr)) return MGW_ERR_ARG;
     if (dgamma == nullptr || dbeta == nullptr || save_mean == nullptr || save_invstd == nullptr) return MGW_ERR_ARG;
     const int mask1 = !relu ? 0 : (relu_bits != nullptr ? 3 : (y != nullptr ? 1 : 2));          // mask used by the reduce pass
     const int mask2 = dz != nullptr ? 0 : mask1;                   // apply pass: dz already carries the mask
     const BwdArgs a = {dy, dy2, y, relu_bits, x, dz, dx, M, C, gamma, beta, save_mean, save_invstd, mask1, mask2, dgamma, dbeta,
-                       partials, {nullptr, nullptr, 0, 0, 0, 0}, ldx};
+                       partials, {nullptr, nullptr, 0, 0, 0, 0}, ldx, lddx, accumulate};
     const cudaError_t e = (C % 4 == 0) ? launch_bwd<4, false>(a, (cudaStream_t)stream) : launch_bwd<1, false>(a, (cudaStream_t)stream);
     MGW_CUDA_CHECK(e);
     return MGW_OK;
@@ -827,7 +842,7 @@ int mgw_bn_relu_bwd_ld(const float* dy, const float* dy2, const float* y, const 
 int mgw_bn_relu_bwd(const float* dy, const float* dy2, const float* y, const float* x, float* dz, float* dx, long long M, int C, const float* gamma,
                     const float* beta, const float* save_mean, const float* save_invstd, int relu, float* dgamma, float* dbeta,
                     float* partials, const unsigned char* relu_bits, void* stream) {
-    return mgw_bn_relu_bwd_ld(dy, dy2, y, x, C, dz, dx, M, C, gamma, beta, save_mean, save_invstd, relu, dgamma, dbeta, partials,
+    return mgw_bn_relu_bwd_ld(dy, dy2, y, x, C, dz, dx, C, 0, M, C, gamma, beta, save_mean, save_invstd, relu, dgamma, dbeta, partials,
                               relu_bits, stream);
 }
 
@@ -868,7 +883,7 @@ int mgw_bn_relu_maxpool_bwd(const float* dp, const unsigned char* idx, const flo
         return MGW_ERR_ARG;
     const long long M = (long long)N * H * W;
     const BwdArgs a = {nullptr, nullptr, nullptr, nullptr, x, nullptr, dx, M, C, gamma, beta, save_mean, save_invstd, 2, 2, dgamma,
-                       dbeta, partials, {dp, idx, H, W, (H + 2 - 3) / 2 + 1, (W + 2 - 3) / 2 + 1}, C};
+                       dbeta, partials, {dp, idx, H, W, (H + 2 - 3) / 2 + 1, (W + 2 - 3) / 2 + 1}, C, C, 0};
     const cudaError_t e = (C % 4 == 0) ? launch_bwd<4, true>(a, (cudaStream_t)stream) : launch_bwd<1, true>(a, (cudaStream_t)stream);
     MGW_CUDA_CHECK(e);
     return MGW_OK;

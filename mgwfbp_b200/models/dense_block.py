@@ -13,7 +13,9 @@ Backward walks the layers in reverse over one gradient buffer of the same shape:
 is complete when its turn comes (every later layer has already added its share), the layer's own graph is run by a
 nested ``torch.autograd.backward`` (parameter gradients accumulate as usual, so gradient hooks fire in the usual
 order) and its input gradient is added to the first ``C_l`` channels in ONE kernel.  L additions instead of
-L (L - 1) / 2, moving the same bytes.
+L (L - 1) / 2, moving the same bytes.  On the GPU the first BatchNorm of a layer reads its channel slice of the buffer
+in place (row stride = total channels) and its backward kernel adds the input gradient into the gradient buffer
+directly (``ops/bn_relu.py``), so neither a concatenated copy nor a separate addition kernel remains.
 
 Parameters, buffers and ``state_dict`` keys are untouched: :func:`fuse_dense_blocks` only binds a new ``forward``.
 """
@@ -35,12 +37,14 @@ class _Tap(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, cell):
         ctx.cell = cell
+        ctx.set_materialize_grads(False)        # no gradient (the consumer added it to the buffer itself) stays None
         return x.view_as(x)
 
     @staticmethod
     @once_differentiable
     def backward(ctx, grad):
-        ctx.cell['sink'](grad)
+        if grad is not None:
+            ctx.cell['sink'](grad)
         return None, None
 
 
@@ -81,7 +85,9 @@ class _DenseBlockFn(torch.autograd.Function):
             cell = {}
             with torch.enable_grad():
                 xin = _alias(buf[:, :c]).requires_grad_(True)
-                out = _layer_body(layer, _Tap.apply(xin, cell))
+                tapped = _Tap.apply(xin, cell)
+                tapped._mgw_grad_cell = cell         # the fused BatchNorm adds its input gradient to cell['target'] itself
+                out = _layer_body(layer, tapped)
             g = out.shape[1]
             buf[:, c:c + g].copy_(out.detach())
             steps.append((c, g, cell, out))          # `out` keeps the layer's autograd graph alive until backward
@@ -96,7 +102,7 @@ class _DenseBlockFn(torch.autograd.Function):
         steps, ctx.steps = ctx.steps, None
         for c, g, cell, out in reversed(steps):
             head = grad[:, :c]
-            cell['sink'] = head.add_
+            cell['sink'], cell['target'] = head.add_, head
             torch.autograd.backward(out, grad[:, c:c + g])
             cell.clear()
         return grad[:, :ctx.c0], None

@@ -72,7 +72,8 @@ def _declare(lib) -> None:
     if _HAS_LD:
         lib.mgw_bn_relu_fwd_ld.argtypes = [C.c_void_p, C.c_longlong] + list(lib.mgw_bn_relu_fwd.argtypes[1:])
         lib.mgw_bn_relu_bwd_ld.argtypes = (list(lib.mgw_bn_relu_bwd.argtypes[:4]) + [C.c_longlong] +
-                                           list(lib.mgw_bn_relu_bwd.argtypes[4:]))
+                                           list(lib.mgw_bn_relu_bwd.argtypes[4:6]) + [C.c_longlong, C.c_int] +
+                                           list(lib.mgw_bn_relu_bwd.argtypes[6:]))
     lib.mgw_bn_launches.argtypes = [C.c_longlong, C.c_int, C.c_int]
     lib.mgw_bn_set_sm_budget.argtypes = [C.c_int]
     lib.mgw_bn_cluster_supported.argtypes = [C.c_longlong, C.c_int]
@@ -145,6 +146,9 @@ class _BNReLU(torch.autograd.Function):
             counters.bump('bn_relu_fwd', lib.mgw_bn_launches(M, Cc, 0))
         ctx.save_for_backward(x, y if (needs_mask and bits is None) else None, weight, bias, mean, invstd, bits)
         ctx.relu, ctx.has_residual, ctx.rows, ctx.ld = bool(relu), residual is not None, (M, Cc), ld
+        # A caller that sums the gradients of several consumers of x in one buffer (models/dense_block.py) leaves a dict
+        # on the input tensor; when backward runs, its 'target' entry is where this layer's input gradient is ADDED.
+        ctx.grad_cell = getattr(x, '_mgw_grad_cell', None)
         ctx.mark_non_differentiable(*[t for t in (running_mean, running_var, num_batches_tracked) if t is not None])
         if dual:
             # two handles on the same output: each consumer's gradient then reaches backward() separately
@@ -160,29 +164,48 @@ class _BNReLU(torch.autograd.Function):
         x, y, weight, bias, mean, invstd, bits = ctx.saved_tensors
         M, Cc = ctx.rows
         ld = ctx.ld
-        dx = torch.empty_like(x) if ld == Cc else torch.empty(x.shape, dtype=x.dtype, device=x.device, memory_format=torch.channels_last)
-        if _as_rows(dy) is None or dy.stride() != dx.stride():
-            dy = dy.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else dy.contiguous()
-        if dy2 is not None and (_as_rows(dy2) is None or dy2.stride() != dx.stride()):
-            dy2 = dy2.contiguous(memory_format=torch.channels_last) if x.dim() == 4 else dy2.contiguous()
+        four_d = x.dim() == 4
+        # where the input gradient goes: a dense tensor of its own, or -- added -- the caller's wider gradient buffer
+        target = ctx.grad_cell.get('target') if (ctx.grad_cell is not None and _HAS_LD and not ctx.has_residual) else None
+        if target is not None:
+            t_layout = _row_layout(target)
+            if target.shape != x.shape or target.dtype != x.dtype or t_layout is None:
+                target = None
+        if target is None:
+            dx = torch.empty_like(x) if ld == Cc else torch.empty(x.shape, dtype=x.dtype, device=x.device,
+                                                                  memory_format=torch.channels_last)
+            dense_stride = dx.stride()
+        else:
+            dx = None
+            n_, c_, h_, w_ = x.shape
+            dense_stride = (h_ * w_ * c_, 1, w_ * c_, c_)
+        if _as_rows(dy) is None or dy.stride() != dense_stride:
+            dy = dy.contiguous(memory_format=torch.channels_last) if four_d else dy.contiguous()
+        if dy2 is not None and (_as_rows(dy2) is None or dy2.stride() != dense_stride):
+            dy2 = dy2.contiguous(memory_format=torch.channels_last) if four_d else dy2.contiguous()
         dz = torch.empty_like(dx) if ctx.has_residual else None     # only a residual needs the masked gradient itself
         dgamma = torch.empty(Cc, dtype=torch.float32, device=x.device)
         dbeta = torch.empty(Cc, dtype=torch.float32, device=x.device)
         s = torch.cuda.current_stream().cuda_stream
-        if ld == Cc and _use_cluster(lib, M, Cc):
+        if target is None and ld == Cc and _use_cluster(lib, M, Cc):
             _lib.check(lib.mgw_bn_relu_bwd_cluster(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
                                                    _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
                                                    dgamma.data_ptr(), dbeta.data_ptr(), _ptr(bits), s), 'bn_relu_bwd_cluster')
             counters.bump('bn_relu_bwd_cluster', 1)
         else:
             partials = torch.empty(lib.mgw_bn_partials_floats(M, Cc), dtype=torch.float32, device=x.device)
-            if ld == Cc:
+            if target is not None:      # dx is added into the caller's buffer and never exists by itself
+                _lib.check(lib.mgw_bn_relu_bwd_ld(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), ld, None, target.data_ptr(),
+                                                  t_layout[2], 1, M, Cc, _ptr(weight), _ptr(bias), mean.data_ptr(),
+                                                  invstd.data_ptr(), int(ctx.relu), dgamma.data_ptr(), dbeta.data_ptr(),
+                                                  partials.data_ptr(), _ptr(bits), s), 'bn_relu_bwd_ld(accumulate)')
+            elif ld == Cc:
                 _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
                                                _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
                                                dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), _ptr(bits), s), 'bn_relu_bwd')
             else:
-                _lib.check(lib.mgw_bn_relu_bwd_ld(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), ld, _ptr(dz), dx.data_ptr(), M, Cc,
-                                                  _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
+                _lib.check(lib.mgw_bn_relu_bwd_ld(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), ld, _ptr(dz), dx.data_ptr(), Cc, 0,
+                                                  M, Cc, _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),
                                                   dgamma.data_ptr(), dbeta.data_ptr(), partials.data_ptr(), _ptr(bits), s),
                            'bn_relu_bwd_ld')
             counters.bump('bn_relu_bwd', lib.mgw_bn_launches(M, Cc, 1))
@@ -313,7 +336,7 @@ def bn_relu_maxpool(bn: torch.nn.BatchNorm2d, pool: torch.nn.MaxPool2d, x: torch
     writing the full-resolution normalised tensor; any other configuration runs the modules one after the other."""
     def _pair(v):
         return tuple(v) if isinstance(v, (tuple, list)) else (v, v)
-    fusable = (isinstance(bn, _FusedBNMixin) and bn._native_ok(x) and x.dim() == 4 and x.shape[1] % 4 == 0
+    fusable = (isinstance(bn, _FusedBNMixin) and bn._native_ok(x) and x.dim() == 4 and _as_rows(x) is not None and x.shape[1] % 4 == 0
                and _pair(pool.kernel_size) == (3, 3) and _pair(pool.stride) == (2, 2) and _pair(pool.padding) == (1, 1)
                and _pair(pool.dilation) == (1, 1) and not pool.ceil_mode and not pool.return_indices)
     if not fusable:

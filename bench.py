@@ -203,7 +203,9 @@ def run_ours(args):
     counters.reset()
     if args.profiler_range:
         torch.cuda.profiler.start()
+    step.replays, step.replay_host_s = 0, 0.0
     ms_dev = _time_steps(torch, world > 1, step_device, args.steps, barrier)
+    host_replay_ms = 1e3 * step.replay_host_s / step.replays if step.replays else None      # host side of one graph launch
     if args.profiler_range:
         torch.cuda.profiler.stop()
     launches = counters.total()
@@ -279,7 +281,7 @@ def run_ours(args):
             'exposed_comm_ms': exposed, 'comm_kernel_ms': comm_ms,
             'selfcheck': selfcheck, 'schedule_tuning': tuning,
             'sgd_stock_fallback_steps': getattr(getattr(optimizer, '_fast_sgd', None), 'fallback_steps', 0),
-            'eager_steps_after_capture': step.eager_after_capture,
+            'eager_steps_after_capture': step.eager_after_capture, 'host_graph_launch_ms': host_replay_ms,
         }
         print(json.dumps(out))
     hvd.shutdown()

@@ -16,6 +16,7 @@ B200-oriented differences:
 """
 from __future__ import annotations
 
+import time
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -34,6 +35,7 @@ class TrainStep:
         self.trainer = trainer
         self.track_accuracy = bool(track_accuracy)
         self.eager_after_capture = 0     # steps that ran eagerly after the capture because their batch had another shape
+        self.replays, self.replay_host_s = 0, 0.0       # graph replays and the host time their launch calls took
         self._replayed_last = False
         self.optimizer = trainer.optimizer
         self.cuda = trainer.is_cuda
@@ -172,7 +174,10 @@ class TrainStep:
             sync = getattr(self.trainer.optimizer, 'sync_hyper', None)
             if sync is not None:
                 sync()                         # on the replaying stream: ordered after the previous replay, before this one
+            t_host = time.perf_counter()
             self._graph.replay()
+            self.replay_host_s += time.perf_counter() - t_host          # what the host spends handing one step to the driver
+            self.replays += 1
             self._replayed_last = True
             counters.bump_many(self._launches_per_replay)
             self._track(self._static_loss, self._static_outputs, self._static_labels)

@@ -98,8 +98,10 @@ class _DenseBlockFn(torch.autograd.Function):
     @staticmethod
     @once_differentiable
     def backward(ctx, grad_out):
-        grad = grad_out.clone(memory_format=torch.preserve_format)        # accumulated in place below
         steps, ctx.steps = ctx.steps, None
+        if steps is None:
+            raise RuntimeError('a dense block can run backward once per forward: the graphs of its layers are freed by it')
+        grad = grad_out.clone(memory_format=torch.preserve_format)        # accumulated in place below
         for c, g, cell, out in reversed(steps):
             head = grad[:, :c]
             cell['sink'], cell['target'] = head.add_, head

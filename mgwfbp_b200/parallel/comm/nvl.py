@@ -71,7 +71,8 @@ class NvlComm(Communicator):
         self.lib = _lib.load(allow_build=False)
         self._rank, self._world = runtime.rank(), runtime.size()
         self.device = torch.device('cuda', torch.cuda.current_device())
-        self.stream = torch.cuda.Stream(device=self.device, priority=-1)
+        self._side_stream = torch.cuda.Stream(device=self.device, priority=-1)
+        self._on_main = os.environ.get('MGWFBP_COMM_STREAM', 'side').strip().lower() == 'main'
         self.timeout_ns = int(float(os.environ.get('MGWFBP_COMM_TIMEOUT_S', '10')) * 1e9)
         self.oneshot_max_bytes = _env_int('MGWFBP_ONESHOT_MAX_BYTES', 512 * 1024)
         self.max_ctas_oneshot = min(_env_int('MGWFBP_ONESHOT_CTAS', 8), _lib.MAX_CTAS)
@@ -130,6 +131,13 @@ class NvlComm(Communicator):
             from ...ops.bn_relu import set_sm_budget
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
             set_sm_budget(max(sms // 2, sms - self.overlap_ctas))
+
+    @property
+    def stream(self) -> torch.cuda.Stream:
+        """Where communication kernels are launched: a high-priority side stream of their own, so that they run beside
+        backward; with ``MGWFBP_COMM_STREAM=main`` the stream that is current at the call, which gives up the overlap and
+        keeps a captured training step a single chain of kernels."""
+        return torch.cuda.current_stream(self.device) if self._on_main else self._side_stream
 
     @property
     def nvls_available(self) -> bool:

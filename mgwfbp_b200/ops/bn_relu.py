@@ -40,7 +40,7 @@ def _row_layout(x: torch.Tensor):
     rows = _as_rows(x)
     if rows is not None:
         return rows[0], rows[1], rows[1]
-    if not _HAS_LD or x.dim() != 4:
+    if x.dim() != 4:
         return None
     n, c, h, w = x.shape
     ld = x.stride(3)
@@ -52,7 +52,6 @@ def _row_layout(x: torch.Tensor):
 
 
 _declared = False
-_HAS_LD = True            # cleared by _declare() when the loaded library predates the strided entry points
 
 
 def _declare(lib) -> None:
@@ -67,13 +66,11 @@ def _declare(lib) -> None:
     lib.mgw_bn_relu_bwd.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong, C.c_int,
                                     C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,
                                     C.c_void_p, C.c_void_p, C.c_void_p]
-    global _HAS_LD
-    _HAS_LD = hasattr(lib, 'mgw_bn_relu_fwd_ld')
-    if _HAS_LD:
-        lib.mgw_bn_relu_fwd_ld.argtypes = [C.c_void_p, C.c_longlong] + list(lib.mgw_bn_relu_fwd.argtypes[1:])
-        lib.mgw_bn_relu_bwd_ld.argtypes = (list(lib.mgw_bn_relu_bwd.argtypes[:4]) + [C.c_longlong] +
-                                           list(lib.mgw_bn_relu_bwd.argtypes[4:6]) + [C.c_longlong, C.c_int] +
-                                           list(lib.mgw_bn_relu_bwd.argtypes[6:]))
+    # the same with a row stride for x, and (backward) a row stride and an accumulate flag for dx
+    lib.mgw_bn_relu_fwd_ld.argtypes = [C.c_void_p, C.c_longlong] + list(lib.mgw_bn_relu_fwd.argtypes[1:])
+    lib.mgw_bn_relu_bwd_ld.argtypes = (list(lib.mgw_bn_relu_bwd.argtypes[:4]) + [C.c_longlong] +
+                                       list(lib.mgw_bn_relu_bwd.argtypes[4:6]) + [C.c_longlong, C.c_int] +
+                                       list(lib.mgw_bn_relu_bwd.argtypes[6:]))
     lib.mgw_bn_launches.argtypes = [C.c_longlong, C.c_int, C.c_int]
     lib.mgw_bn_set_sm_budget.argtypes = [C.c_int]
     lib.mgw_bn_cluster_supported.argtypes = [C.c_longlong, C.c_int]
@@ -166,7 +163,7 @@ class _BNReLU(torch.autograd.Function):
         ld = ctx.ld
         four_d = x.dim() == 4
         # where the input gradient goes: a dense tensor of its own, or -- added -- the caller's wider gradient buffer
-        target = ctx.grad_cell.get('target') if (ctx.grad_cell is not None and _HAS_LD and not ctx.has_residual) else None
+        target = ctx.grad_cell.get('target') if (ctx.grad_cell is not None and not ctx.has_residual) else None
         if target is not None:
             t_layout = _row_layout(target)
             if target.shape != x.shape or target.dtype != x.dtype or t_layout is None:

@@ -22,7 +22,6 @@ Parameters, buffers and ``state_dict`` keys are untouched: :func:`fuse_dense_blo
 from __future__ import annotations
 
 import os
-import types
 
 import torch
 import torch.nn.functional as F
@@ -130,9 +129,10 @@ def fuse_dense_blocks(net: torch.nn.Module) -> int:
         from torchvision.models.densenet import _DenseBlock
     except Exception:      # pragma: no cover - torchvision is optional
         return 0
+    from .fuse import _bind
     n = 0
     for m in net.modules():
         if isinstance(m, _DenseBlock):
-            m.forward = types.MethodType(_block_forward, m)
+            _bind(m, _block_forward)
             n += 1
     return n

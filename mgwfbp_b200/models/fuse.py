@@ -14,8 +14,6 @@ that reference the original modules stay valid.
 """
 from __future__ import annotations
 
-import types
-
 import torch
 import torch.nn as nn
 import torch.nn.functional as F
@@ -105,8 +103,22 @@ def _cifar_resnet_forward(self, x):
     return self.classifier(x.reshape(x.size(0), -1))
 
 
+_bound_classes = {}
+
+
 def _bind(module, fn):
-    module.forward = types.MethodType(fn, module)
+    """Give ``module`` the forward ``fn`` by moving it to a subclass of its class that defines it.  (An instance
+    attribute ``module.forward = MethodType(fn, module)`` would be copied by ``nn.DataParallel``'s replication still bound
+    to the original module, so every replica would run on the original's parameters.)"""
+    base = type(module)
+    if base.__dict__.get('_mgw_bound_forward') is fn:
+        return
+    key = (base, fn)
+    cls = _bound_classes.get(key)
+    if cls is None:
+        cls = type(base.__name__, (base,), {'forward': fn, '_mgw_bound_forward': fn, '__module__': base.__module__})
+        _bound_classes[key] = cls
+    module.__class__ = cls
 
 
 def fuse_model(net: nn.Module) -> nn.Module:

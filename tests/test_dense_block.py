@@ -75,3 +75,17 @@ def test_dense_block_two_steps_of_sgd_match():
             opt.step()
     for (n, a), b in zip(ours.named_parameters(), ref.parameters()):
         torch.testing.assert_close(a, b, rtol=1e-8, atol=1e-10, msg=lambda m, n=n: '%s: %s' % (n, m))
+
+
+def test_fused_forwards_follow_the_module_through_replication():
+    """nn.DataParallel replicates modules by copying their __dict__: a rebound forward has to live on the class, or every
+    replica would run the original module's forward (on the original's parameters)."""
+    from mgwfbp_b200.models.fuse import fuse_model
+    net = fuse_model(tv.models.densenet121(num_classes=10))
+    for m in (net.features.denseblock1, net.features.denseblock1.denselayer1, net):
+        rep = m._replicate_for_data_parallel()
+        assert rep.forward.__self__ is rep
+        assert 'forward' not in m.__dict__
+    assert isinstance(net.features.denseblock1, tv.models.densenet._DenseBlock)
+    fuse_model(net)                                       # idempotent: no second layer of subclasses
+    assert type(net.features.denseblock1).__mro__[1] is tv.models.densenet._DenseBlock

@@ -140,6 +140,7 @@ class _BNReLU(torch.autograd.Function):
                                                   _ptr(running_mean), _ptr(running_var), _ptr(num_batches_tracked),
                                                   float(momentum), float(eps), int(relu), mean.data_ptr(), invstd.data_ptr(),
                                                   partials.data_ptr(), _ptr(bits), s), 'bn_relu_fwd_ld')
+                counters.bump('note:bn_relu_fwd_strided', 1)
             counters.bump('bn_relu_fwd', lib.mgw_bn_launches(M, Cc, 0))
         ctx.save_for_backward(x, y if (needs_mask and bits is None) else None, weight, bias, mean, invstd, bits)
         ctx.relu, ctx.has_residual, ctx.rows, ctx.ld = bool(relu), residual is not None, (M, Cc), ld
@@ -196,6 +197,7 @@ class _BNReLU(torch.autograd.Function):
                                                   t_layout[2], 1, M, Cc, _ptr(weight), _ptr(bias), mean.data_ptr(),
                                                   invstd.data_ptr(), int(ctx.relu), dgamma.data_ptr(), dbeta.data_ptr(),
                                                   partials.data_ptr(), _ptr(bits), s), 'bn_relu_bwd_ld(accumulate)')
+                counters.bump('note:bn_relu_bwd_accumulate', 1)
             elif ld == Cc:
                 _lib.check(lib.mgw_bn_relu_bwd(dy.data_ptr(), _ptr(dy2), _ptr(y), x.data_ptr(), _ptr(dz), dx.data_ptr(), M, Cc,
                                                _ptr(weight), _ptr(bias), mean.data_ptr(), invstd.data_ptr(), int(ctx.relu),

@@ -456,8 +456,9 @@ def tune_schedule(trainer, build_optimizer, candidates: Sequence[dict], steps: i
     seen, report = {}, []
     for cand in candidates:
         opt = build_optimizer(**cand)
-        key = (opt.merge_schedule.digest(), getattr(opt, '_update_mode', ''))
+        key = (opt.merge_schedule.digest(), getattr(opt, '_update_mode', ''), tuple(sorted(getattr(opt, '_late_groups', ()))))
         row = dict(cand, groups=len(opt.merge_schedule.groups), update=getattr(opt, '_update_mode', None),
+                   late_groups=sorted(getattr(opt, '_late_groups', ())),
                    group_mb=[round(4e-6 * n, 2) for n in opt.merge_schedule.group_sizes])
         if key in seen:
             opt.close()
@@ -525,14 +526,14 @@ def build_distributed_optimizer(trainer, seq_layernames=None, layerwise_times=No
     named = list(trainer.net.named_parameters())
     info = {'interference': None, 'trial': None, 'cost_model': None, 'cost_model_overlapped': None}
 
-    def build(rho=None, cost=None, cost_last=None, update=None, slices=None):
+    def build(rho=None, cost=None, cost_last=None, update=None, slices=None, late=False):
         schedule = None
         if slices:
             schedule = lambda n, s, t, _k=int(slices): groups_time_sliced(n, s, t, _k)      # noqa: E731
         return DistributedOptimizer(base, named_parameters=named, compression=compression, seq_layernames=seq_layernames,
                                     layerwise_times=layerwise_times, norm_clip=norm_clip, threshold=threshold, writer=writer,
                                     gradient_path=gradient_path, cost_model=cost, cost_model_last=cost_last, interference=rho,
-                                    fused_update=update, schedule=schedule)
+                                    fused_update=update, schedule=schedule, late_full=bool(late))
 
     adaptive_fused = (runtime.size() > 1 and trainer.is_cuda and not settings.ORIGINAL_HOROVOD and settings.ADAPTIVE_MERGE
                       and layerwise_times is not None)
@@ -560,15 +561,19 @@ def build_distributed_optimizer(trainer, seq_layernames=None, layerwise_times=No
             r = round(max(r, 1e-3), 4)
             if r not in rhos:
                 rhos.append(r)
-    mk = lambda rho, update, slices: build(rho, cost_ovl, cost_full, update, slices)      # noqa: E731
+    mk = lambda rho, update, slices, late=False: build(rho, cost_ovl, cost_full, update, slices, late)      # noqa: E731
     # plain SGD without clipping may run its update inside the group kernels or once after backward: try both
     modes = ['fused', 'deferred'] if (norm_clip is None and settings.UPDATE_MODE == 'fused' and
                                       isinstance(base, torch.optim.SGD)) else [None]
     # schedules from the interference-aware MG-WFBP search, and time-sliced ones (messages ready at equal distances in
     # backward time + a small last message) that the cost model cannot tell apart from them
-    candidates = [{'rho': r, 'update': m, 'slices': None} for m in modes for r in rhos]
+    candidates = [{'rho': r, 'update': m, 'slices': None, 'late': False} for m in modes for r in rhos]
     if not settings.INTERFERENCE_PINNED:
-        candidates += [{'rho': None, 'update': m, 'slices': k} for m in modes for k in (3, 6)]
+        candidates += [{'rho': None, 'update': m, 'slices': k, 'late': False} for m in modes for k in (3, 6)]
+    if settings.TRY_LATE_GROUPS:
+        # the same schedules with their late groups (ready within settings.LATE_GROUP_MS of the end of backward) given the
+        # whole GPU; a candidate without such a group is recognised as a repetition and not run again
+        candidates += [dict(c, late=True) for c in candidates]
     if tune and len(candidates) > 1:
         opt, info['trial'] = tune_schedule(trainer, mk, candidates, steps=trial_steps, use_graph=use_graph)
     else:

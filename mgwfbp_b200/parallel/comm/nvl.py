@@ -250,11 +250,12 @@ class NvlComm(Communicator):
         total = 0
         sizes = []
         n_groups = len(opt._groups)
+        late = getattr(opt, '_late_groups', frozenset())      # ready so close to the end of backward that they count as last
         for gi, names in enumerate(opt._groups):
             params = [named[n] for n in names]
             n_vec = sum((p.numel() + 3) // 4 for p in params)
             # every group but the last one of the schedule is launched while backward still runs
-            algo, n_ctas = self.choose(n_vec, overlapped=gi < n_groups - 1)
+            algo, n_ctas = self.choose(n_vec, overlapped=gi < n_groups - 1 and gi not in late)
             nbytes = int(self.lib.mgw_stage_bytes(algo, n_vec, self._world))
             sizes.append((algo, n_ctas, nbytes))
             total += (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
@@ -289,7 +290,7 @@ class NvlComm(Communicator):
             stage_top += (nbytes + _ALIGN - 1) // _ALIGN * _ALIGN
             plan.partials_off = p_off
             plan.block = block
-            plan.overlapped = len(plans) < n_groups - 1
+            plan.overlapped = len(plans) < n_groups - 1 and len(plans) not in late
             plan.copy_pack = bool(self.pack_mode == 'copy' and plan.overlapped and algo != _lib.ALGO_ONESHOT)
             plan.stage_views = None
             self._fill_args(plan, block, hyper.data_ptr(), partials.data_ptr() + 4 * p_off)

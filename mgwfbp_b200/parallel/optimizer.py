@@ -55,9 +55,11 @@ class _DistributedMixin:
     # ------------------------------------------------------------------ construction
     def _dist_init(self, base_optimizer, named_parameters, compression, seq_layernames, layerwise_times,
                    norm_clip, threshold, writer, gradient_path, comm, cost_model, fused_update, interference=None,
-                   cost_model_last=None, schedule=None):
+                   cost_model_last=None, schedule=None, late_full=False):
         self._wrapped = base_optimizer
         self._given_schedule = schedule
+        self._late_full = bool(late_full)
+        self._late_groups = frozenset()
         self._interference = interference
         self._cost_model_last = cost_model_last
         self._compression = compression
@@ -238,6 +240,13 @@ class _DistributedMixin:
         else:
             sched = groups_by_threshold(names, sizes, self._threshold)
         self._schedule: MergeSchedule = sched
+        if self._late_full and self._layerwise_times is not None and len(self._layerwise_times) == len(names):
+            # groups (other than the last) that become ready when less than LATE_GROUP_MS of profiled backward time is left:
+            # a group is ready with its earliest layer, and what is left of backward then is the time of the layers before it
+            pos = {n: i for i, n in enumerate(names)}
+            before = np.concatenate(([0.0], np.cumsum(np.asarray(self._layerwise_times, dtype=np.float64))))
+            self._late_groups = frozenset(gi for gi, g in enumerate(sched.groups[:-1])
+                                          if before[min(pos[n] for n in g)] < 1e-3 * settings.LATE_GROUP_MS)
         logger.info('# of parameters: %d', int(np.sum(sizes)) if sizes else 0)
         logger.info('Total number of tensors: %s', len(sizes))
         logger.info('Merged Number of groups: %s', len(sched.groups))
@@ -261,7 +270,8 @@ class _DistributedMixin:
     def _verify_schedule_agreement(self) -> None:
         """Every rank must hold the same schedule: the kernels rely on identical launch order
         instead of Horovod's per-tensor name negotiation."""
-        digests = runtime.allgather_object(self._schedule.digest())
+        # (the late groups change how many CTAs a group's kernel has, and CTAs of different ranks wait for one another)
+        digests = runtime.allgather_object(self._schedule.digest() + '/' + ','.join(map(str, sorted(self._late_groups))))
         if len(set(digests)) != 1:
             raise RuntimeError('ranks disagree on the merge schedule: %s' % digests)
 
@@ -549,7 +559,8 @@ class _DistributedMixin:
 def DistributedOptimizer(optimizer, named_parameters=None, compression=None, density=0.001, seq_layernames=None,
                          layerwise_times=None, norm_clip=None, threshold=0, writer=None, gradient_path=None,
                          comm: Optional[Communicator] = None, cost_model=None, fused_update: Optional[bool] = None,
-                         interference: Optional[float] = None, cost_model_last=None, schedule: Optional[MergeSchedule] = None):
+                         interference: Optional[float] = None, cost_model_last=None, schedule: Optional[MergeSchedule] = None,
+                         late_full: bool = False):
     """Wrap ``optimizer`` so that gradients are averaged across workers before each update.
 
     Signature and merge policies follow reference ``distributed_optimizer.py:435-471``:
@@ -568,7 +579,8 @@ def DistributedOptimizer(optimizer, named_parameters=None, compression=None, den
     backward down (``interference``, see ``engine.fit_interference``; default ``settings.INTERFERENCE``)
     and the cost model of the schedule's last message, which runs with the whole GPU (``cost_model_last``).
     ``schedule`` installs a given :class:`MergeSchedule` (or the result of calling it with the scheduled names, sizes and
-    layer-wise backward times) instead of deriving one.
+    layer-wise backward times) instead of deriving one.  ``late_full`` gives groups that become ready within
+    ``settings.LATE_GROUP_MS`` of the end of backward the CTA count of a message that has the GPU to itself.
 
     Example of gradient clipping::
 
@@ -586,7 +598,8 @@ def DistributedOptimizer(optimizer, named_parameters=None, compression=None, den
     obj.defaults = dict(optimizer.defaults)
     obj.state.update(optimizer.state)
     obj._dist_init(optimizer, named_parameters, compression, seq_layernames, layerwise_times, norm_clip,
-                   threshold, writer, gradient_path, comm, cost_model, fused_update, interference, cost_model_last, schedule)
+                   threshold, writer, gradient_path, comm, cost_model, fused_update, interference, cost_model_last, schedule,
+                   late_full)
     if not obj._active and obj._base_is_sgd:
         first = next(iter(obj._named_parameters.values()), None)
         if first is not None and first.is_cuda:

@@ -113,6 +113,14 @@ SHADOW_EVERY = int(_env_str('SHADOW', '0') or 0)
 _interference_env = _env_str('INTERFERENCE', '')
 INTERFERENCE_PINNED = _interference_env != ''
 INTERFERENCE = float(_interference_env) if INTERFERENCE_PINNED else 0.25
+# A merged group that becomes ready this close to the end of backward (milliseconds of profiled backward time left) can
+# be treated like the schedule's last message: its kernel gets the CTA count of a message that has the GPU to itself
+# instead of the few CTAs of an overlapped one, because most of it runs after backward anyway
+# (``DistributedOptimizer(late_full=True)``; off unless asked for).
+LATE_GROUP_MS = float(_env_str('LATE_GROUP_MS', '0.4'))
+# Let the schedule trial also run its candidates with their late groups given the whole GPU (engine.build_distributed_optimizer).
+# Off by default: the option is tested on CPU only (which groups count as late), no GPU time was left to measure it.
+TRY_LATE_GROUPS = _env_flag('TRY_LATE_GROUPS', False)
 
 # The stock comparison arm (reference dist_trainer.py:12-15 imports horovod.torch itself when this is set): gradients
 # go through torch.distributed (NCCL on GPUs) in Horovod-style fusion buckets of 64 MB, the update is torch's own

@@ -319,11 +319,14 @@ def _trial_harness(rank, world):
     thresholds = {0.0: 0, 0.5: 50000, 1.0: 524288000}
     built = []
 
-    def build(rho, update):
-        opt = hvd.DistributedOptimizer(base, named_parameters=trainer.net.named_parameters(), threshold=thresholds[rho])
+    def build(rho, update, late=False):
+        opt = hvd.DistributedOptimizer(base, named_parameters=trainer.net.named_parameters(), threshold=thresholds[rho],
+                                       late_full=late)
         built.append(opt)
         return opt
-    opt, report = tune_schedule(trainer, build, [{'rho': r, 'update': None} for r in (0.0, 0.5, 1.0, 0.5)], steps=2)
+    # the candidate dictionaries of engine.build_distributed_optimizer have these keys
+    opt, report = tune_schedule(trainer, build, [{'rho': r, 'update': None, 'late': False} for r in (0.0, 0.5, 1.0, 0.5)], steps=2)
+    assert all(r['late_groups'] == [] for r in report)
     assert trainer.optimizer is opt and opt._active
     assert all(not o._active for o in built[:-1]), 'retired wrappers still own hooks'
     assert [r['groups'] for r in report][2] == 1 and report[3].get('same_as_earlier')

@@ -247,3 +247,26 @@ def test_time_sliced_groups_cover_everything_in_backward_order():
     assert spans == [10, 11, 5] or max(spans) <= 12
     # a tail budget smaller than the first tensor still leaves that tensor in the last group
     assert groups_time_sliced(names, sizes, tb, 2, tail_elems=1).groups[-1] == ['l0']
+
+
+def test_late_groups_are_those_ready_close_to_the_end_of_backward():
+    """``late_full``: a group counts as late when less than settings.LATE_GROUP_MS of profiled backward time is left once its
+    earliest layer is done; the schedule's last group never does (it has the GPU to itself anyway)."""
+    import torch
+    import mgwfbp_b200 as hvd
+    from mgwfbp_b200 import settings
+    from mgwfbp_b200.parallel.scheduler import groups_by_threshold
+    net = torch.nn.Sequential(*[torch.nn.Linear(8, 8) for _ in range(6)])
+    names = [n for n, _ in net.named_parameters()]
+    times = [1e-4] * len(names)                     # 0.1 ms of backward per tensor
+    schedule = lambda n, s, t: groups_by_threshold(n, s, 150)           # groups of 5, 5 and 2 tensors, last to first
+
+    def build(**kw):
+        return hvd.DistributedOptimizer(torch.optim.SGD(net.parameters(), lr=0.1), named_parameters=net.named_parameters(),
+                                        seq_layernames=names, layerwise_times=times, schedule=schedule, **kw)
+    assert settings.LATE_GROUP_MS == pytest.approx(0.4)
+    assert sorted(build()._late_groups) == []
+    opt = build(late_full=True)
+    assert [len(g) for g in opt._groups] == [5, 5, 2]
+    # group 1 ends with '1.weight': two tensors (0.2 ms) are left after it -> late; group 0 leaves 0.7 ms -> not late
+    assert sorted(opt._late_groups) == [1]

@@ -104,7 +104,10 @@ class _DenseBlockFn(torch.autograd.Function):
         for c, g, cell, out in reversed(steps):
             head = grad[:, :c]
             cell['sink'], cell['target'] = head.add_, head
-            torch.autograd.backward(out, grad[:, c:c + g])
+            g_out = grad[:, c:c + g]
+            if g_out.dtype != out.dtype:          # mixed precision: the layer ran in a narrower type than the buffer holds
+                g_out = g_out.to(out.dtype)
+            torch.autograd.backward(out, g_out)
             cell.clear()
         return grad[:, :ctx.c0], None
 

@@ -89,3 +89,29 @@ def test_fused_forwards_follow_the_module_through_replication():
     assert isinstance(net.features.denseblock1, tv.models.densenet._DenseBlock)
     fuse_model(net)                                       # idempotent: no second layer of subclasses
     assert type(net.features.denseblock1).__mro__[1] is tv.models.densenet._DenseBlock
+
+
+def test_dense_block_under_autocast():
+    """Mixed precision: layers may produce a narrower type than the block buffer holds; forward and backward still run
+    and agree with the list-and-concatenate path to the precision of the narrow type."""
+    import copy
+    from torchvision.models.densenet import DenseNet
+    from mgwfbp_b200.models.dense_block import fuse_dense_blocks
+    torch.manual_seed(0)
+    ref = DenseNet(growth_rate=8, block_config=(3, 2), num_init_features=16, bn_size=2, num_classes=10).train()
+    ours = copy.deepcopy(ref)
+    fuse_dense_blocks(ours)
+    x = torch.randn(4, 3, 32, 32)
+    y = torch.randint(0, 10, (4,))
+    losses = []
+    for net in (ref, ours):
+        with torch.autocast('cpu', dtype=torch.bfloat16):
+            loss = torch.nn.functional.cross_entropy(net(x).float(), y)
+        loss.backward()
+        losses.append(float(loss))
+    assert abs(losses[0] - losses[1]) < 5e-2
+    for (n, a), b in zip(ours.named_parameters(), ref.parameters()):
+        assert a.grad is not None and a.grad.dtype == b.grad.dtype and torch.isfinite(a.grad).all(), n
+    ga = torch.cat([p.grad.flatten() for p in ours.parameters()])
+    gb = torch.cat([p.grad.flatten() for p in ref.parameters()])
+    assert float((ga - gb).norm() / gb.norm()) < 0.2          # bfloat16 layers: same gradient up to the type's noise

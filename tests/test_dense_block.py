@@ -115,3 +115,28 @@ def test_dense_block_under_autocast():
     ga = torch.cat([p.grad.flatten() for p in ours.parameters()])
     gb = torch.cat([p.grad.flatten() for p in ref.parameters()])
     assert float((ga - gb).norm() / gb.norm()) < 0.2          # bfloat16 layers: same gradient up to the type's noise
+
+
+def test_row_layout_accepts_only_what_the_strided_kernels_can_read():
+    """The BatchNorm kernels read ``x[r * ld + c]``: a dense channels-innermost tensor, or the channels ``[a, a + C)`` of a
+    wider channels-last tensor over ALL of its pixels (any batch range).  Everything else must be refused (and is then
+    copied), because nothing on the device checks the layout."""
+    from mgwfbp_b200.ops.bn_relu import _row_layout
+    w = torch.empty(4, 64, 8, 8).contiguous(memory_format=torch.channels_last)
+    assert _row_layout(w) == (256, 64, 64)
+    assert _row_layout(w[:, :32]) == (256, 32, 64)                  # leading channels
+    assert _row_layout(w[:, 4:36]) == (256, 32, 64)                 # 16-byte aligned channel offset
+    assert _row_layout(w[1:3, :32]) == (128, 32, 64)                # a batch range keeps rows equidistant
+    assert _row_layout(w[:, :30]) == (256, 30, 64)                  # scalar path: no alignment rule on C
+    assert _row_layout(w[:, 1:33]) is None                          # vector path at a 4-byte offset
+    assert _row_layout(w[:, :32, :4]) is None                       # rows of different images are not equidistant
+    assert _row_layout(w[:, :32, :, :4]) is None
+    assert _row_layout(w[:, :32, ::2]) is None
+    assert _row_layout(torch.empty(4, 64, 8, 8)) is None            # NCHW
+    assert _row_layout(torch.empty(4, 64, 8, 8)[:, :32]) is None
+    assert _row_layout(torch.empty(4, 64, 8, 1).contiguous(memory_format=torch.channels_last)[:, :32]) is None   # W = 1
+    odd = torch.empty(4, 66, 8, 8).contiguous(memory_format=torch.channels_last)
+    assert _row_layout(odd[:, :32]) is None                         # row stride 66: rows are not 16-byte aligned
+    assert _row_layout(odd[:, :33]) == (256, 33, 66)
+    two_d = torch.empty(16, 12)
+    assert _row_layout(two_d) == (16, 12, 12) and _row_layout(two_d[:, :8]) is None

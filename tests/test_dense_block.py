@@ -108,7 +108,7 @@ def test_dense_block_under_autocast():
         with torch.autocast('cpu', dtype=torch.bfloat16):
             loss = torch.nn.functional.cross_entropy(net(x).float(), y)
         loss.backward()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
     assert abs(losses[0] - losses[1]) < 5e-2
     for (n, a), b in zip(ours.named_parameters(), ref.parameters()):
         assert a.grad is not None and a.grad.dtype == b.grad.dtype and torch.isfinite(a.grad).all(), n
